@@ -1,0 +1,128 @@
+"""ctypes binding of the C ABI declared in include/flagdnn_b200.h.
+
+The library is loaded from this package directory.  There is no fallback: if
+the library is missing, or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+from typing import Optional
+
+_PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = _PKG_DIR / "libflagdnn_b200.so"
+
+FDNN_OK = 0
+FDNN_BAD_PARAM = 1
+FDNN_NOT_SUPPORTED = 2
+FDNN_ARCH_MISMATCH = 3
+FDNN_WORKSPACE_TOO_SMALL = 4
+FDNN_CUDA_ERROR = 5
+FDNN_DEVICE_TIMEOUT = 6
+
+F16, BF16, F32, F64 = 0, 1, 2, 3
+ALGO_AUTO, ALGO_DIRECT, ALGO_IGEMM = 0, 1, 2
+ACT_NONE, ACT_RELU = 0, 1
+
+EXPORTED_SYMBOLS = (
+    "fdnn_abi_version",
+    "fdnn_status_string",
+    "fdnn_last_error",
+    "fdnn_conv2d_query",
+    "fdnn_conv2d_pack_weight",
+    "fdnn_conv2d_fwd",
+    "fdnn_conv2d_fwd_host",
+    "fdnn_conv2d_host_arena_bytes",
+    "fdnn_device_status",
+)
+
+
+class ConvDesc(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32),
+        ("n", ctypes.c_int32), ("c", ctypes.c_int32), ("h", ctypes.c_int32), ("w", ctypes.c_int32),
+        ("k", ctypes.c_int32), ("r", ctypes.c_int32), ("s", ctypes.c_int32),
+        ("stride_h", ctypes.c_int32), ("stride_w", ctypes.c_int32),
+        ("pad_top", ctypes.c_int32), ("pad_bottom", ctypes.c_int32),
+        ("pad_left", ctypes.c_int32), ("pad_right", ctypes.c_int32),
+        ("dil_h", ctypes.c_int32), ("dil_w", ctypes.c_int32),
+        ("groups", ctypes.c_int32),
+        ("algo", ctypes.c_int32),
+        ("x_strides", ctypes.c_int64 * 4),
+        ("w_strides", ctypes.c_int64 * 4),
+        ("y_strides", ctypes.c_int64 * 4),
+    ]
+
+
+class ConvPlan(ctypes.Structure):
+    _fields_ = [
+        ("algo", ctypes.c_int32),
+        ("oh", ctypes.c_int32), ("ow", ctypes.c_int32),
+        ("tile_m", ctypes.c_int32), ("tile_n", ctypes.c_int32), ("tile_k", ctypes.c_int32),
+        ("stages", ctypes.c_int32),
+        ("x_repacked", ctypes.c_int32),
+        ("w_packed", ctypes.c_int32),
+        ("c_padded", ctypes.c_int32),
+        ("grid", ctypes.c_int32), ("block", ctypes.c_int32),
+        ("launches", ctypes.c_int32),
+        ("workspace_bytes", ctypes.c_int64),
+        ("packed_weight_bytes", ctypes.c_int64),
+        ("smem_bytes", ctypes.c_int64),
+        ("flops", ctypes.c_double),
+        ("bytes", ctypes.c_double),
+    ]
+
+    def as_dict(self) -> dict:
+        return {name: getattr(self, name) for name, _ in self._fields_}
+
+
+class NativeError(RuntimeError):
+    """A non-OK status that maps to RuntimeError in the reference's convention."""
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def load() -> ctypes.CDLL:
+    """Load libflagdnn_b200.so (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m flagdnn_b200.build` "
+            "(there is no CPU or Triton fallback for this path)"
+        )
+    lib = ctypes.CDLL(str(LIB_PATH))
+    vp, i64, i32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
+    lib.fdnn_abi_version.restype = i32
+    lib.fdnn_status_string.restype = ctypes.c_char_p
+    lib.fdnn_status_string.argtypes = [i32]
+    lib.fdnn_last_error.restype = ctypes.c_char_p
+    lib.fdnn_conv2d_query.restype = i32
+    lib.fdnn_conv2d_query.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, ctypes.POINTER(ConvPlan)]
+    lib.fdnn_conv2d_pack_weight.restype = i32
+    lib.fdnn_conv2d_pack_weight.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, i64, vp]
+    lib.fdnn_conv2d_fwd.restype = i32
+    lib.fdnn_conv2d_fwd.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, i32, vp, vp, i64, vp]
+    lib.fdnn_conv2d_fwd_host.restype = i32
+    lib.fdnn_conv2d_fwd_host.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, i32, vp, vp, i64, vp]
+    lib.fdnn_conv2d_host_arena_bytes.restype = i32
+    lib.fdnn_conv2d_host_arena_bytes.argtypes = [ctypes.POINTER(ConvDesc), ctypes.POINTER(i64)]
+    lib.fdnn_device_status.restype = i32
+    lib.fdnn_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
+    _lib = lib
+    return lib
+
+
+def check(status: int) -> None:
+    """Translate a status code into the exception the reference would raise."""
+    if status == FDNN_OK:
+        return
+    lib = load()
+    detail = lib.fdnn_last_error().decode("utf-8", "replace")
+    text = lib.fdnn_status_string(status).decode()
+    msg = f"{detail} [{text}]" if detail else text
+    if status in (FDNN_NOT_SUPPORTED, FDNN_ARCH_MISMATCH):
+        raise NotImplementedError(msg)
+    raise NativeError(msg)

@@ -1,0 +1,340 @@
+"""Host side of the conv2d hot path: same signatures, checks and exceptions as
+the reference's ``flag_dnn.ops.conv2d`` (src/flag_dnn/ops/conv2d.py:3575-3611)
+and ``fused_conv2d_bias_relu`` (src/flag_dnn/graph/kernels/fused_conv.py:62-130),
+with the Triton launches replaced by calls into the C ABI
+(include/flagdnn_b200.h).  There is no CPU fallback: CPU tensors raise
+``NotImplementedError`` exactly as the reference does.
+"""
+from __future__ import annotations
+
+import ctypes
+import weakref
+from collections import OrderedDict
+from typing import Any, Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _native as nat
+
+_DTYPE_IDS = {
+    torch.float16: nat.F16,
+    torch.bfloat16: nat.BF16,
+    torch.float32: nat.F32,
+    torch.float64: nat.F64,
+}
+
+# Packed filters are kept in a small LRU keyed on tensor identity and version,
+# validated with a weak reference, like src/flag_dnn/ops/conv2d.py:24-32, 154-190.
+_PACKED_WEIGHT_CACHE: "OrderedDict[tuple, tuple[weakref.ReferenceType, torch.Tensor]]" = OrderedDict()
+_PACKED_WEIGHT_CACHE_MAX = 32
+
+# Plans are pure functions of geometry, strides and pointer alignment.
+_PLAN_CACHE: "OrderedDict[tuple, tuple[nat.ConvDesc, nat.ConvPlan]]" = OrderedDict()
+_PLAN_CACHE_MAX = 256
+
+_FORCED_ALGO = nat.ALGO_AUTO
+
+
+def set_algo(algo: Union[int, str]) -> int:
+    """Force the kernel family for subsequent calls: "auto", "direct" or "igemm".
+
+    Returns the previous setting.  Meant for tests and benchmarks.
+    """
+    global _FORCED_ALGO
+    names = {"auto": nat.ALGO_AUTO, "direct": nat.ALGO_DIRECT, "igemm": nat.ALGO_IGEMM}
+    prev = _FORCED_ALGO
+    _FORCED_ALGO = names[algo] if isinstance(algo, str) else int(algo)
+    return prev
+
+
+def _pair(v: Union[int, Sequence[int]]) -> Tuple[int, int]:
+    if isinstance(v, int):
+        return v, v
+    if len(v) != 2:
+        raise RuntimeError(f"expected length 2, but got {v}")
+    return int(v[0]), int(v[1])
+
+
+def _conv_out_dim(size: int, pad_before: int, pad_after: int, dilation: int, kernel: int, stride: int) -> int:
+    return (size + pad_before + pad_after - dilation * (kernel - 1) - 1) // stride + 1
+
+
+def _normalize_padding(weight, stride, padding, dilation) -> Tuple[int, int, int, int]:
+    """(top, bottom, left, right); rule of src/flag_dnn/ops/conv2d.py:65-87."""
+    if isinstance(padding, str):
+        if padding == "valid":
+            return (0, 0, 0, 0)
+        if padding == "same":
+            if stride != (1, 1):
+                raise RuntimeError("padding='same' is not supported for strided convolutions")
+            kh, kw = weight.shape[2], weight.shape[3]
+            pad_h = max(dilation[0] * (kh - 1), 0)
+            pad_w = max(dilation[1] * (kw - 1), 0)
+            return (pad_h // 2, pad_h - pad_h // 2, pad_w // 2, pad_w - pad_w // 2)
+        raise RuntimeError("padding must be 'valid', 'same', int, or tuple")
+    pad_h, pad_w = _pair(padding)
+    return (pad_h, pad_h, pad_w, pad_w)
+
+
+def _check_conv2d_inputs(input, weight, bias, stride, padding, dilation, groups) -> None:
+    """Same checks and messages as src/flag_dnn/ops/conv2d.py:90-135."""
+    if input.dim() != 4 or weight.dim() != 4:
+        raise RuntimeError("flag_dnn conv2d expects 4D input and weight")
+    if input.dtype not in _DTYPE_IDS:
+        raise NotImplementedError(f"Unsupported dtype: {input.dtype}")
+    if weight.dtype != input.dtype:
+        raise RuntimeError("input and weight must have the same dtype")
+    if input.device != weight.device:
+        raise RuntimeError("input and weight must be on the same device")
+    if bias is not None:
+        if bias.dtype != input.dtype:
+            raise RuntimeError("bias must have the same dtype as input")
+        if bias.device != input.device:
+            raise RuntimeError("bias must be on the same device as input")
+    if groups <= 0:
+        raise RuntimeError("groups must be a positive integer")
+    if stride[0] <= 0 or stride[1] <= 0:
+        raise RuntimeError("stride must be positive")
+    if dilation[0] <= 0 or dilation[1] <= 0:
+        raise RuntimeError("dilation must be positive")
+    if min(padding) < 0:
+        raise RuntimeError("negative padding is not supported")
+    c_in = input.shape[1]
+    c_out, c_per_group = weight.shape[0], weight.shape[1]
+    if c_in % groups != 0 or c_out % groups != 0:
+        raise RuntimeError("channels must be divisible by groups")
+    if c_per_group != c_in // groups:
+        raise RuntimeError("weight.shape[1] must match input_channels // groups")
+    if bias is not None and (bias.dim() != 1 or bias.numel() != c_out):
+        raise RuntimeError(f"bias shape mismatch, expected ({c_out},)")
+
+
+def _ptr(t: torch.Tensor) -> int:
+    return 0 if t.device.type == "meta" else t.data_ptr()
+
+
+def _plan_for(input, weight, out, stride, padding4, dilation, groups, algo):
+    key = (
+        input.dtype, tuple(input.shape), tuple(input.stride()), tuple(weight.shape), tuple(weight.stride()),
+        tuple(out.stride()), stride, padding4, dilation, groups, algo,
+        _ptr(input) % 16, _ptr(weight) % 16, _ptr(out) % 16,
+    )
+    hit = _PLAN_CACHE.get(key)
+    if hit is not None:
+        _PLAN_CACHE.move_to_end(key)
+        return hit
+    lib = nat.load()
+    d = nat.ConvDesc()
+    d.dtype = _DTYPE_IDS[input.dtype]
+    d.n, d.c, d.h, d.w = input.shape
+    d.k, _, d.r, d.s = weight.shape
+    d.stride_h, d.stride_w = stride
+    d.pad_top, d.pad_bottom, d.pad_left, d.pad_right = padding4
+    d.dil_h, d.dil_w = dilation
+    d.groups = groups
+    d.algo = algo
+    for i in range(4):
+        d.x_strides[i] = input.stride(i)
+        d.w_strides[i] = weight.stride(i)
+        d.y_strides[i] = out.stride(i)
+    plan = nat.ConvPlan()
+    nat.check(lib.fdnn_conv2d_query(ctypes.byref(d), _ptr(input) or None, _ptr(weight) or None,
+                                    _ptr(out) or None, ctypes.byref(plan)))
+    _PLAN_CACHE[key] = (d, plan)
+    while len(_PLAN_CACHE) > _PLAN_CACHE_MAX:
+        _PLAN_CACHE.popitem(last=False)
+    return d, plan
+
+
+def _packed_weight(weight: torch.Tensor, d: nat.ConvDesc, plan: nat.ConvPlan, stream: int) -> torch.Tensor:
+    version = int(getattr(weight, "_version", 0))
+    key = ("krsc", id(weight), weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()),
+           str(weight.dtype), weight.device.type, weight.device.index, version)
+    entry = _PACKED_WEIGHT_CACHE.get(key)
+    if entry is not None:
+        owner_ref, value = entry
+        if owner_ref() is weight:
+            _PACKED_WEIGHT_CACHE.move_to_end(key)
+            return value
+        del _PACKED_WEIGHT_CACHE[key]
+    packed = torch.empty(plan.packed_weight_bytes, dtype=torch.uint8, device=weight.device)
+    nat.check(nat.load().fdnn_conv2d_pack_weight(ctypes.byref(d), weight.data_ptr(), packed.data_ptr(),
+                                                 plan.packed_weight_bytes, stream))
+    _PACKED_WEIGHT_CACHE[key] = (weakref.ref(weight), packed)
+    while len(_PACKED_WEIGHT_CACHE) > _PACKED_WEIGHT_CACHE_MAX:
+        _PACKED_WEIGHT_CACHE.popitem(last=False)
+    return packed
+
+
+def conv2d_plan(input, weight, stride=1, padding=0, dilation=1, groups=1, algo=None) -> dict:
+    """What the library would do for this call (kernel family, tile, scratch sizes)."""
+    stride = _pair(stride)
+    dilation = _pair(dilation)
+    padding4 = _normalize_padding(weight, stride, padding, dilation)
+    n, _, h, w = input.shape
+    c_out, _, kh, kw = weight.shape
+    oh = max(_conv_out_dim(h, padding4[0], padding4[1], dilation[0], kh, stride[0]), 0)
+    ow = max(_conv_out_dim(w, padding4[2], padding4[3], dilation[1], kw, stride[1]), 0)
+    out = _empty_output(input, n, c_out, oh, ow, meta=True)
+    _, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups,
+                        _FORCED_ALGO if algo is None else algo)
+    return plan.as_dict()
+
+
+def _empty_output(input, n, c_out, oh, ow, meta=False):
+    # channels_last output iff the input has unit channel stride
+    # (src/flag_dnn/ops/conv2d.py:3729-3738, fused_conv.py:120-130); fp64 always
+    # produces a contiguous NCHW tensor (conv2d.py:3631-3633).
+    use_cl = input.dim() == 4 and input.stride(1) == 1 and input.dtype != torch.float64
+    return torch.empty(
+        (n, c_out, oh, ow),
+        device="meta" if meta else input.device,
+        dtype=input.dtype,
+        memory_format=torch.channels_last if use_cl else torch.contiguous_format,
+    )
+
+
+def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activation) -> torch.Tensor:
+    n, _, h, w = input.shape
+    c_out, _, kh, kw = weight.shape
+    oh = _conv_out_dim(h, padding4[0], padding4[1], dilation[0], kh, stride[0])
+    ow = _conv_out_dim(w, padding4[2], padding4[3], dilation[1], kw, stride[1])
+    if oh < 0 or ow < 0:
+        raise RuntimeError("computed output size is negative")
+    if oh == 0 or ow == 0:
+        return torch.empty((n, c_out, max(oh, 0), max(ow, 0)), device=input.device, dtype=input.dtype)
+    if bias is not None and not bias.is_contiguous():
+        bias = bias.contiguous()
+    if scale is not None and not scale.is_contiguous():
+        scale = scale.contiguous()
+    lib = nat.load()
+    with torch.cuda.device(input.device):
+        out = _empty_output(input, n, c_out, oh, ow)
+        if n == 0:
+            return out
+        d, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups, _FORCED_ALGO)
+        stream = torch.cuda.current_stream().cuda_stream
+        packed_ptr = None
+        packed = None
+        if plan.algo == nat.ALGO_IGEMM and plan.w_packed:
+            packed = _packed_weight(weight, d, plan, stream)
+            packed_ptr = packed.data_ptr()
+        ws_ptr = None
+        ws = None
+        if plan.workspace_bytes > 0:
+            ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=input.device)
+            ws_ptr = ws.data_ptr()
+        nat.check(lib.fdnn_conv2d_fwd(
+            ctypes.byref(d), input.data_ptr(), weight.data_ptr(), packed_ptr,
+            None if bias is None else bias.data_ptr(),
+            None if scale is None else scale.data_ptr(),
+            activation, out.data_ptr(), ws_ptr, plan.workspace_bytes, stream))
+        if ws is not None:
+            ws.record_stream(torch.cuda.current_stream())
+    return out
+
+
+def conv2d(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    stride: Union[int, Tuple[int, int]] = 1,
+    padding: Union[str, int, Tuple[int, int]] = 0,
+    dilation: Union[int, Tuple[int, int]] = 1,
+    groups: int = 1,
+) -> torch.Tensor:
+    """Drop-in for ``flag_dnn.ops.conv2d`` (src/flag_dnn/ops/conv2d.py:3575)."""
+    stride = _pair(stride)
+    dilation = _pair(dilation)
+    padding4 = _normalize_padding(weight, stride, padding, dilation)
+    _check_conv2d_inputs(input, weight, bias, stride, padding4, dilation, groups)
+    if not input.is_cuda:
+        raise NotImplementedError("flag_dnn conv2d CUDA implementation requires CUDA input")
+    return _run(input, weight, bias, None, stride, padding4, dilation, groups, nat.ACT_NONE)
+
+
+def fused_conv2d_bias_relu(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    bias: torch.Tensor,
+    *,
+    stride: Union[int, Tuple[int, int]] = 1,
+    padding: Union[str, int, Tuple[int, int]] = 0,
+    dilation: Union[int, Tuple[int, int]] = 1,
+    groups: int = 1,
+    config: Optional[dict[str, Any]] = None,
+    scale: Optional[torch.Tensor] = None,
+    activation: str = "relu",
+) -> torch.Tensor:
+    """Drop-in for the reference's fused op (src/flag_dnn/graph/kernels/fused_conv.py:62-72).
+
+    ``config`` (the reference's Triton tile override) is accepted and ignored.
+    Two additions the reference's callers never pass: ``scale`` (BN-folded
+    per-channel multiplier applied before the bias) and ``activation`` ("relu"
+    or "none").
+    """
+    del config
+    if not (isinstance(input, torch.Tensor) and input.is_cuda):
+        raise NotImplementedError("fused_conv2d_bias_relu requires runtime device input")
+    if groups != 1:
+        raise NotImplementedError("fused_conv2d_bias_relu currently supports groups=1")
+    if input.dim() != 4 or weight.dim() != 4 or bias.dim() != 1:
+        raise RuntimeError("fused_conv2d_bias_relu expects 4D input/weight and 1D bias")
+    if input.dtype != weight.dtype or input.dtype != bias.dtype:
+        raise RuntimeError("input, weight, and bias must have the same dtype")
+    if input.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise NotImplementedError(f"fused_conv2d_bias_relu does not support dtype={input.dtype}")
+    if input.device != weight.device or input.device != bias.device:
+        raise RuntimeError("input, weight, and bias must be on the same device")
+    if scale is not None and (scale.dtype != input.dtype or scale.device != input.device or scale.dim() != 1):
+        raise RuntimeError("scale must be a 1D tensor with the dtype and device of input")
+    if activation not in ("relu", "none"):
+        raise NotImplementedError(f"unsupported activation {activation!r}")
+    stride = _pair(stride)
+    dilation = _pair(dilation)
+    padding4 = _normalize_padding(weight, stride, padding, dilation)
+    c_in = input.shape[1]
+    c_out, c_per_group = weight.shape[0], weight.shape[1]
+    if c_per_group != c_in:
+        raise RuntimeError("weight.shape[1] must match input channels for groups=1")
+    if bias.numel() != c_out:
+        raise RuntimeError(f"bias shape mismatch, expected ({c_out},)")
+    if scale is not None and scale.numel() != c_out:
+        raise RuntimeError(f"scale shape mismatch, expected ({c_out},)")
+    act = nat.ACT_RELU if activation == "relu" else nat.ACT_NONE
+    return _run(input, weight, bias, scale, stride, padding4, dilation, 1, act)
+
+
+def conv2d_bias_act(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    *,
+    stride: Union[int, Tuple[int, int]] = 1,
+    padding: Union[str, int, Tuple[int, int]] = 0,
+    dilation: Union[int, Tuple[int, int]] = 1,
+    groups: int = 1,
+    scale: Optional[torch.Tensor] = None,
+    relu: bool = False,
+) -> torch.Tensor:
+    """conv2d with the full epilogue (scale, bias, ReLU) and conv2d's argument
+    range (any groups, fp64).  The graph executor uses it for fused nodes that
+    fall outside ``fused_conv2d_bias_relu``'s contract."""
+    stride = _pair(stride)
+    dilation = _pair(dilation)
+    padding4 = _normalize_padding(weight, stride, padding, dilation)
+    _check_conv2d_inputs(input, weight, bias, stride, padding4, dilation, groups)
+    if not input.is_cuda:
+        raise NotImplementedError("flag_dnn conv2d CUDA implementation requires CUDA input")
+    return _run(input, weight, bias, scale, stride, padding4, dilation, groups,
+                nat.ACT_RELU if relu else nat.ACT_NONE)
+
+
+def device_status() -> int:
+    """Synchronise the current device and return its incident word (0 = clean)."""
+    word = ctypes.c_uint32(0)
+    lib = nat.load()
+    status = lib.fdnn_device_status(ctypes.byref(word))
+    if status not in (nat.FDNN_OK, nat.FDNN_DEVICE_TIMEOUT):
+        nat.check(status)
+    return int(word.value)

@@ -1,0 +1,423 @@
+// Implicit-GEMM convolution forward for sm_100a.
+//
+//   y[m, k] = act( scale[k] * sum_{r,s,c} x[n, oh*sh + r*dh - pt, ow*sw + s*dw - pl, c] * w[k, r, s, c] + bias[k] )
+//
+// with m = (n, oh, ow) flattened.  One persistent CTA per SM walks 128-row
+// output tiles.  Three roles, one pipeline:
+//   warp 0      TMA producer: per (r, s, channel block) one im2col-mode copy of
+//               128 pixels x 128 bytes of activations (padding arrives as the
+//               copy's zero fill) and one tiled copy of the filter slice, into
+//               a ring of shared-memory stages guarded by full/empty mbarriers;
+//   warp 1      MMA issuer: tcgen05.mma from shared-memory descriptors into one
+//               of two fp32 accumulators in tensor memory; tcgen05.commit frees
+//               the stage and, after the last reduction step, publishes the
+//               accumulator;
+//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator, per-channel
+//               scale, bias, ReLU, one rounding to the output type, store —
+//               while the issuer already fills the other accumulator.
+// fp32 tensors run the same loop on TF32-split operands (high and low halves
+// staged side by side): lo*hi + hi*lo + hi*hi per reduction step.
+//
+// The arithmetic restated here is that of the reference's fused kernel
+// (src/flag_dnn/graph/kernels/fused_conv.py:249-310): fp32 accumulate, bias
+// added in fp32, max(., 0), single cast at the store.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
+#include "conv_internal.h"
+#include "sm100_ptx.cuh"
+
+namespace fdnn {
+
+namespace {
+
+constexpr int kBM = 128;            // output rows per tile (= tcgen05 M, = TMEM lanes)
+constexpr int kRowBytes = 128;      // one swizzled shared-memory row
+constexpr int kThreads = 192;       // 6 warps: producer, issuer, 4 epilogue
+constexpr int kEpiWarps = 4;
+
+template <typename T, int BN>
+struct TileCfg {
+  static constexpr bool kSplit = std::is_same<T, float>::value;
+  static constexpr int kKB = kRowBytes / int(sizeof(T));  // reduction elements per stage
+  static constexpr int kUK = 32 / int(sizeof(T));         // reduction elements per MMA
+  static constexpr int kABytes = kBM * kRowBytes;
+  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kStageBytes = (kSplit ? 2 : 1) * (kABytes + kBBytes);
+  static constexpr int kStages = (192 * 1024) / kStageBytes;
+  static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128, 256 or 512
+  // per-warp scale and bias staging, then barriers and bookkeeping words
+  static constexpr int kEpiBytes = kEpiWarps * 2 * BN * int(sizeof(float));
+  static constexpr int kBarBytes = (2 * kStages + 4 + 1) * 8 + 16;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
+  static_assert(kStages >= 2, "pipeline needs at least two stages");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+};
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ uint32_t pack2(__half a, __half b) {
+  __half2 h = __halves2half2(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack2(__nv_bfloat16 a, __nv_bfloat16 b) {
+  __nv_bfloat162 h = __halves2bfloat162(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// 32 finished values of one output pixel -> 32 consecutive channels of y.
+template <typename T>
+__device__ __forceinline__ void store32_contig(T* dst, const float (&v)[32]) {
+  if constexpr (std::is_same<T, float>::value) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float4 q = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      reinterpret_cast<float4*>(dst)[i] = q;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 q;
+      q.x = pack2(from_f32<T>(v[8 * i + 0]), from_f32<T>(v[8 * i + 1]));
+      q.y = pack2(from_f32<T>(v[8 * i + 2]), from_f32<T>(v[8 * i + 3]));
+      q.z = pack2(from_f32<T>(v[8 * i + 4]), from_f32<T>(v[8 * i + 5]));
+      q.w = pack2(from_f32<T>(v[8 * i + 6]), from_f32<T>(v[8 * i + 7]));
+      reinterpret_cast<uint4*>(dst)[i] = q;
+    }
+  }
+}
+
+template <typename T, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+                  const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
+                  const IgemmParams p) {
+  using Cfg = TileCfg<T, BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : (std::is_same<T, __nv_bfloat16>::value ? 1u : 2u);
+  constexpr uint32_t kIdesc = make_idesc(kFmt, kBM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  float* epi_stage = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kEpiBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + kStages;
+  uint64_t* tmem_full = bars + 2 * kStages;       // [2]
+  uint64_t* tmem_empty = bars + 2 * kStages + 2;  // [2]
+  uint64_t* drain_bar = bars + 2 * kStages + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_full[1], 1);
+    mbar_init(&tmem_empty[0], kEpiWarps * 32);
+    mbar_init(&tmem_empty[1], kEpiWarps * 32);
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if constexpr (Cfg::kSplit) {
+      tma_prefetch_desc(&tmA2);
+      tma_prefetch_desc(&tmB2);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int k_iters = p.R * p.S * p.c_blocks;
+  const int ohw = p.OH * p.OW;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        const int m_tile = tile / p.n_tiles;
+        const int n_tile = tile - m_tile * p.n_tiles;
+        const int m0 = m_tile * kBM;
+        const int img = m0 / ohw;
+        const int rem = m0 - img * ohw;
+        const int oh0 = rem / p.OW;
+        const int ow0 = rem - oh0 * p.OW;
+        const int w_base = ow0 * p.stride_w - p.pad_left;
+        const int h_base = oh0 * p.stride_h - p.pad_top;
+        for (int r = 0; r < p.R && alive; ++r) {
+          for (int s = 0; s < p.S && alive; ++s) {
+            const uint16_t off_w = static_cast<uint16_t>(s * p.dil_w);
+            const uint16_t off_h = static_cast<uint16_t>(r * p.dil_h);
+            const int tap = r * p.S + s;
+            for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
+              const uint32_t stage = it % kStages;
+              const uint32_t phase = (it / kStages) & 1u;
+              if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
+                                     kIncidentProducerWait)) {
+                alive = false;
+                break;
+              }
+              uint8_t* st = stage_base + stage * Cfg::kStageBytes;
+              mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+              const int c0 = cb * Cfg::kKB;
+              tma_load_im2col_4d(st, &tmA, &full_bar[stage], c0, w_base, h_base, img, off_w, off_h);
+              if constexpr (Cfg::kSplit) {
+                tma_load_im2col_4d(st + Cfg::kABytes, &tmA2, &full_bar[stage], c0, w_base, h_base,
+                                   img, off_w, off_h);
+                tma_load_3d(st + 2 * Cfg::kABytes, &tmB, &full_bar[stage], c0, tap, n_tile * BN);
+                tma_load_3d(st + 2 * Cfg::kABytes + Cfg::kBBytes, &tmB2, &full_bar[stage], c0, tap,
+                            n_tile * BN);
+              } else {
+                tma_load_3d(st + Cfg::kABytes, &tmB, &full_bar[stage], c0, tap, n_tile * BN);
+              }
+            }
+          }
+        }
+      }
+      if (!alive || *abort_flag) {
+        // Teardown after an incident: let the copies already issued land before
+        // the CTA gives its shared memory back.
+        const uint32_t first = it > uint32_t(kStages) ? it - kStages : 0u;
+        for (uint32_t j = first; j < it; ++j) {
+          volatile uint32_t never = 0;
+          mbar_wait_bounded(&full_bar[j % kStages], (j / kStages) & 1u, &never, p.status,
+                            kIncidentDrainWait, kWaitLimitCycles / 16);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- issuer
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t tcount = 0;
+      bool alive = true;
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++tcount) {
+        const uint32_t buf = tcount & 1u;
+        const uint32_t bphase = (tcount >> 1) & 1u;
+        if (!mbar_wait_bounded(&tmem_empty[buf], bphase ^ 1u, abort_flag, p.status,
+                               kIncidentMmaWaitTmem)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kit = 0; kit < k_iters; ++kit, ++it) {
+          const uint32_t stage = it % kStages;
+          const uint32_t phase = (it / kStages) & 1u;
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status,
+                                 kIncidentMmaWaitFull)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t st = smem_u32(stage_base + stage * Cfg::kStageBytes);
+#pragma unroll
+          for (int k = 0; k < Cfg::kKB / Cfg::kUK; ++k) {
+            const uint32_t acc = (kit > 0 || k > 0) ? 1u : 0u;
+            if constexpr (Cfg::kSplit) {
+              const uint64_t a_hi = make_sw128_kmajor_desc(st + k * 32);
+              const uint64_t a_lo = make_sw128_kmajor_desc(st + Cfg::kABytes + k * 32);
+              const uint64_t b_hi = make_sw128_kmajor_desc(st + 2 * Cfg::kABytes + k * 32);
+              const uint64_t b_lo =
+                  make_sw128_kmajor_desc(st + 2 * Cfg::kABytes + Cfg::kBBytes + k * 32);
+              mma_tf32(d_tmem, a_lo, b_hi, kIdesc, acc);
+              mma_tf32(d_tmem, a_hi, b_lo, kIdesc, 1u);
+              mma_tf32(d_tmem, a_hi, b_hi, kIdesc, 1u);
+            } else {
+              const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
+              const uint64_t b = make_sw128_kmajor_desc(st + Cfg::kABytes + k * 32);
+              mma_f16(d_tmem, a, b, kIdesc, acc);
+            }
+          }
+          tc_commit(&empty_bar[stage]);
+        }
+        if (alive) tc_commit(&tmem_full[buf]);
+      }
+      if (!alive || *abort_flag) {
+        // Make sure no MMA is still writing tensor memory before it is freed.
+        volatile uint32_t never = 0;
+        tc_commit(drain_bar);
+        mbar_wait_bounded(drain_bar, 0u, &never, p.status, kIncidentDrainWait, kWaitLimitCycles / 16);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int ew = warp & 3;  // tensor-memory lane quarter this warp may read
+    float* s_scale = epi_stage + (warp - 2) * 2 * BN;
+    float* s_bias = s_scale + BN;
+    const T* g_bias = static_cast<const T*>(p.bias);
+    const T* g_scale = static_cast<const T*>(p.scale);
+    T* y = static_cast<T*>(p.y);
+    uint32_t tcount = 0;
+    int staged_n_tile = -1;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+      const int m_tile = tile / p.n_tiles;
+      const int n_tile = tile - m_tile * p.n_tiles;
+      const int n0 = n_tile * BN;
+      const uint32_t buf = tcount & 1u;
+      const uint32_t bphase = (tcount >> 1) & 1u;
+
+      if (n_tile != staged_n_tile) {
+        __syncwarp();
+        for (int j = lane; j < BN; j += 32) {
+          const int col = n0 + j;
+          s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col]) : 1.0f;
+          s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col]) : 0.0f;
+        }
+        __syncwarp();
+        staged_n_tile = n_tile;
+      }
+
+      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+
+      const int m = m_tile * kBM + ew * 32 + lane;
+      const bool row_ok = m < p.M;
+      long long y_off = 0;
+      if (row_ok) {
+        const int img = m / ohw;
+        const int rem = m - img * ohw;
+        const int oh = rem / p.OW;
+        const int ow = rem - oh * p.OW;
+        y_off = img * p.y_sn + oh * p.y_sh + ow * p.y_sw;
+      }
+      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        const int col0 = n0 + chunk * 32;
+        if (col0 >= p.Kout) break;  // uniform across the warp
+        uint32_t raw[32];
+        tmem_ld_32x32b_x32(t_row + chunk * 32, raw);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float a = __uint_as_float(raw[j]);
+          a = fmaf(a, s_scale[chunk * 32 + j], s_bias[chunk * 32 + j]);
+          if (p.relu) a = (a < 0.0f) ? 0.0f : a;  // keeps NaN, like torch.relu
+          v[j] = a;
+        }
+        if (row_ok) {
+          if (p.vec_store && col0 + 32 <= p.Kout) {
+            store32_contig<T>(y + y_off + col0, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.Kout) y[y_off + (long long)(col0 + j) * p.y_sk] = from_f32<T>(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <typename T, int BN>
+cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
+                       const CUtensorMap& tmB2, const IgemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = TileCfg<T, BN>;
+  conv_igemm_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, p);
+  return cudaGetLastError();
+}
+
+template <typename T, int BN>
+cudaError_t prepare_one() {
+  using Cfg = TileCfg<T, BN>;
+  return cudaFuncSetAttribute(conv_igemm_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Cfg::kSmemBytes);
+}
+
+}  // namespace
+
+cudaError_t igemm_prepare_device() {
+  cudaError_t e;
+#define FDNN_PREP(T, BN)                 \
+  e = prepare_one<T, BN>();              \
+  if (e != cudaSuccess) return e;
+  FDNN_PREP(__half, 64) FDNN_PREP(__half, 128) FDNN_PREP(__half, 256)
+  FDNN_PREP(__nv_bfloat16, 64) FDNN_PREP(__nv_bfloat16, 128) FDNN_PREP(__nv_bfloat16, 256)
+  FDNN_PREP(float, 64) FDNN_PREP(float, 128)
+#undef FDNN_PREP
+  return cudaSuccess;
+}
+
+int igemm_smem_bytes(int dtype, int tile_n) {
+  if (dtype == FDNN_F32) return tile_n == 64 ? TileCfg<float, 64>::kSmemBytes : TileCfg<float, 128>::kSmemBytes;
+  if (tile_n == 64) return TileCfg<__half, 64>::kSmemBytes;
+  if (tile_n == 128) return TileCfg<__half, 128>::kSmemBytes;
+  return TileCfg<__half, 256>::kSmemBytes;
+}
+
+int igemm_stages(int dtype, int tile_n) {
+  if (dtype == FDNN_F32) return tile_n == 64 ? TileCfg<float, 64>::kStages : TileCfg<float, 128>::kStages;
+  if (tile_n == 64) return TileCfg<__half, 64>::kStages;
+  if (tile_n == 128) return TileCfg<__half, 128>::kStages;
+  return TileCfg<__half, 256>::kStages;
+}
+
+cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
+                         const CUtensorMap& tmB, const CUtensorMap& tmB2, const IgemmParams& p,
+                         int grid, cudaStream_t stream) {
+#define FDNN_GO(T, BN) return launch_one<T, BN>(tmA, tmA2, tmB, tmB2, p, grid, stream);
+  if (dtype == FDNN_F16) {
+    if (tile_n == 64) FDNN_GO(__half, 64)
+    if (tile_n == 128) FDNN_GO(__half, 128)
+    if (tile_n == 256) FDNN_GO(__half, 256)
+  } else if (dtype == FDNN_BF16) {
+    if (tile_n == 64) FDNN_GO(__nv_bfloat16, 64)
+    if (tile_n == 128) FDNN_GO(__nv_bfloat16, 128)
+    if (tile_n == 256) FDNN_GO(__nv_bfloat16, 256)
+  } else if (dtype == FDNN_F32) {
+    if (tile_n == 64) FDNN_GO(float, 64)
+    if (tile_n == 128) FDNN_GO(float, 128)
+  }
+#undef FDNN_GO
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fdnn

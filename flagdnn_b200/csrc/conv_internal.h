@@ -1,0 +1,71 @@
+// Internal declarations shared by the C-ABI front end (conv_api.cu) and the
+// kernel translation units.  Nothing here is exported.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/flagdnn_b200.h"
+
+namespace fdnn {
+
+// Per-device incident word written by bounded waits (see sm100_ptx.cuh).
+uint32_t* device_status_word();  // device address for the current device, or nullptr on error
+
+// Geometry handed to the implicit-GEMM kernel.  GEMM view: rows m = (n, oh, ow)
+// flattened, columns = output channels, reduction = (r, s, c) with c innermost.
+struct IgemmParams {
+  int M;                 // N * OH * OW
+  int Kout;              // output channels
+  int OH, OW;
+  int stride_h, stride_w, pad_top, pad_left, dil_h, dil_w;
+  int R, S;
+  int c_blocks;          // ceil(Cpad / channels per 128-byte row)
+  int m_tiles, n_tiles;
+  long long y_sn, y_sk, y_sh, y_sw;  // element strides of y
+  const void* bias;      // [Kout] in the tensor dtype, or nullptr
+  const void* scale;     // [Kout] in the tensor dtype, or nullptr
+  void* y;
+  int relu;
+  int vec_store;         // 1: y is channel-contiguous and 16-byte aligned per pixel
+  uint32_t* status;
+};
+
+// Launchers (defined in conv_igemm_sm100.cu).  `dtype` is FDNN_F16/BF16/F32.
+// tmA2 / tmB2 are the low-half operands of the split-TF32 path (ignored for
+// 16-bit types).  Returns a cudaError_t from the launch.
+cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
+                         const CUtensorMap& tmB, const CUtensorMap& tmB2, const IgemmParams& p,
+                         int grid, cudaStream_t stream);
+// Dynamic shared memory and pipeline depth of a tile configuration.
+int igemm_smem_bytes(int dtype, int tile_n);
+int igemm_stages(int dtype, int tile_n);
+// One-time opt-in to large dynamic shared memory for every instantiation.
+cudaError_t igemm_prepare_device();
+
+// Direct convolution on CUDA cores (conv_direct.cu): any dtype, groups, strides.
+struct DirectParams {
+  int N, C, H, W, K, R, S, OH, OW;
+  int stride_h, stride_w, pad_top, pad_left, dil_h, dil_w, groups;
+  long long x_s[4], w_s[4], y_s[4];
+  const void* x;
+  const void* w;
+  const void* bias;
+  const void* scale;
+  void* y;
+  int relu;
+};
+cudaError_t launch_direct(int dtype, const DirectParams& p, cudaStream_t stream);
+
+// Relayout kernels (conv_repack.cu).
+// x[N,C,H,W] (any strides) -> dense NHWC with C padded to c_pad (zeros).  For
+// f32 two planes are written: TF32-rounded high halves at dst, the rounded
+// remainders at dst + plane_elems.
+cudaError_t launch_repack_x(int dtype, const void* x, const long long x_s[4], int N, int C, int H,
+                            int W, int c_pad, void* dst, long long plane_elems,
+                            cudaStream_t stream);
+// w[K,C,R,S] (any strides) -> dense [K,R,S,c_pad]; f32 split like x.
+cudaError_t launch_pack_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
+                          int S, int c_pad, void* dst, long long plane_elems, cudaStream_t stream);
+
+}  // namespace fdnn

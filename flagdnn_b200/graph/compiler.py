@@ -1,0 +1,390 @@
+"""Capture -> optimise -> plan -> run, the user-facing half of the graph API.
+
+Mirrors the call surface of the reference (src/flag_dnn/graph/capture.py:
+109-208 ``graph`` / ``compile`` / ``CompiledGraph``; planner, kernel selector
+and executor in src/flag_dnn/graph/{planner,kernel_selector,backend,executor,
+plan,cache}.py) for graphs built from the ops this package registers.  The
+keys of ``plan.debug_info`` that the reference's tests read ("fusion",
+"kernel_candidates", "backend", "cache_hit", "cache_layer", "autotune",
+"candidate_count") are kept.
+"""
+from __future__ import annotations
+
+import functools
+import hashlib
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Callable, Optional
+
+import torch
+
+from .ir import Graph
+from .passes import apply_fusion_pass, eliminate_dead_nodes
+from .registry import get_op_schema
+from .spec import GraphTensor, TensorSpec, torch_dtype
+
+_CAPTURE_STACK: list = []
+
+
+def is_capturing() -> bool:
+    return bool(_CAPTURE_STACK)
+
+
+def current_capture() -> Optional["GraphCapture"]:
+    return _CAPTURE_STACK[-1] if _CAPTURE_STACK else None
+
+
+class GraphCapture:
+    """Context in which op wrappers record nodes instead of running kernels."""
+
+    def __init__(self, input_specs: list):
+        self.graph = Graph()
+        self.input_specs = input_specs
+        self.graph_inputs: list = []
+
+    def __enter__(self) -> "GraphCapture":
+        _CAPTURE_STACK.append(self)
+        for index, spec in enumerate(self.input_specs):
+            self.graph_inputs.append(self.graph.add_input(spec if spec.name else spec.with_name(f"arg{index}")))
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        if _CAPTURE_STACK.pop() is not self:
+            raise RuntimeError("graph capture stack is corrupted")
+
+    def is_tensor_like(self, value: Any) -> bool:
+        return isinstance(value, (GraphTensor, torch.Tensor))
+
+    def as_value(self, value: Any, name_hint: str = "value") -> int:
+        if isinstance(value, GraphTensor):
+            if value.graph is not self.graph:
+                raise RuntimeError("cannot mix GraphTensor values from graphs")
+            return value.value_id
+        if isinstance(value, (torch.Tensor, int, float, bool)):
+            return self.graph.add_constant(value, name_hint=name_hint).value_id
+        raise TypeError(f"unsupported graph operand type: {type(value)!r}")
+
+    def add_op_call(self, op_type: str, args: tuple, kwargs: dict) -> GraphTensor:
+        input_ids, attrs = get_op_schema(op_type).normalize(self, args, dict(kwargs))
+        return self.graph.add_op(op_type, input_ids, attrs)
+
+    def add_binary_op(self, op_type: str, left: Any, right: Any, reverse: bool = False) -> GraphTensor:
+        attrs: dict = {}
+        if reverse and self.is_tensor_like(right):
+            ids = [self.as_value(right, "other"), self.as_value(left, "input")]
+        else:
+            ids = [self.as_value(left, "input")]
+            if self.is_tensor_like(right):
+                ids.append(self.as_value(right, "other"))
+            else:
+                attrs["other"] = right
+                attrs["reverse"] = reverse
+        return self.graph.add_op(op_type, ids, attrs)
+
+    def finalize(self, outputs: Any) -> tuple:
+        flat, structure = _flatten_outputs(outputs)
+        self.graph.mark_outputs(flat)
+        self.graph.lint()
+        return self.graph, structure
+
+
+def _flatten_outputs(outputs: Any) -> tuple:
+    flat: list = []
+
+    def visit(value: Any) -> Any:
+        if isinstance(value, GraphTensor):
+            flat.append(value.value_id)
+            return ("leaf",)
+        if isinstance(value, (tuple, list)):
+            return ("tuple" if isinstance(value, tuple) else "list", [visit(v) for v in value])
+        if isinstance(value, dict):
+            return ("dict", [(k, visit(v)) for k, v in value.items()])
+        raise TypeError(f"graph functions must return GraphTensor values, got {type(value)!r}")
+
+    return flat, visit(outputs)
+
+
+def _rebuild_outputs(structure: Any, flat: list) -> Any:
+    it = iter(flat)
+
+    def build(node: Any) -> Any:
+        kind = node[0]
+        if kind == "leaf":
+            return next(it)
+        if kind == "tuple":
+            return tuple(build(c) for c in node[1])
+        if kind == "list":
+            return [build(c) for c in node[1]]
+        return {k: build(c) for k, c in node[1]}
+
+    return build(structure)
+
+
+class GraphFunction:
+    def __init__(self, fn: Callable, **options: Any) -> None:
+        self.fn = fn
+        self.options = dict(options)
+        functools.update_wrapper(self, fn)
+
+    def __call__(self, *args: Any, **kwargs: Any) -> Any:
+        return self.fn(*args, **kwargs)
+
+
+def graph(fn: Optional[Callable] = None, **options: Any):
+    """Decorator marking a function for ``compile`` (src/flag_dnn/graph/capture.py:121)."""
+    if fn is None:
+        return lambda inner: GraphFunction(inner, **options)
+    return GraphFunction(fn, **options)
+
+
+# ------------------------------------------------------------------ planning
+@dataclass
+class ExecutionStep:
+    op_type: str
+    inputs: list
+    outputs: list
+    attrs: dict = field(default_factory=dict)
+    backend: str = "sm100"
+    kernel_name: Optional[str] = None
+    workspace: int = 0
+
+
+@dataclass
+class MemoryPlan:
+    workspace_size: int = 0
+    buffers: dict = field(default_factory=dict)
+
+    def to_dict(self) -> dict:
+        return {"workspace_size": self.workspace_size, "buffers": dict(self.buffers)}
+
+
+@dataclass
+class ExecutionPlan:
+    graph_hash: str
+    plan_id: str
+    graph: Graph
+    steps: list
+    input_specs: list
+    output_specs: list
+    workspace_size: int = 0
+    memory_plan: Optional[MemoryPlan] = None
+    tuned: bool = False
+    debug_info: dict = field(default_factory=dict)
+
+    def run(self, *inputs: Any) -> Any:
+        return execute_plan(self, inputs)
+
+
+def _candidates_for(node, graph: Graph) -> list:
+    """Kernel candidates of a node, best first (cf. backend.py:109-151 of the reference)."""
+    if node.op_type == "fused_conv2d_bias_relu":
+        return [
+            {"name": "fused_conv2d_bias_relu.sm100_igemm", "backend": "sm100", "op_type": node.op_type,
+             "implementation": "sm100_fused", "priority": 0,
+             "configs": [{"tile_m": 128, "tile_k_bytes": 128, "accumulators": 2}]},
+            {"name": "fused_conv2d_bias_relu.sm100_direct", "backend": "sm100", "op_type": node.op_type,
+             "implementation": "sm100_direct", "priority": 50, "configs": []},
+        ]
+    if node.op_type == "conv2d":
+        return [{"name": "conv2d.sm100", "backend": "sm100", "op_type": node.op_type,
+                 "implementation": "sm100", "priority": 0, "configs": []}]
+    return [{"name": node.op_type, "backend": "torch", "op_type": node.op_type,
+             "implementation": "default", "priority": 100, "configs": []}]
+
+
+def _build_plan(graph_obj: Graph, specs: list, output_structure: Any, options: dict) -> ExecutionPlan:
+    steps, chosen, total_candidates = [], [], 1
+    for node in graph_obj.topological_nodes():
+        cands = _candidates_for(node, graph_obj)
+        total_candidates *= len(cands)
+        best = cands[0]
+        attrs = dict(node.attrs)
+        attrs["_implementation"] = best["implementation"]
+        attrs["_kernel_candidate"] = best["name"]
+        if best["configs"]:
+            attrs["_kernel_config"] = dict(best["configs"][0])
+        steps.append(ExecutionStep(node.op_type, list(node.inputs), list(node.outputs), attrs,
+                                   backend=best["backend"], kernel_name=best["name"]))
+        chosen.append(best)
+    # Intermediate values: their sizes are reported, storage comes from torch's
+    # caching allocator at run time (the reference computes a workspace it never
+    # consumes, src/flag_dnn/graph/registry.py:1431-1434).
+    buffers = {}
+    for node in graph_obj.nodes:
+        for vid in node.outputs:
+            if vid not in graph_obj.outputs:
+                buffers[str(vid)] = graph_obj.values[vid].spec.nbytes()
+    memory_plan = MemoryPlan(workspace_size=sum(buffers.values()), buffers=buffers)
+    ghash = graph_obj.graph_hash()
+    autotune = bool(options.get("autotune", False)) or str(os.getenv("FLAGDNN_AUTOTUNE", "0")).lower() in ("1", "true", "yes")
+    debug = {
+        "backend": "sm100",
+        "requested_backend": str(options.get("backend", "auto")),
+        "cache_hit": False,
+        "output_structure": output_structure,
+        "num_steps": len(steps),
+        "fusion": dict(graph_obj.attrs.get("fusion", {})),
+        "kernel_candidates": chosen,
+        "candidate_count": min(total_candidates, int(options.get("max_plan_candidates", 8))),
+        "memory": memory_plan.to_dict(),
+        "selector": "static_priority",
+        # Tile selection happens inside the native library from the problem
+        # geometry (fdnn_conv2d_query); there is nothing to time at plan level.
+        "autotune": {"enabled": autotune, "results": [], "selected": chosen[0]["name"] if chosen else None},
+    }
+    return ExecutionPlan(
+        graph_hash=ghash,
+        plan_id=hashlib.sha256((ghash + json.dumps([c["name"] for c in chosen])).encode()).hexdigest()[:16],
+        graph=graph_obj, steps=steps, input_specs=specs,
+        output_specs=[graph_obj.values[v].spec for v in graph_obj.outputs],
+        workspace_size=memory_plan.workspace_size, memory_plan=memory_plan, tuned=False, debug_info=debug)
+
+
+class PlanCache:
+    """In-memory plan cache (the reference's also persists JSON; src/flag_dnn/graph/cache.py:62-130)."""
+
+    def __init__(self, enable_disk: bool = False, max_entries: int = 128):
+        self.enable_disk = False  # plans hold live graphs; only the memory layer is implemented
+        self.max_entries = max_entries
+        self._plans: dict = {}
+
+    def get(self, key: str) -> Optional[ExecutionPlan]:
+        return self._plans.get(key)
+
+    def put(self, key: str, plan: ExecutionPlan) -> None:
+        if len(self._plans) >= self.max_entries:
+            self._plans.pop(next(iter(self._plans)))
+        self._plans[key] = plan
+
+
+_DEFAULT_CACHE = PlanCache()
+
+
+def get_default_plan_cache() -> PlanCache:
+    return _DEFAULT_CACHE
+
+
+def _cache_key(graph_obj: Graph, specs: list, backend: str) -> str:
+    payload = {"graph": graph_obj.graph_hash(), "backend": backend,
+               "specs": [dict(s.signature(), name=s.name) for s in specs]}
+    return hashlib.sha256(json.dumps(payload, sort_keys=True, default=str).encode()).hexdigest()
+
+
+class CompiledGraph:
+    def __init__(self, plan: ExecutionPlan):
+        self.plan = plan
+        self.graph = plan.graph
+
+    def run(self, *inputs: Any) -> Any:
+        return self.plan.run(*inputs)
+
+    def __call__(self, *inputs: Any) -> Any:
+        return self.run(*inputs)
+
+
+def _fusion_enabled(options: dict) -> bool:
+    if str(os.getenv("FLAGDNN_GRAPH_FUSION", "1")).lower() in ("0", "false", "no"):
+        return False
+    return bool(options.get("fusion", True))
+
+
+def _dump_graph(graph_obj: Graph, stage: str) -> None:
+    if str(os.getenv("FLAGDNN_DUMP_GRAPH", "0")).lower() in ("0", "false", "no"):
+        return
+    dump_dir = os.getenv("FLAGDNN_DUMP_GRAPH_DIR", "/tmp/flagdnn_graphs")
+    try:
+        os.makedirs(dump_dir, exist_ok=True)
+        stem = os.path.join(dump_dir, f"{stage}_{graph_obj.graph_hash()[:12]}")
+        with open(stem + ".json", "w", encoding="utf-8") as fh:
+            json.dump(graph_obj.to_dict(), fh, indent=2, default=str)
+        with open(stem + ".txt", "w", encoding="utf-8") as fh:
+            fh.write(graph_obj.dump_text())
+    except OSError:
+        return
+
+
+def compile(fn: Callable, inputs: Optional[list] = None, input_specs: Optional[list] = None,
+            options: Optional[dict] = None) -> CompiledGraph:
+    """Capture ``fn`` on symbolic inputs, fuse, and plan it (src/flag_dnn/graph/capture.py:127)."""
+    opts: dict = {}
+    if isinstance(fn, GraphFunction):
+        opts.update(fn.options)
+        fn = fn.fn
+    if options:
+        opts.update(options)
+    values = input_specs if input_specs is not None else inputs
+    specs = []
+    for index, value in enumerate(values or []):
+        if isinstance(value, TensorSpec):
+            spec = value
+        elif isinstance(value, torch.Tensor):
+            spec = TensorSpec.from_tensor(value)
+        else:
+            raise TypeError(f"compile inputs must be TensorSpec or torch.Tensor values, got {type(value)!r}")
+        specs.append(spec if spec.name else spec.with_name(f"arg{index}"))
+    if not specs:
+        raise ValueError("compile requires input TensorSpec values or tensors")
+
+    with GraphCapture(specs) as ctx:
+        outputs = fn(*ctx.graph_inputs)
+    captured, structure = ctx.finalize(outputs)
+    _dump_graph(captured, "capture")
+    eliminate_dead_nodes(captured)
+    if _fusion_enabled(opts):
+        apply_fusion_pass(captured)
+        eliminate_dead_nodes(captured)
+    captured.lint()
+    _dump_graph(captured, "optimized")
+
+    cache = opts.get("cache", get_default_plan_cache())
+    key = _cache_key(captured, specs, str(opts.get("backend", "auto")))
+    plan = cache.get(key) if cache is not None else None
+    if plan is None:
+        plan = _build_plan(captured, specs, structure, opts)
+        if cache is not None:
+            cache.put(key, plan)
+    else:
+        plan.debug_info["cache_hit"] = True
+        plan.debug_info["cache_layer"] = "memory"
+        plan.debug_info["output_structure"] = structure
+    return CompiledGraph(plan)
+
+
+# ----------------------------------------------------------------- execution
+def _validate_input(spec: TensorSpec, tensor: Any, index: int) -> None:
+    """Shape, dtype, exact strides and device must match what was compiled
+    (src/flag_dnn/graph/executor.py:235-262)."""
+    if not isinstance(tensor, torch.Tensor):
+        raise TypeError(f"graph input {index} ({spec.name}) must be a tensor")
+    if tuple(tensor.shape) != tuple(spec.shape):
+        raise RuntimeError(f"graph input {index} ({spec.name}) shape {tuple(tensor.shape)} != compiled {spec.shape}")
+    if tensor.dtype != torch_dtype(spec.dtype):
+        raise RuntimeError(f"graph input {index} ({spec.name}) dtype {tensor.dtype} != compiled {spec.dtype}")
+    if spec.stride is not None and tuple(tensor.stride()) != tuple(spec.stride):
+        raise RuntimeError(f"graph input {index} ({spec.name}) stride {tuple(tensor.stride())} != compiled {spec.stride}")
+    if spec.device is not None and torch.device(spec.device).type != tensor.device.type:
+        raise RuntimeError(f"graph input {index} ({spec.name}) device {tensor.device} != compiled {spec.device}")
+
+
+def execute_plan(plan: ExecutionPlan, inputs: tuple) -> Any:
+    graph_obj = plan.graph
+    if len(inputs) != len(graph_obj.inputs):
+        raise RuntimeError(f"graph expects {len(graph_obj.inputs)} inputs, got {len(inputs)}")
+    for index, (spec, tensor) in enumerate(zip(plan.input_specs, inputs)):
+        _validate_input(spec, tensor, index)
+    if len(plan.steps) == 1:  # single fused node: skip the environment bookkeeping
+        step = plan.steps[0]
+        if all(v in graph_obj.inputs for v in step.inputs) and graph_obj.outputs == step.outputs:
+            args = [inputs[graph_obj.inputs.index(v)] for v in step.inputs]
+            out = get_op_schema(step.op_type).run(args, step.attrs)
+            return _rebuild_outputs(plan.debug_info.get("output_structure") or ("leaf",), [out])
+    env: dict = dict(zip(graph_obj.inputs, inputs))
+    for value in graph_obj.values.values():
+        if value.is_constant:
+            env[value.id] = value.const_value
+    for step in plan.steps:
+        result = get_op_schema(step.op_type).run([env[v] for v in step.inputs], step.attrs)
+        env[step.outputs[0]] = result
+    flat = [env[v] for v in graph_obj.outputs]
+    return _rebuild_outputs(plan.debug_info.get("output_structure") or ("leaf",), flat)

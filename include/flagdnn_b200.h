@@ -1,0 +1,154 @@
+/*
+ * flagdnn_b200 — C ABI of the B200 (sm_100a) convolution forward path.
+ *
+ * This is the boundary a FlagDNN maintainer binds to replace the Triton
+ * launches of the conv2d hot path.  Plain pointers and sizes only: no torch,
+ * no C++ types.  Every entry point returns an fdnn_status code; nothing
+ * aborts, traps or throws.  All device pointers are caller-owned; the library
+ * allocates no device memory (fdnn_conv2d_query tells the caller how much
+ * workspace and packed-filter storage to provide).
+ *
+ * Tensor conventions follow the reference: logical shapes are always
+ * x[N,C,H,W], w[K,C/groups,R,S], bias[K], y[N,K,OH,OW]; the physical layout
+ * (NCHW, NHWC/channels_last, or any strided view) is carried by element
+ * strides in that logical order, as torch reports them.
+ */
+#ifndef FLAGDNN_B200_H_
+#define FLAGDNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FDNN_ABI_VERSION 1
+
+/* Status codes.  The Python shim maps BAD_PARAM / CUDA_ERROR / DEVICE_TIMEOUT /
+ * WORKSPACE_TOO_SMALL to RuntimeError and NOT_SUPPORTED / ARCH_MISMATCH to
+ * NotImplementedError, the two exception types the reference raises
+ * (src/flag_dnn/ops/conv2d.py:99-135, 3592-3595;
+ *  src/flag_dnn/graph/kernels/fused_conv.py:73-90). */
+typedef enum fdnn_status {
+  FDNN_OK = 0,
+  FDNN_BAD_PARAM = 1,
+  FDNN_NOT_SUPPORTED = 2,
+  FDNN_ARCH_MISMATCH = 3,
+  FDNN_WORKSPACE_TOO_SMALL = 4,
+  FDNN_CUDA_ERROR = 5,
+  FDNN_DEVICE_TIMEOUT = 6
+} fdnn_status;
+
+/* dtype ids, same numbering as _dtype_id in src/flag_dnn/ops/conv2d.py:138-147 */
+#define FDNN_F16 0
+#define FDNN_BF16 1
+#define FDNN_F32 2
+#define FDNN_F64 3
+
+/* algorithm selector */
+#define FDNN_ALGO_AUTO 0
+#define FDNN_ALGO_DIRECT 1 /* CUDA-core direct convolution (any dtype, groups) */
+#define FDNN_ALGO_IGEMM 2  /* tcgen05 implicit GEMM (f16/bf16, f32 via 3xTF32) */
+
+/* epilogue activation */
+#define FDNN_ACT_NONE 0
+#define FDNN_ACT_RELU 1
+
+/* Problem descriptor.  Replaces the argument list the reference passes to its
+ * Triton launches (src/flag_dnn/graph/kernels/fused_conv.py:151-191,
+ * src/flag_dnn/ops/conv2d.py:3826-3865). */
+typedef struct fdnn_conv_desc {
+  int32_t dtype;                /* FDNN_F16 .. FDNN_F64; x, w, bias, scale, y share it */
+  int32_t n, c, h, w;           /* input  x[N,C,H,W] */
+  int32_t k, r, s;              /* filter w[K,C/groups,R,S] */
+  int32_t stride_h, stride_w;
+  int32_t pad_top, pad_bottom, pad_left, pad_right;
+  int32_t dil_h, dil_w;
+  int32_t groups;
+  int32_t algo;                 /* FDNN_ALGO_* */
+  int64_t x_strides[4];         /* element strides of x in (n,c,h,w) order */
+  int64_t w_strides[4];         /* element strides of w in (k,c,r,s) order */
+  int64_t y_strides[4];         /* element strides of y in (n,k,oh,ow) order */
+} fdnn_conv_desc;
+
+/* What fdnn_conv2d_query decides for a descriptor. */
+typedef struct fdnn_conv_plan {
+  int32_t algo;                 /* FDNN_ALGO_DIRECT or FDNN_ALGO_IGEMM */
+  int32_t oh, ow;               /* output size, rule of src/flag_dnn/ops/conv2d.py:52-62 */
+  int32_t tile_m, tile_n, tile_k, stages; /* igemm tile; 0 for direct */
+  int32_t x_repacked;           /* 1: x is first rewritten into the workspace as NHWC, C padded */
+  int32_t w_packed;             /* 1: fwd needs a packed filter from fdnn_conv2d_pack_weight */
+  int32_t c_padded;             /* channel count the igemm kernel iterates over */
+  int32_t grid, block;          /* launch shape of the main kernel */
+  int32_t launches;             /* kernels one fwd call launches (main + repack) */
+  int64_t workspace_bytes;      /* scratch fwd needs (0 when x is consumed in place) */
+  int64_t packed_weight_bytes;  /* size of the packed filter (0 when w is consumed in place) */
+  int64_t smem_bytes;           /* dynamic shared memory of the main kernel */
+  double flops;                 /* 2*N*OH*OW*K*(C/groups)*R*S, benchmark/test_conv2d_perf.py:139-148 */
+  double bytes;                 /* x + w + bias + y once each, benchmark/base.py:661-668 */
+} fdnn_conv_plan;
+
+/* Library/ABI version (FDNN_ABI_VERSION of the built library). */
+int fdnn_abi_version(void);
+
+/* Human-readable text for a status code; never NULL. */
+const char* fdnn_status_string(int status);
+
+/* Detail text of the last non-OK status returned on the calling thread. */
+const char* fdnn_last_error(void);
+
+/* Validates `desc` (same rules and order as _check_conv2d_inputs,
+ * src/flag_dnn/ops/conv2d.py:90-135) and fills `plan`.  Needs no GPU except to
+ * read the current device's SM count for the grid size (148 assumed if no
+ * device is visible).  `x`, `w`, `y` may be NULL; when given, their alignment
+ * decides whether the tensors can be consumed in place by TMA. */
+int fdnn_conv2d_query(const fdnn_conv_desc* desc, const void* x, const void* w,
+                      const void* y, fdnn_conv_plan* plan);
+
+/* One-time filter relayout, the counterpart of the reference's packers
+ * (src/flag_dnn/ops/conv2d.py:193-276): w[K,C/g,R,S] (any strides) ->
+ * [K,R,S,Cpad] with zero padding; for f32 a second copy holds the low TF32
+ * halves.  `packed` must hold plan.packed_weight_bytes.  Asynchronous on
+ * `stream` (a cudaStream_t passed as void*). */
+int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w,
+                            void* packed, int64_t packed_bytes, void* stream);
+
+/* y = act( conv(x, w) * scale[k] + bias[k] ), fp32 accumulate, one rounding to
+ * the output dtype.  Replaces conv2d()'s Triton launches
+ * (src/flag_dnn/ops/conv2d.py:3575-4449) and fused_conv2d_bias_relu()
+ * (src/flag_dnn/graph/kernels/fused_conv.py:62-193).
+ *   w_packed : from fdnn_conv2d_pack_weight when plan.w_packed, else NULL
+ *   bias     : [K] or NULL;  scale : [K] or NULL (BN-folded per-channel scale)
+ *   workspace: >= plan.workspace_bytes, 256-byte aligned (may be NULL if 0)
+ * Asynchronous on `stream`; performs no allocation and no host sync, so it
+ * can be captured into a CUDA graph.  The device current at the call must be
+ * the one that owns the pointers. */
+int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w,
+                    const void* w_packed, const void* bias, const void* scale,
+                    int activation, void* y, void* workspace,
+                    int64_t workspace_bytes, void* stream);
+
+/* Host-buffer convenience: same as fdnn_conv2d_fwd but x, w, bias, scale and y
+ * are HOST pointers (dense, described by the strides in `desc`); copies in,
+ * runs and copies y back on `stream`, using the caller-provided device arena
+ * `dev_arena` of `arena_bytes` (see fdnn_conv2d_host_arena_bytes).
+ * Synchronises `stream` before returning. */
+int fdnn_conv2d_fwd_host(const fdnn_conv_desc* desc, const void* x_host,
+                         const void* w_host, const void* bias_host,
+                         const void* scale_host, int activation, void* y_host,
+                         void* dev_arena, int64_t arena_bytes, void* stream);
+
+/* Device bytes fdnn_conv2d_fwd_host needs for `desc`. */
+int fdnn_conv2d_host_arena_bytes(const fdnn_conv_desc* desc, int64_t* bytes);
+
+/* Every wait inside the kernels is bounded; a wait that runs out records a
+ * code in a per-device status word and the kernel returns early.  This call
+ * synchronises the current device, returns the word in *word (0 = no
+ * incident) and clears it.  Returns FDNN_DEVICE_TIMEOUT if it was non-zero. */
+int fdnn_device_status(uint32_t* word);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAGDNN_B200_H_ */

@@ -1,0 +1,386 @@
+"""Benchmark of the fused conv2d hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3]
+
+A step is one pass of the fused conv -> bias -> ReLU graph over one batch of
+synthetic input.  The default workload is the 3x3 256-channel layer the
+headline target is quoted on; --workload picks the 1x1, stem or fp32 layers.
+With N > 1 (launched under torchrun, one rank per GPU) every rank runs the
+same batch-sized problem on its own GPU — the path shards along the batch with
+replicated filters and needs no collective — so the scaling is weak.
+
+One JSON line is printed by rank 0:
+  value     device-resident throughput (TFLOP/s over all ranks): inputs already
+            in HBM, steps replayed from a CUDA graph, operands rotated through
+            more buffers than L2 holds so every step reads from DRAM;
+  e2e       the same metric through the public API from pinned HOST buffers,
+            host->device and device->host copies inside the timed region;
+  roofline  the implicit-GEMM kernel against the measured tensor (or HBM) peak;
+  cpu_baseline  the reference's CPU path (torch.nn.functional.conv2d + relu,
+            what src/flag_dnn/graph/registry.py:1357-1365,1426 runs on CPU
+            tensors) on a bounded sample, all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# name: (N, C, H, K, R, stride, pad, dtype, layout, x distribution, roofline bound)
+WORKLOADS = {
+    "c3": dict(desc="3x3 conv+bias+ReLU bf16 NHWC N=256 C=K=256 H=W=14 s1 p1", n=256, c=256, hw=14, k=256, r=3,
+               stride=1, pad=1, dtype="bfloat16", layout="nhwc", dist="normal", bound="tensor"),
+    "c2": dict(desc="1x1 conv+bias+ReLU bf16 NHWC N=256 C=256 H=W=56 K=64", n=256, c=256, hw=56, k=64, r=1,
+               stride=1, pad=0, dtype="bfloat16", layout="nhwc", dist="normal", bound="hbm"),
+    "c4": dict(desc="7x7 s2 stem conv+bias+ReLU bf16 NHWC N=256 C=3 H=W=224 K=64", n=256, c=3, hw=224, k=64, r=7,
+               stride=2, pad=3, dtype="bfloat16", layout="nhwc", dist="uniform", bound="hbm"),
+    "c1": dict(desc="3x3 conv+bias fp32 NCHW N=4 C=64 H=W=56 K=64 s1 p1 (split TF32)", n=4, c=64, hw=56, k=64, r=3,
+               stride=1, pad=1, dtype="float32", layout="nchw", dist="normal", bound="tensor"),
+}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the implicit-GEMM
+# kernel, from the ncu captures summarised under profiles/ (None = not captured).
+NCU_TRAFFIC_BYTES = {"c3": None, "c2": None, "c4": None, "c1": None}
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            data = json.load(fh)
+        return {k: float(data[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+def out_dim(size, pad, r, stride):
+    return (size + 2 * pad - (r - 1) - 1) // stride + 1
+
+
+def workload_numbers(wl):
+    oh = out_dim(wl["hw"], wl["pad"], wl["r"], wl["stride"])
+    es = 2 if wl["dtype"] != "float32" else 4
+    flops = 2.0 * wl["n"] * oh * oh * wl["k"] * wl["c"] * wl["r"] * wl["r"]
+    x_bytes = wl["n"] * wl["c"] * wl["hw"] * wl["hw"] * es
+    w_bytes = wl["k"] * wl["c"] * wl["r"] * wl["r"] * es
+    y_bytes = wl["n"] * wl["k"] * oh * oh * es
+    return dict(oh=oh, flops=flops, x_bytes=x_bytes, w_bytes=w_bytes, y_bytes=y_bytes,
+                bytes=x_bytes + w_bytes + y_bytes + wl["k"] * es)
+
+
+def make_inputs(wl, n, seed, device, torch):
+    """Seeded synthetic tensors with the configuration's shapes and distributions."""
+    dtype = getattr(torch, wl["dtype"])
+    g = torch.Generator(device=device).manual_seed(seed)
+    shape = (n, wl["c"], wl["hw"], wl["hw"])
+    if wl["dist"] == "uniform":
+        x = torch.rand(shape, generator=g, device=device) * 2 - 1
+    else:
+        x = torch.randn(shape, generator=g, device=device)
+    fan_in = wl["c"] * wl["r"] * wl["r"]
+    w = torch.randn((wl["k"], wl["c"], wl["r"], wl["r"]), generator=g, device=device) * fan_in ** -0.5
+    b = torch.randn((wl["k"],), generator=g, device=device) * 0.1
+    x, w, b = x.to(dtype), w.to(dtype), b.to(dtype)
+    if wl["layout"] == "nhwc":
+        x = x.contiguous(memory_format=torch.channels_last)
+        w = w.contiguous(memory_format=torch.channels_last)
+    return x, w, b
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        nv = self._nvml
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=1.0)
+        return False
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_baseline_leg(wl, torch, sample_n, min_seconds=2.0):
+    """The reference's CPU path timed on the host cores; test-infrastructure code (oracle/) as the checker's timer."""
+    import oracle
+
+    x, w, b = make_inputs(wl, sample_n, 0, "cpu", torch)
+    relu = wl["dtype"] != "float32"
+    cdt = getattr(torch, wl["dtype"])  # the reference runs F.conv2d in the tensors' own dtype
+    oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
+    times, t_all = [], time.perf_counter()
+    while len(times) < 3 or (time.perf_counter() - t_all < min_seconds and len(times) < 200):
+        t0 = time.perf_counter()
+        oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    nums = workload_numbers(dict(wl, n=sample_n))
+    return dict(value=nums["flops"] / med / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+                sample=f"{sample_n} of {wl['n']} images, {len(times)} repeats, median; torch.nn.functional.conv2d+relu "
+                       f"in {wl['dtype']} on CPU (the call the reference's CPU graph path makes)",
+                ms_per_sample=med * 1e3)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    wl = WORKLOADS[args.workload]
+    sample_n = min(wl["n"], 32)
+    nums = workload_numbers(dict(wl, n=sample_n))
+    import oracle
+
+    x, w, b = make_inputs(wl, sample_n, 0, "cpu", torch)
+    relu = wl["dtype"] != "float32"
+    cdt = getattr(torch, wl["dtype"])
+    for _ in range(max(args.warmup, 1)):
+        oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
+    steps = max(1, min(args.steps, 50))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
+    dt = (time.perf_counter() - t0) / steps
+    value = nums["flops"] / dt / 1e12
+    sample = (f"each step = {sample_n} of {wl['n']} images through torch.nn.functional.conv2d+relu in {wl['dtype']} "
+              f"on the host CPU (the reference's CPU graph path); {steps} steps timed")
+    line = {
+        "impl": "reference", "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+        "config": {"workload": args.workload, "description": wl["desc"], "sample_images": sample_n},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+
+    import flagdnn_b200 as fd
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for this library)")
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    device = torch.device("cuda", local_rank)
+    wl = WORKLOADS[args.workload]
+    nums = workload_numbers(wl)
+    peaks, peak_src = load_peaks()
+    relu = wl["dtype"] != "float32"
+
+    # ---- operands: enough rotating (x, y) sets that a set is evicted from L2 before it is reused
+    l2_bytes = 126 * 1024 * 1024
+    per_set = nums["x_bytes"] + nums["y_bytes"]
+    n_sets = max(2, min(16, -(-3 * l2_bytes // per_set)))
+    xs = []
+    w = b = None
+    for i in range(n_sets):
+        x, w_i, b_i = make_inputs(wl, wl["n"], 100 * rank + i, device, torch)
+        xs.append(x)
+        if w is None:
+            w, b = w_i, b_i
+
+    @fd.graph
+    def layer(x, weight, bias):
+        y = fd.conv2d(x, weight, stride=wl["stride"], padding=wl["pad"])
+        y = fd.bias_add(y, bias)
+        return fd.relu(y) if relu else y
+
+    compiled = fd.compile(layer, inputs=[xs[0], w, b], options={"cache": None})
+    node_types = [n.op_type for n in compiled.graph.nodes]
+    plan = fd.conv2d_plan(xs[0], w, stride=wl["stride"], padding=wl["pad"])
+    launches_per_step = plan["launches"]
+
+    # warm-up through the eager API (also packs the filter and sets kernel attributes)
+    for i in range(max(args.warmup, 3)):
+        compiled.run(xs[i % n_sets], w, b)
+    torch.cuda.synchronize()
+
+    # ---- device-resident leg: one CUDA graph holding one step per operand set
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    outs = []
+    with torch.cuda.stream(stream):
+        for i in range(n_sets):
+            compiled.run(xs[i], w, b)
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(n_sets):
+                outs.append(compiled.run(xs[i], w, b))
+    replays = max(1, -(-args.steps // n_sets))
+    steps = replays * n_sets
+    warm_replays = max(1, -(-max(args.warmup, 3) // n_sets))
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        for _ in range(warm_replays):
+            graph.replay()
+        stream.synchronize()
+        barrier()
+        with ClockSampler(local_rank) as clocks:
+            e0.record(stream)
+            for _ in range(replays):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / steps
+    value = world * nums["flops"] / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end-to-end leg: pinned host buffers -> device -> fused op -> host, copies inside the timed region
+    x_host = xs[0].cpu().pin_memory()
+    y_host = torch.empty_like(outs[0], device="cpu").pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+    x_dev = torch.empty_like(xs[0])
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        y = compiled.run(x_dev, w, b)
+        y_host.copy_(y, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * nums["flops"] / (e2e_ms / e2e_steps * 1e-3) / 1e12
+
+    status_word = fd.device_status()
+
+    if rank == 0:
+        # ---- roofline of the dominant kernel (the implicit-GEMM kernel; one launch per step)
+        if wl["bound"] == "tensor":
+            achieved = nums["flops"] / (ms_per_step * 1e-3) / 1e12
+            peak, unit = peaks["bf16_tflops"], "TFLOP/s"
+            extra = {"frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"]}
+        else:
+            achieved = nums["bytes"] / (ms_per_step * 1e-3) / 1e9
+            peak, unit = peaks["hbm_gbs"], "GB/s"
+            extra = {}
+        roofline = {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                    "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peak_src}",
+                    "kernel": "conv_igemm_kernel", "algorithmic_flops_per_launch": nums["flops"],
+                    "algorithmic_bytes_per_launch": nums["bytes"], **extra}
+        cpu = cpu_baseline_leg(wl, torch, sample_n=min(wl["n"], 32))
+        line = {
+            "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": warm_replays * n_sets, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+            "config": {"workload": args.workload, "description": wl["desc"], "graph_nodes": node_types,
+                       "launch": "cuda_graph_replay", "l2": f"{n_sets} rotating (x, y) sets = "
+                       f"{n_sets * per_set / 2**20:.0f} MiB > 126 MiB L2; filter and bias shared",
+                       "per_gpu_batch": wl["n"], "parallelism": f"batch-sharded replicas x{world}, no collective",
+                       "tile": [plan["tile_m"], plan["tile_n"], plan["tile_k"]], "stages": plan["stages"],
+                       "grid": plan["grid"]},
+            "pct_of_bf16_peak": 100.0 * (value / world) / peaks["bf16_tflops"],
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": nums["x_bytes"],
+                    "d2h_bytes_per_step": nums["y_bytes"], "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": steps * launches_per_step,
+            "clocks": clocks.summary(), "device_status_word": status_word,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

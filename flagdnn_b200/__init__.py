@@ -17,7 +17,7 @@ from typing import Optional
 import torch
 
 from . import ops  # noqa: F401
-from .conv2d import (  # noqa: F401
+from .conv_host import (  # noqa: F401
     conv2d_bias_act,
     conv2d_plan,
     device_status,
@@ -42,7 +42,7 @@ _ATEN_LIB: Optional[torch.library.Library] = None
 
 
 def _aten_conv2d(input, weight, bias=None, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1):
-    from . import conv2d as native
+    from . import conv_host as native
 
     return native.conv2d(input, weight, bias, tuple(stride), tuple(padding), tuple(dilation), groups)
 

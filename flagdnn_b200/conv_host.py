@@ -229,8 +229,8 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
             None if bias is None else bias.data_ptr(),
             None if scale is None else scale.data_ptr(),
             activation, out.data_ptr(), ws_ptr, plan.workspace_bytes, stream))
-        if ws is not None:
-            ws.record_stream(torch.cuda.current_stream())
+        # `ws` goes back to torch's caching allocator when this frame ends; the
+        # allocator orders reuse on the stream the kernels were queued on.
     return out
 
 

@@ -81,11 +81,6 @@ bool aligned16(const void* p) { return p == nullptr || (reinterpret_cast<uintptr
 
 int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
-struct Decision {
-  fdnn_conv_plan plan;
-  bool igemm_possible;
-};
-
 // Can the tensor-core path express this geometry?  Limits are those of the
 // im2col tensor map: box corners in [-128, 127], tap offsets <= 255,
 // traversal strides <= 8.
@@ -156,14 +151,18 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
 
   const int gran = 16 / es;  // channels per 16 bytes
   const bool is16 = es == 2;
+  // A stride over an extent of one carries no information (torch reports
+  // arbitrary values there), so only strides of real extents are constrained.
+  auto stride_ok = [gran](long long extent, long long stride) { return extent <= 1 || stride % gran == 0; };
   // x in place: channel-contiguous, every other stride a multiple of 16 bytes
-  const bool x_inplace = is16 && d->x_strides[1] == 1 && d->x_strides[0] % gran == 0 &&
-                         d->x_strides[2] % gran == 0 && d->x_strides[3] % gran == 0 &&
-                         d->x_strides[3] >= d->c && aligned16(x);
+  const bool x_inplace = is16 && (d->c == 1 || d->x_strides[1] == 1) && stride_ok(d->n, d->x_strides[0]) &&
+                         stride_ok(d->h, d->x_strides[2]) && stride_ok(d->w, d->x_strides[3]) &&
+                         (d->w <= 1 || d->x_strides[3] >= d->c) && aligned16(x);
   // w in place: [K, R, S, C]-like memory, taps evenly spaced
-  const bool w_inplace = is16 && d->w_strides[1] == 1 && d->w_strides[3] % gran == 0 &&
-                         d->w_strides[3] >= d->c && d->w_strides[0] % gran == 0 &&
-                         (d->r == 1 || d->w_strides[2] == (long long)d->s * d->w_strides[3]) &&
+  const bool w_inplace = is16 && (d->c == 1 || d->w_strides[1] == 1) && stride_ok(d->k, d->w_strides[0]) &&
+                         stride_ok(d->s, d->w_strides[3]) && (d->s <= 1 || d->w_strides[3] >= d->c) &&
+                         (d->r <= 1 || (d->s > 1 ? d->w_strides[2] == (long long)d->s * d->w_strides[3]
+                                                 : d->w_strides[2] % gran == 0)) &&
                          aligned16(w);
   const int c_pad = round_up(d->c, gran);
   plan->c_padded = c_pad;
@@ -276,6 +275,7 @@ __device__ uint32_t g_status_word;
 
 std::once_flag g_prepare_once[64];
 cudaError_t g_prepare_result[64];
+uint32_t* g_status_ptr[64];  // device address of g_status_word, looked up once per device
 
 }  // namespace
 
@@ -382,6 +382,7 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
     int major = 0;
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     g_prepare_result[dev] = (major == 10) ? igemm_prepare_device() : cudaErrorNoKernelImageForDevice;
+    g_status_ptr[dev] = device_status_word();
   });
   if (g_prepare_result[dev] == cudaErrorNoKernelImageForDevice)
     return fail(FDNN_ARCH_MISMATCH, "the implicit-GEMM kernels are built for sm_100a only");
@@ -403,7 +404,11 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   const int es = elem_size(d.dtype);
   const int c_pad = plan.c_padded;
   const void* a_base = x;
-  long long a_sw = d.x_strides[3], a_sh = d.x_strides[2], a_sn = d.x_strides[0];
+  // Extent-one dimensions get a harmless aligned stride (theirs may be anything).
+  const long long any_stride = c_pad;
+  long long a_sw = d.w > 1 ? d.x_strides[3] : any_stride;
+  long long a_sh = d.h > 1 ? d.x_strides[2] : any_stride;
+  long long a_sn = d.n > 1 ? d.x_strides[0] : any_stride;
   int a_c = d.c;
   long long a_plane = 0;
   if (plan.x_repacked) {
@@ -418,7 +423,8 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
     a_c = c_pad;
   }
   const void* b_base = w;
-  long long b_stap = d.w_strides[3], b_sk = d.w_strides[0];
+  long long b_stap = d.s > 1 ? d.w_strides[3] : (d.r > 1 ? d.w_strides[2] : any_stride);
+  long long b_sk = d.k > 1 ? d.w_strides[0] : any_stride;
   int b_c = d.c;
   long long b_plane = 0;
   if (plan.w_packed) {
@@ -464,7 +470,7 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
                  d.y_strides[3] % gran == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0)
                     ? 1
                     : 0;
-  p.status = device_status_word();
+  p.status = g_status_ptr[dev];
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
   e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, p, plan.grid, stream);
   if (e != cudaSuccess) return fail_cuda("igemm launch", e);

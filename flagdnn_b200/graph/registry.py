@@ -121,12 +121,12 @@ def _require_device(inputs: list, what: str) -> None:
 
 
 def _run_conv2d(inputs: list, attrs: dict) -> torch.Tensor:
-    from .. import conv2d as native
+    from .. import conv_host as native
 
     _require_device(inputs, "conv2d")
     a = _public(attrs)
     bias = inputs[2] if len(inputs) > 2 else None
-    scale = inputs[3] if len(inputs) > 3 else None
+    scale = inputs[3].reshape(-1) if len(inputs) > 3 else None
     if scale is None:
         return native.conv2d(inputs[0], inputs[1], bias, a.get("stride", 1), a.get("padding", 0),
                              a.get("dilation", 1), a.get("groups", 1))
@@ -136,11 +136,11 @@ def _run_conv2d(inputs: list, attrs: dict) -> torch.Tensor:
 
 
 def _run_fused_conv2d_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
-    from .. import conv2d as native
+    from .. import conv_host as native
 
     _require_device(inputs, "fused_conv2d_bias_relu")
     a = _public(attrs)
-    scale = inputs[3] if len(inputs) > 3 else None
+    scale = inputs[3].reshape(-1) if len(inputs) > 3 else None  # (K,), (K,1,1) or (1,K,1,1)
     kw = dict(stride=a.get("stride", 1), padding=a.get("padding", 0), dilation=a.get("dilation", 1))
     try:
         return native.fused_conv2d_bias_relu(inputs[0], inputs[1], inputs[2], groups=a.get("groups", 1),

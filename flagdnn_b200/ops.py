@@ -11,7 +11,7 @@ from typing import Any
 
 import torch
 
-from . import conv2d as _conv
+from . import conv_host as _conv
 from .graph.compiler import current_capture
 
 

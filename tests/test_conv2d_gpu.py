@@ -1,0 +1,301 @@
+"""Parity of the CUDA path with the oracle, through the public API (which
+calls the C ABI).  Modelled on the reference's own tests: eager conv2d against
+an upcast torch result (tests/test_conv2d.py:56-116) and the compiled
+conv -> bias -> ReLU graph against a second implementation
+(tests_graph/test_graph_conv_bias_relu.py:113-145), here the CPU oracle."""
+import pytest
+import torch
+
+import oracle
+from cases import EAGER_CASES, FUSED_CASES, TOL
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16,
+          "float64": torch.float64}
+
+
+@pytest.fixture(scope="module")
+def fd(native_lib):
+    import flagdnn_b200
+
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    yield flagdnn_b200
+    flagdnn_b200.set_algo("auto")
+    assert flagdnn_b200.device_status() == 0, "a kernel recorded a bounded-wait incident"
+
+
+def _to_dev(t, dtype, channels_last):
+    if t is None:
+        return None
+    t = t.to(dtype).cuda()
+    if channels_last and t.dim() == 4:
+        t = t.contiguous(memory_format=torch.channels_last)
+    return t
+
+
+def _check(out, ref, dtype_name):
+    assert out.shape == ref.shape
+    torch.testing.assert_close(out.detach().float().cpu() if dtype_name != "float64" else out.cpu(),
+                               ref.float() if dtype_name != "float64" else ref, **TOL[dtype_name])
+
+
+@pytest.mark.parametrize("algo", ["igemm", "direct"])
+@pytest.mark.parametrize("channels_last", [True, False])
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16", "float16"])
+@pytest.mark.parametrize("idx", range(len(FUSED_CASES)))
+def test_fused_graph_matches_oracle(fd, golden, idx, dtype_name, channels_last, algo):
+    ishape, wshape, stride, padding, dilation = FUSED_CASES[idx]
+    key = f"fused_{idx:02d}"
+    dtype = DTYPES[dtype_name]
+    x, w, b = (torch.from_numpy(golden[key + s]) for s in ("_x", "_w", "_b"))
+    xd, wd, bd = _to_dev(x, dtype, channels_last), _to_dev(w, dtype, channels_last), _to_dev(b, dtype, False)
+
+    @fd.graph
+    def fn(x, weight, bias):
+        y = fd.conv2d(x, weight, stride=stride, padding=padding, dilation=dilation, groups=1)
+        return fd.relu(fd.bias_add(y, bias))
+
+    compiled = fd.compile(fn, inputs=[fd.TensorSpec.from_tensor(xd, "x"), fd.TensorSpec.from_tensor(wd, "weight"),
+                                      fd.TensorSpec.from_tensor(bd, "bias")], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["fused_conv2d_bias_relu"]
+    assert compiled.plan.debug_info["fusion"]["conv2d_bias_activation_fused"] == 1
+    fd.set_algo(algo)
+    try:
+        out = compiled.run(xd.clone(), wd.clone(), bd.clone())
+    finally:
+        fd.set_algo("auto")
+    assert out.dtype == dtype
+    assert out.is_contiguous(memory_format=torch.channels_last) == (xd.stride(1) == 1) or out.shape[1] == 1
+    # oracle on the very bits the GPU saw
+    ref = oracle.conv2d_torch_cpu(xd, wd, bd, stride, padding, dilation, 1, relu=True)
+    _check(out, ref, dtype_name)
+    if dtype_name == "float32":  # the stored output of the reference itself
+        _check(out, torch.from_numpy(golden[key + "_y"]), dtype_name)
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16", "float16", "float64"])
+@pytest.mark.parametrize("idx", range(len(EAGER_CASES)))
+def test_eager_conv2d_matches_oracle(fd, golden, idx, dtype_name):
+    ishape, wshape, has_bias, stride, padding, dilation, groups = EAGER_CASES[idx]
+    key = f"eager_{idx:02d}"
+    dtype = DTYPES[dtype_name]
+    x, w = torch.from_numpy(golden[key + "_x"]), torch.from_numpy(golden[key + "_w"])
+    b = torch.from_numpy(golden[key + "_b"]) if has_bias else None
+    xd, wd, bd = _to_dev(x, dtype, False), _to_dev(w, dtype, False), _to_dev(b, dtype, False)
+    for algo in ("auto", "igemm", "direct"):
+        if algo == "igemm" and (groups != 1 or dtype_name == "float64"):
+            continue
+        fd.set_algo(algo)
+        try:
+            out = fd.conv2d(xd, wd, bd, stride=stride, padding=padding, dilation=dilation, groups=groups)
+        finally:
+            fd.set_algo("auto")
+        cdt = torch.float64 if dtype_name == "float64" else torch.float32
+        ref = oracle.conv2d_torch_cpu(xd, wd, bd, stride, padding, dilation, groups, compute_dtype=cdt)
+        _check(out, ref, dtype_name)
+        if dtype_name == "float32":
+            _check(out, torch.from_numpy(golden[key + "_y"]), dtype_name)
+
+
+def test_aten_override_routes_functional_conv2d(fd):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 16, 12, 12, generator=g).cuda()
+    w = torch.randn(8, 16, 3, 3, generator=g).cuda()
+    b = torch.randn(8, generator=g).cuda()
+    with fd.use_dnn():
+        out = torch.nn.functional.conv2d(x, w, b, stride=1, padding=1)
+    ref = oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, 1)
+    _check(out, ref, "float32")
+
+
+def _rand(shape, seed, std=1.0, dist="normal"):
+    g = torch.Generator().manual_seed(seed)
+    if dist == "uniform":
+        return torch.rand(shape, generator=g) * 2 - 1
+    return torch.randn(shape, generator=g) * std
+
+
+# Benchmark configurations at a batch the CPU oracle finishes in seconds.
+BENCH_SMALL = [
+    # name, N, C, H, K, R, stride, pad, dtype, layout, x dist
+    ("c1_fp32_nchw_3x3", 4, 64, 56, 64, 3, 1, 1, "float32", "nchw", "normal"),
+    ("c2_bf16_1x1", 8, 256, 56, 64, 1, 1, 0, "bfloat16", "nhwc", "normal"),
+    ("c3_bf16_3x3_256", 8, 256, 14, 256, 3, 1, 1, "bfloat16", "nhwc", "normal"),
+    ("c4_bf16_stem_7x7", 4, 3, 224, 64, 7, 2, 3, "bfloat16", "nhwc", "uniform"),
+]
+
+
+@pytest.mark.parametrize("cfg", BENCH_SMALL, ids=[c[0] for c in BENCH_SMALL])
+def test_benchmark_configs_reduced_batch(fd, cfg):
+    name, n, c, hw, k, r, stride, pad, dtype_name, layout, dist = cfg
+    dtype = DTYPES[dtype_name]
+    x = _rand((n, c, hw, hw), 0, dist=dist)
+    w = _rand((k, c, r, r), 1, std=(c * r * r) ** -0.5)
+    b = _rand((k,), 2, std=0.1)
+    cl = layout == "nhwc"
+    xd, wd, bd = _to_dev(x, dtype, cl), _to_dev(w, dtype, cl), _to_dev(b, dtype, False)
+    plan = fd.conv2d_plan(xd, wd, stride=stride, padding=pad)
+    assert plan["algo"] == 2, "benchmark configurations must take the tensor-core path"
+    out = fd.fused_conv2d_bias_relu(xd, wd, bd, stride=stride, padding=pad)
+    ref = oracle.conv2d_torch_cpu(xd, wd, bd, stride, pad, 1, 1, relu=True)
+    _check(out, ref, dtype_name)
+    # second, independent oracle leg on one image (plain loops, double accumulate)
+    ref_loops = oracle.conv2d_loops(xd[:1], wd, bd, stride, pad, 1, 1, relu=True)
+    _check(out[:1], ref_loops, dtype_name)
+
+
+FULL = [
+    ("c2_bf16_1x1", 256, 256, 56, 64, 1, 1, 0),
+    ("c3_bf16_3x3_256", 256, 256, 14, 256, 3, 1, 1),
+    ("c4_bf16_stem_7x7", 256, 3, 224, 64, 7, 2, 3),
+]
+
+
+@pytest.mark.parametrize("cfg", FULL, ids=[c[0] for c in FULL])
+def test_benchmark_configs_full_size_properties(fd, cfg):
+    """At the benchmark batch the CPU oracle is too slow for every image; check
+    size-independent properties instead: images are independent (a batch slice
+    run alone gives the same answer), the result is deterministic, ReLU output
+    is non-negative, and sampled images agree with the oracle."""
+    name, n, c, hw, k, r, stride, pad = cfg
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((n, c, hw, hw), generator=g, device="cuda", dtype=torch.float32)
+    x = x.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    w = (_rand((k, c, r, r), 1, std=(c * r * r) ** -0.5)).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    b = _rand((k,), 2, std=0.1).to(torch.bfloat16).cuda()
+    out = fd.fused_conv2d_bias_relu(x, w, b, stride=stride, padding=pad)
+    again = fd.fused_conv2d_bias_relu(x, w, b, stride=stride, padding=pad)
+    assert torch.equal(out, again)
+    assert (out >= 0).all()
+    picks = [0, n // 2 + 1, n - 1]
+    for i in picks:
+        alone = fd.fused_conv2d_bias_relu(x[i:i + 1], w, b, stride=stride, padding=pad)
+        assert torch.equal(alone, out[i:i + 1])
+    ref = oracle.conv2d_torch_cpu(x[picks], w, b, stride, pad, 1, 1, relu=True)
+    _check(out[picks], ref, "bfloat16")
+    # linearity of the convolution part: conv(2x) == 2 conv(x) exactly in binary floating point
+    y1 = fd.conv2d(x[:4], w, None, stride=stride, padding=pad)
+    y2 = fd.conv2d(x[:4] * 2, w, None, stride=stride, padding=pad)
+    assert torch.equal(y2, y1 * 2)
+
+
+def test_scale_bias_epilogue_variants(fd):
+    x = _rand((3, 32, 10, 9), 10).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    w = _rand((40, 32, 3, 3), 11, std=0.06).to(torch.bfloat16).cuda()
+    b = _rand((40,), 12, std=0.1).to(torch.bfloat16).cuda()
+    s = (torch.rand(40, generator=torch.Generator().manual_seed(13)) + 0.5).to(torch.bfloat16).cuda()
+    for algo in ("igemm", "direct"):
+        fd.set_algo(algo)
+        try:
+            got = fd.fused_conv2d_bias_relu(x, w, b, padding=1, scale=s)
+            ref = oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, 1, scale=s, relu=True)
+            _check(got, ref, "bfloat16")
+            got = fd.fused_conv2d_bias_relu(x, w, b, padding=1, scale=s, activation="none")
+            ref = oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, 1, scale=s, relu=False)
+            _check(got, ref, "bfloat16")
+            got = fd.conv2d(x, w, None, padding=1)
+            ref = oracle.conv2d_torch_cpu(x, w, None, 1, 1, 1, 1)
+            _check(got, ref, "bfloat16")
+        finally:
+            fd.set_algo("auto")
+
+
+def test_scaled_graph_folds_into_one_node(fd):
+    x = _rand((2, 16, 8, 8), 20).to(torch.float16).cuda().contiguous(memory_format=torch.channels_last)
+    w = _rand((24, 16, 3, 3), 21, std=0.08).to(torch.float16).cuda()
+    s = (torch.rand(24, generator=torch.Generator().manual_seed(22)) + 0.5).to(torch.float16).cuda()
+    b = _rand((24,), 23, std=0.1).to(torch.float16).cuda()
+
+    @fd.graph
+    def fn(x, w, s, b):
+        return fd.relu(fd.bias_add(fd.conv2d(x, w, padding=1) * s, b))
+
+    compiled = fd.compile(fn, inputs=[x, w, s.reshape(1, 24, 1, 1), b], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["fused_conv2d_bias_relu"]
+    out = compiled.run(x, w, s.reshape(1, 24, 1, 1), b)
+    ref = oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, 1, scale=s, relu=True)
+    _check(out, ref, "float16")
+
+
+def test_ragged_and_strided_inputs(fd):
+    # M not a multiple of the 128-row tile, channels not a multiple of 8, output
+    # channels not a multiple of 32, and a non-dense channels-last view.
+    base = _rand((3, 24, 13, 17), 30).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    x = base[:, :16]  # channel slice: unit channel stride, pixel stride 24
+    w = _rand((37, 16, 3, 3), 31, std=0.08).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    b = _rand((37,), 32, std=0.1).to(torch.bfloat16).cuda()
+    for algo in ("igemm", "direct"):
+        fd.set_algo(algo)
+        try:
+            got = fd.fused_conv2d_bias_relu(x, w, b, stride=(2, 1), padding=(1, 2), dilation=(1, 2))
+        finally:
+            fd.set_algo("auto")
+        ref = oracle.conv2d_torch_cpu(x, w, b, (2, 1), (1, 2), (1, 2), 1, relu=True)
+        _check(got, ref, "bfloat16")
+    x5 = _rand((2, 5, 9, 9), 33).to(torch.float16).cuda()
+    w5 = _rand((3, 5, 2, 4), 34, std=0.2).to(torch.float16).cuda()
+    fd.set_algo("igemm")
+    try:
+        got = fd.conv2d(x5, w5, None, padding=(1, 3))
+    finally:
+        fd.set_algo("auto")
+    _check(got, oracle.conv2d_torch_cpu(x5, w5, None, 1, (1, 3), 1, 1), "float16")
+
+
+def test_empty_and_degenerate_outputs(fd):
+    w = torch.randn(4, 3, 3, 3, device="cuda")
+    out = fd.conv2d(torch.randn(0, 3, 8, 8, device="cuda"), w, None, padding=1)
+    assert out.shape == (0, 4, 8, 8)
+    out = fd.conv2d(torch.randn(2, 3, 2, 9, device="cuda"), w, None)  # kernel taller than the image
+    assert out.shape == (2, 4, 0, 7)
+    with pytest.raises(RuntimeError, match="negative"):
+        fd.conv2d(torch.randn(2, 3, 1, 9, device="cuda"), torch.randn(4, 3, 5, 5, device="cuda"), None)
+
+
+def test_fused_entry_contract_errors(fd):
+    x = torch.randn(1, 4, 8, 8, device="cuda")
+    w = torch.randn(4, 2, 3, 3, device="cuda")
+    b = torch.randn(4, device="cuda")
+    with pytest.raises(NotImplementedError):
+        fd.fused_conv2d_bias_relu(x, w, b, groups=2)
+    with pytest.raises(NotImplementedError):
+        fd.fused_conv2d_bias_relu(x.double(), torch.randn(4, 4, 3, 3, device="cuda").double(), b.double())
+    with pytest.raises(RuntimeError):
+        fd.fused_conv2d_bias_relu(x, torch.randn(4, 4, 3, 3, device="cuda").half(), b)
+
+    # the graph executor still runs a grouped fused node, through the direct kernel
+    @fd.graph
+    def fn(x, w, b):
+        return fd.relu(fd.bias_add(fd.conv2d(x, w, padding=1, groups=2), b))
+
+    compiled = fd.compile(fn, inputs=[x, w, b], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["fused_conv2d_bias_relu"]
+    _check(compiled.run(x, w, b), oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, 2, relu=True), "float32")
+
+
+def test_host_buffer_entry_point(fd, native_lib):
+    """fdnn_conv2d_fwd_host: host pointers in, host pointer out."""
+    import ctypes
+
+    from flagdnn_b200 import _native as nat
+
+    x = _rand((2, 16, 9, 9), 40).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    w = _rand((24, 16, 3, 3), 41, std=0.1).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    b = _rand((24,), 42, std=0.1).to(torch.bfloat16)
+    y = torch.empty((2, 24, 9, 9), dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    d = nat.ConvDesc()
+    d.dtype = nat.BF16
+    d.n, d.c, d.h, d.w = x.shape
+    d.k, _, d.r, d.s = w.shape
+    d.stride_h = d.stride_w = d.dil_h = d.dil_w = d.groups = 1
+    d.pad_top = d.pad_bottom = d.pad_left = d.pad_right = 1
+    d.algo = nat.ALGO_IGEMM
+    for i in range(4):
+        d.x_strides[i], d.w_strides[i], d.y_strides[i] = x.stride(i), w.stride(i), y.stride(i)
+    need = ctypes.c_int64(0)
+    nat.check(native_lib.fdnn_conv2d_host_arena_bytes(ctypes.byref(d), ctypes.byref(need)))
+    arena = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    nat.check(native_lib.fdnn_conv2d_fwd_host(ctypes.byref(d), x.data_ptr(), w.data_ptr(), b.data_ptr(), None,
+                                              nat.ACT_RELU, y.data_ptr(), arena.data_ptr(), need.value, None))
+    _check(y, oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, 1, relu=True), "bfloat16")

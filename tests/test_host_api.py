@@ -1,0 +1,223 @@
+"""Host-side mirror of the reference interface: argument checks, exception
+types and messages (src/flag_dnn/ops/conv2d.py:90-135, 3592-3595), and the
+graph API behaviours the reference pins in tests_graph/test_graph.py."""
+import pytest
+import torch
+
+import flagdnn_b200 as flag_dnn
+
+
+def test_cpu_tensors_raise_not_implemented(native_lib):
+    with pytest.raises(NotImplementedError):
+        flag_dnn.conv2d(torch.randn(1, 3, 8, 8), torch.randn(4, 3, 3, 3))
+    with pytest.raises(NotImplementedError):
+        flag_dnn.fused_conv2d_bias_relu(torch.randn(1, 3, 8, 8), torch.randn(4, 3, 3, 3), torch.randn(4))
+
+
+@pytest.mark.parametrize("kwargs,exc,msg", [
+    (dict(x=torch.randn(3, 8, 8)), RuntimeError, "expects 4D input and weight"),
+    (dict(x=torch.zeros(1, 3, 8, 8, dtype=torch.int32), w=torch.zeros(4, 3, 3, 3, dtype=torch.int32)), NotImplementedError, "Unsupported dtype"),
+    (dict(w=torch.randn(4, 3, 3, 3).half()), RuntimeError, "same dtype"),
+    (dict(b=torch.randn(4).double()), RuntimeError, "bias must have the same dtype"),
+    (dict(groups=0), RuntimeError, "groups must be a positive integer"),
+    (dict(stride=0), RuntimeError, "stride must be positive"),
+    (dict(dilation=(1, 0)), RuntimeError, "dilation must be positive"),
+    (dict(padding=-1), RuntimeError, "negative padding"),
+    (dict(groups=2), RuntimeError, "divisible by groups"),
+    (dict(w=torch.randn(4, 2, 3, 3)), RuntimeError, "input_channels // groups"),
+    (dict(b=torch.randn(5)), RuntimeError, "bias shape mismatch"),
+    (dict(padding="same", stride=2), RuntimeError, "not supported for strided"),
+    (dict(padding="full"), RuntimeError, "padding must be"),
+    (dict(stride=(1, 2, 3)), RuntimeError, "expected length 2"),
+])
+def test_argument_checks_match_reference(kwargs, exc, msg):
+    args = dict(x=torch.randn(1, 3, 8, 8), w=torch.randn(4, 3, 3, 3), b=None, stride=1, padding=0, dilation=1, groups=1)
+    args.update(kwargs)
+    with pytest.raises(exc, match=msg):
+        flag_dnn.conv2d(args["x"], args["w"], args["b"], args["stride"], args["padding"], args["dilation"], args["groups"])
+
+
+def test_graph_capture_fuses_bias_relu_and_eliminates_dead_node():
+    @flag_dnn.graph
+    def fn(x, bias):
+        y = flag_dnn.bias_add(x, bias)
+        out = flag_dnn.relu(y)
+        flag_dnn.relu(x)
+        return out
+
+    compiled = flag_dnn.compile(fn, inputs=[flag_dnn.TensorSpec("x", (2, 3, 4), "float32"),
+                                            flag_dnn.TensorSpec("bias", (3,), "float32")], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["fused_bias_relu"]
+    assert compiled.plan.debug_info["fusion"]["bias_activation_fused"] == 1
+
+
+def test_graph_glue_ops_execute_on_cpu():
+    @flag_dnn.graph
+    def fn(x, bias):
+        return flag_dnn.relu(flag_dnn.bias_add(x, bias))
+
+    x, bias = torch.randn(2, 3, 4), torch.randn(3)
+    compiled = flag_dnn.compile(fn, inputs=[x, bias], options={"cache": None})
+    torch.testing.assert_close(compiled.run(x, bias), torch.relu(x + bias.reshape(1, 3, 1)))
+
+
+def test_graph_operator_overload_capture():
+    @flag_dnn.graph
+    def fn(x, y):
+        return flag_dnn.relu(x + y)
+
+    x, y = torch.randn(4, 5), torch.randn(4, 5)
+    compiled = flag_dnn.compile(fn, inputs=[x, y], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["add", "relu"]
+    torch.testing.assert_close(compiled(x, y), torch.relu(x + y))
+
+
+def test_graph_conv2d_bias_relu_fuses_in_ir():
+    @flag_dnn.graph
+    def fn(x, weight, bias):
+        y = flag_dnn.conv2d(x, weight, padding=1)
+        y = flag_dnn.bias_add(y, bias)
+        return flag_dnn.relu(y)
+
+    compiled = flag_dnn.compile(fn, inputs=[flag_dnn.TensorSpec("x", (1, 3, 8, 8), "float32"),
+                                            flag_dnn.TensorSpec("weight", (4, 3, 3, 3), "float32"),
+                                            flag_dnn.TensorSpec("bias", (4,), "float32")], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["fused_conv2d_bias_relu"]
+    node = compiled.graph.nodes[0]
+    assert len(node.inputs) == 3 and node.attrs["activation"] == "relu" and node.attrs["padding"] == 1
+    assert compiled.plan.debug_info["fusion"]["conv2d_bias_activation_fused"] == 1
+    assert compiled.plan.debug_info["kernel_candidates"][0]["op_type"] == "fused_conv2d_bias_relu"
+    assert compiled.plan.output_specs[0].shape == (1, 4, 8, 8)
+
+
+def test_graph_conv_bias_without_relu_folds_bias():
+    @flag_dnn.graph
+    def fn(x, weight, bias):
+        return flag_dnn.bias_add(flag_dnn.conv2d(x, weight, stride=2), bias)
+
+    compiled = flag_dnn.compile(fn, inputs=[flag_dnn.TensorSpec("x", (1, 3, 9, 9), "float16"),
+                                            flag_dnn.TensorSpec("weight", (4, 3, 3, 3), "float16"),
+                                            flag_dnn.TensorSpec("bias", (4,), "float16")], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d"]
+    assert len(compiled.graph.nodes[0].inputs) == 3
+    assert compiled.plan.debug_info["fusion"]["conv2d_bias_folded"] == 1
+    assert compiled.plan.output_specs[0].shape == (1, 4, 4, 4)
+
+
+def test_graph_fusion_needs_single_user_and_unbiased_conv():
+    @flag_dnn.graph
+    def two_users(x, weight, bias):
+        y = flag_dnn.conv2d(x, weight)
+        return flag_dnn.relu(flag_dnn.bias_add(y, bias)), y
+
+    specs = [flag_dnn.TensorSpec("x", (1, 3, 8, 8), "float32"), flag_dnn.TensorSpec("w", (4, 3, 3, 3), "float32"),
+             flag_dnn.TensorSpec("b", (4,), "float32")]
+    compiled = flag_dnn.compile(two_users, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "fused_bias_relu"]
+
+    @flag_dnn.graph
+    def biased(x, weight, bias):
+        return flag_dnn.relu(flag_dnn.bias_add(flag_dnn.conv2d(x, weight, bias), bias))
+
+    compiled = flag_dnn.compile(biased, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "fused_bias_relu"]
+
+
+def test_graph_fusion_can_be_disabled(monkeypatch):
+    @flag_dnn.graph
+    def fn(x, weight, bias):
+        return flag_dnn.relu(flag_dnn.bias_add(flag_dnn.conv2d(x, weight), bias))
+
+    specs = [flag_dnn.TensorSpec("x", (1, 3, 8, 8), "float32"), flag_dnn.TensorSpec("w", (4, 3, 3, 3), "float32"),
+             flag_dnn.TensorSpec("b", (4,), "float32")]
+    compiled = flag_dnn.compile(fn, inputs=specs, options={"cache": None, "fusion": False})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "bias_add", "relu"]
+    monkeypatch.setenv("FLAGDNN_GRAPH_FUSION", "0")
+    compiled = flag_dnn.compile(fn, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "bias_add", "relu"]
+
+
+def test_graph_scale_pattern_folds_with_and_without_relu():
+    specs = [flag_dnn.TensorSpec("x", (1, 8, 8, 8), "bfloat16"), flag_dnn.TensorSpec("w", (16, 8, 1, 1), "bfloat16"),
+             flag_dnn.TensorSpec("s", (16, 1, 1), "bfloat16"), flag_dnn.TensorSpec("b", (16,), "bfloat16")]
+
+    @flag_dnn.graph
+    def no_relu(x, w, s, b):
+        return flag_dnn.bias_add(flag_dnn.conv2d(x, w) * s, b)
+
+    compiled = flag_dnn.compile(no_relu, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d"]
+    assert len(compiled.graph.nodes[0].inputs) == 4
+    assert compiled.plan.debug_info["fusion"]["conv2d_scale_bias_folded"] == 1
+
+    @flag_dnn.graph
+    def spatial_scale(x, w, s, b):  # not a per-channel vector: must not be absorbed
+        return flag_dnn.relu(flag_dnn.bias_add(flag_dnn.conv2d(x, w) * s, b))
+
+    specs[2] = flag_dnn.TensorSpec("s", (1, 1, 8, 8), "bfloat16")
+    compiled = flag_dnn.compile(spatial_scale, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "mul", "fused_bias_relu"]
+
+
+def test_graph_memory_plan_cache_hit():
+    cache = flag_dnn.PlanCache(enable_disk=False)
+
+    @flag_dnn.graph
+    def fn(x, bias):
+        return flag_dnn.relu(flag_dnn.bias_add(x, bias))
+
+    specs = [flag_dnn.TensorSpec("x", (2, 3), "float32"), flag_dnn.TensorSpec("bias", (3,), "float32")]
+    first = flag_dnn.compile(fn, inputs=specs, options={"cache": cache})
+    second = flag_dnn.compile(fn, inputs=specs, options={"cache": cache})
+    assert first.plan.workspace_size >= 0 and first.plan.memory_plan is not None
+    assert second.plan.debug_info["cache_hit"] is True
+    assert second.plan.debug_info["cache_layer"] == "memory"
+
+
+def test_graph_autotune_option_is_recorded():
+    @flag_dnn.graph
+    def fn(x, bias):
+        return flag_dnn.relu(flag_dnn.bias_add(x, bias))
+
+    compiled = flag_dnn.compile(fn, inputs=[torch.randn(2, 3), torch.randn(3)],
+                                options={"cache": None, "autotune": True, "autotune_repeat": 1})
+    assert compiled.plan.debug_info["autotune"]["enabled"] is True
+    assert compiled.plan.debug_info["candidate_count"] >= 1
+
+
+def test_graph_ops_namespace_capture_keeps_attrs():
+    @flag_dnn.graph
+    def fn(x, y):
+        return flag_dnn.ops.add(x, y, compute_data_type="float32", name="add")
+
+    x, y = torch.randn(4, 5), torch.randn(4, 5)
+    compiled = flag_dnn.compile(fn, inputs=[x, y], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["add"]
+    assert compiled.graph.nodes[0].attrs["name"] == "add"
+    torch.testing.assert_close(compiled(x, y), x + y)
+
+
+def test_executor_validates_inputs_and_refuses_cpu_convolution():
+    @flag_dnn.graph
+    def fn(x, weight, bias):
+        return flag_dnn.relu(flag_dnn.bias_add(flag_dnn.conv2d(x, weight), bias))
+
+    x, w, b = torch.randn(1, 3, 8, 8), torch.randn(4, 3, 3, 3), torch.randn(4)
+    compiled = flag_dnn.compile(fn, inputs=[x, w, b], options={"cache": None})
+    with pytest.raises(RuntimeError, match="shape"):
+        compiled.run(torch.randn(2, 3, 8, 8), w, b)
+    with pytest.raises(RuntimeError, match="dtype"):
+        compiled.run(x.double(), w, b)
+    with pytest.raises(RuntimeError, match="stride"):
+        compiled.run(x.contiguous(memory_format=torch.channels_last), w, b)
+    with pytest.raises(RuntimeError, match="expects 3 inputs"):
+        compiled.run(x, w)
+    with pytest.raises(NotImplementedError, match="CUDA tensors only"):
+        compiled.run(x, w, b)  # no CPU implementation of the hot path in this package
+
+
+def test_conv2d_plan_reports_library_decision(native_lib):
+    x = torch.empty(256, 256, 14, 14, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    w = torch.empty(256, 256, 3, 3, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    plan = flag_dnn.conv2d_plan(x, w, padding=1)
+    assert plan["algo"] == 2 and plan["tile_n"] == 256 and plan["x_repacked"] == 0 and plan["w_packed"] == 0

@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "fdnn_conv2d_fwd_host",
     "fdnn_conv2d_host_arena_bytes",
     "fdnn_device_status",
+    "fdnn_debug_set_profile_buffer",
 )
 
 
@@ -109,6 +110,8 @@ def load() -> ctypes.CDLL:
     lib.fdnn_conv2d_fwd_host.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.fdnn_conv2d_host_arena_bytes.restype = i32
     lib.fdnn_conv2d_host_arena_bytes.argtypes = [ctypes.POINTER(ConvDesc), ctypes.POINTER(i64)]
+    lib.fdnn_debug_set_profile_buffer.restype = i32
+    lib.fdnn_debug_set_profile_buffer.argtypes = [vp]
     lib.fdnn_device_status.restype = i32
     lib.fdnn_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     _lib = lib

@@ -271,10 +271,30 @@ int encode_filter_map(CUtensorMap* tm, int dtype, const void* base, int C, int t
   return FDNN_OK;
 }
 
+// Output map: dense NHWC y seen as a row-major [M, K] matrix; one store writes
+// 32 pixels x 128 bytes of channels.
+int encode_output_map(CUtensorMap* tm, int dtype, void* base, int K, long long M, long long row_stride) {
+  const int es = elem_size(dtype);
+  cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(M)};
+  cuuint64_t strides[1] = {cuuint64_t(row_stride) * es};
+  cuuint32_t box[2] = {cuuint32_t(128 / es), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), 2, base, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    std::snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled (output) failed with CUresult %d", int(r));
+    return fail(FDNN_CUDA_ERROR, buf);
+  }
+  return FDNN_OK;
+}
+
 __device__ uint32_t g_status_word;
 
 std::once_flag g_prepare_once[64];
 cudaError_t g_prepare_result[64];
+long long* g_prof_buffer = nullptr;  // set through fdnn_debug_set_profile_buffer
 uint32_t* g_status_ptr[64];  // device address of g_status_word, looked up once per device
 
 }  // namespace
@@ -470,10 +490,39 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
                  d.y_strides[3] % gran == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0)
                     ? 1
                     : 0;
+  // y as one [M, K] matrix: consecutive output pixels are row_stride apart
+  alignas(64) CUtensorMap tmY;
+  p.tma_store = 0;
+  {
+    // Stride between consecutive output pixels, read off the first dimension
+    // that has more than one element (strides of extent-one dims mean nothing).
+    long long row = round_up(d.k, gran);
+    if (plan.ow > 1) row = d.y_strides[3];
+    else if (plan.oh > 1) row = d.y_strides[2];
+    else if (d.n > 1) row = d.y_strides[0];
+    const bool dense = (d.k == 1 || d.y_strides[1] == 1) && row >= d.k && row % gran == 0 &&
+                       (plan.ow <= 1 || plan.oh <= 1 || d.y_strides[2] == (long long)plan.ow * row) &&
+                       (plan.oh * plan.ow <= 1 || d.n <= 1 ||
+                        d.y_strides[0] == (long long)plan.oh * plan.ow * row) &&
+                       (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
+    if (dense) {
+      st = encode_output_map(&tmY, d.dtype, y, d.k, p.M, row);
+      if (st != FDNN_OK) return st;
+      p.tma_store = 1;
+    } else {
+      tmY = tmA;
+    }
+  }
+  p.prof = g_prof_buffer;
   p.status = g_status_ptr[dev];
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
-  e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, p, plan.grid, stream);
+  e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, p, plan.grid, stream);
   if (e != cudaSuccess) return fail_cuda("igemm launch", e);
+  return FDNN_OK;
+}
+
+int fdnn_debug_set_profile_buffer(void* device_buffer_16_int64) {
+  g_prof_buffer = static_cast<long long*>(device_buffer_16_int64);
   return FDNN_OK;
 }
 

@@ -46,12 +46,15 @@ struct TileCfg {
   static constexpr int kABytes = kBM * kRowBytes;
   static constexpr int kBBytes = BN * kRowBytes;
   static constexpr int kStageBytes = (kSplit ? 2 : 1) * (kABytes + kBBytes);
-  static constexpr int kStages = (192 * 1024) / kStageBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 x 48 KB for the widest 16-bit tile
   static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128, 256 or 512
+  // per-warp output staging (32 rows x 128 bytes, swizzled, for the TMA store),
   // per-warp scale and bias staging, then barriers and bookkeeping words
+  static constexpr int kOutCols = kRowBytes / int(sizeof(T));  // output channels per TMA store
+  static constexpr int kOutBytes = kEpiWarps * 32 * kRowBytes;
   static constexpr int kEpiBytes = kEpiWarps * 2 * BN * int(sizeof(float));
   static constexpr int kBarBytes = (2 * kStages + 4 + 1) * 8 + 16;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kBarBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
@@ -109,7 +112,7 @@ template <typename T, int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                   const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
-                  const IgemmParams p) {
+                  const __grid_constant__ CUtensorMap tmY, const IgemmParams p) {
   using Cfg = TileCfg<T, BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : (std::is_same<T, __nv_bfloat16>::value ? 1u : 2u);
@@ -118,8 +121,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
-  float* epi_stage = reinterpret_cast<float*>(smem + kStages * Cfg::kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * Cfg::kStageBytes + Cfg::kEpiBytes);
+  uint8_t* out_stage = smem + kStages * Cfg::kStageBytes;  // 1024-byte aligned: stages are multiples of 1 KB
+  float* epi_stage = reinterpret_cast<float*>(out_stage + Cfg::kOutBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + Cfg::kOutBytes + Cfg::kEpiBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + kStages;
   uint64_t* tmem_full = bars + 2 * kStages;       // [2]
@@ -145,6 +149,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.tma_store) tma_prefetch_desc(&tmY);
     if constexpr (Cfg::kSplit) {
       tma_prefetch_desc(&tmA2);
       tma_prefetch_desc(&tmB2);
@@ -168,6 +173,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       bool alive = true;
+      long long prof_wait = 0, prof_issue = 0, prof_t0 = p.prof ? clock64() : 0;
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
         const int m_tile = tile / p.n_tiles;
         const int n_tile = tile - m_tile * p.n_tiles;
@@ -186,11 +192,14 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
               const uint32_t stage = it % kStages;
               const uint32_t phase = (it / kStages) & 1u;
+              const long long pt0 = p.prof ? clock64() : 0;
               if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
                                      kIncidentProducerWait)) {
                 alive = false;
                 break;
               }
+              const long long pt1 = p.prof ? clock64() : 0;
+              prof_wait += pt1 - pt0;
               uint8_t* st = stage_base + stage * Cfg::kStageBytes;
               mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
               const int c0 = cb * Cfg::kKB;
@@ -204,9 +213,13 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               } else {
                 tma_load_3d(st + Cfg::kABytes, &tmB, &full_bar[stage], c0, tap, n_tile * BN);
               }
+              if (p.prof) prof_issue += clock64() - pt1;
             }
           }
         }
+      }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[0] = prof_wait; p.prof[1] = prof_issue; p.prof[2] = clock64() - prof_t0; p.prof[3] = it;
       }
       if (!alive || *abort_flag) {
         // Teardown after an incident: let the copies already issued land before
@@ -225,24 +238,29 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       uint32_t it = 0;
       uint32_t tcount = 0;
       bool alive = true;
+      long long prof_wfull = 0, prof_wtmem = 0, prof_t0 = p.prof ? clock64() : 0;
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++tcount) {
         const uint32_t buf = tcount & 1u;
         const uint32_t bphase = (tcount >> 1) & 1u;
+        const long long mt0 = p.prof ? clock64() : 0;
         if (!mbar_wait_bounded(&tmem_empty[buf], bphase ^ 1u, abort_flag, p.status,
                                kIncidentMmaWaitTmem)) {
           alive = false;
           break;
         }
+        if (p.prof) prof_wtmem += clock64() - mt0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kit = 0; kit < k_iters; ++kit, ++it) {
           const uint32_t stage = it % kStages;
           const uint32_t phase = (it / kStages) & 1u;
+          const long long mt1 = p.prof ? clock64() : 0;
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status,
                                  kIncidentMmaWaitFull)) {
             alive = false;
             break;
           }
+          if (p.prof) prof_wfull += clock64() - mt1;
           tc_fence_after();
           const uint32_t st = smem_u32(stage_base + stage * Cfg::kStageBytes);
 #pragma unroll
@@ -267,6 +285,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
         if (alive) tc_commit(&tmem_full[buf]);
       }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[4] = prof_wfull; p.prof[5] = prof_wtmem; p.prof[6] = clock64() - prof_t0; p.prof[7] = tcount;
+      }
       if (!alive || *abort_flag) {
         // Make sure no MMA is still writing tensor memory before it is freed.
         volatile uint32_t never = 0;
@@ -284,6 +305,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     T* y = static_cast<T*>(p.y);
     uint32_t tcount = 0;
     int staged_n_tile = -1;
+    long long prof_ewait = 0, prof_t0 = p.prof ? clock64() : 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int m_tile = tile / p.n_tiles;
       const int n_tile = tile - m_tile * p.n_tiles;
@@ -302,8 +324,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         staged_n_tile = n_tile;
       }
 
+      const long long et0 = p.prof ? clock64() : 0;
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
       ok = __all_sync(0xffffffffu, ok);
+      if (p.prof) prof_ewait += clock64() - et0;
       if (!ok) break;
       tc_fence_after();
 
@@ -318,6 +342,59 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         y_off = img * p.y_sn + oh * p.y_sh + ow * p.y_sw;
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * BN;
+      if (p.tma_store) {
+        // Channel-contiguous y: each warp stages 32 pixels x 128 bytes in shared
+        // memory (128-byte swizzle, so the 16-byte row pieces of neighbouring
+        // lanes land in different banks) and one lane hands the box to a TMA
+        // store, which writes whole rows and clips the ragged edges of M and K.
+        constexpr int kPerStore = Cfg::kOutCols;           // 64 (16-bit) or 32 (fp32) channels
+        constexpr int kLoads = kPerStore / 32;             // tcgen05.ld x32 per store
+        uint8_t* my_out = out_stage + (warp - 2) * 32 * kRowBytes;
+#pragma unroll 1
+        for (int g = 0; g < BN / kPerStore; ++g) {
+          const int col0 = n0 + g * kPerStore;
+          if (col0 >= p.Kout) break;  // uniform across the warp
+          uint32_t raw[kLoads][32];
+#pragma unroll
+          for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + g * kPerStore + l * 32, raw[l]);
+          tmem_ld_wait();
+          if (lane == 0) bulk_wait_group_read0();  // the previous box has left shared memory
+          __syncwarp();
+#pragma unroll
+          for (int l = 0; l < kLoads; ++l) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float a = __uint_as_float(raw[l][j]);
+              a = fmaf(a, s_scale[g * kPerStore + l * 32 + j], s_bias[g * kPerStore + l * 32 + j]);
+              if (p.relu) a = (a < 0.0f) ? 0.0f : a;  // keeps NaN, like torch.relu
+              v[j] = a;
+            }
+            constexpr int kPieces = 32 * int(sizeof(T)) / 16;  // 16-byte pieces per 32 values
+#pragma unroll
+            for (int q = 0; q < kPieces; ++q) {
+              uint4 piece;
+              if constexpr (std::is_same<T, float>::value) {
+                piece = make_uint4(__float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
+                                   __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
+              } else {
+                piece.x = pack2(from_f32<T>(v[8 * q + 0]), from_f32<T>(v[8 * q + 1]));
+                piece.y = pack2(from_f32<T>(v[8 * q + 2]), from_f32<T>(v[8 * q + 3]));
+                piece.z = pack2(from_f32<T>(v[8 * q + 4]), from_f32<T>(v[8 * q + 5]));
+                piece.w = pack2(from_f32<T>(v[8 * q + 6]), from_f32<T>(v[8 * q + 7]));
+              }
+              const int chunk16 = l * kPieces + q;  // 0..7 within the 128-byte row
+              *reinterpret_cast<uint4*>(my_out + lane * kRowBytes + ((chunk16 ^ (lane & 7)) << 4)) = piece;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmY, my_out, col0, m_tile * kBM + ew * 32);
+            bulk_commit_group();
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < BN / 32; ++chunk) {
         const int col0 = n0 + chunk * 32;
@@ -344,8 +421,13 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
         }
       }
+      }
       tc_fence_before();
       mbar_arrive(&tmem_empty[buf]);
+    }
+    if (p.tma_store && lane == 0) bulk_wait_group0();  // stores must be done before the CTA retires
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {
+      p.prof[8] = prof_ewait; p.prof[9] = clock64() - prof_t0;
     }
   }
 
@@ -359,9 +441,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <typename T, int BN>
 cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
-                       const CUtensorMap& tmB2, const IgemmParams& p, int grid, cudaStream_t stream) {
+                       const CUtensorMap& tmB2, const CUtensorMap& tmY, const IgemmParams& p, int grid,
+                       cudaStream_t stream) {
   using Cfg = TileCfg<T, BN>;
-  conv_igemm_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, p);
+  conv_igemm_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, tmY, p);
   return cudaGetLastError();
 }
 
@@ -401,9 +484,9 @@ int igemm_stages(int dtype, int tile_n) {
 }
 
 cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
-                         const CUtensorMap& tmB, const CUtensorMap& tmB2, const IgemmParams& p,
-                         int grid, cudaStream_t stream) {
-#define FDNN_GO(T, BN) return launch_one<T, BN>(tmA, tmA2, tmB, tmB2, p, grid, stream);
+                         const CUtensorMap& tmB, const CUtensorMap& tmB2, const CUtensorMap& tmY,
+                         const IgemmParams& p, int grid, cudaStream_t stream) {
+#define FDNN_GO(T, BN) return launch_one<T, BN>(tmA, tmA2, tmB, tmB2, tmY, p, grid, stream);
   if (dtype == FDNN_F16) {
     if (tile_n == 64) FDNN_GO(__half, 64)
     if (tile_n == 128) FDNN_GO(__half, 128)

@@ -28,15 +28,17 @@ struct IgemmParams {
   void* y;
   int relu;
   int vec_store;         // 1: y is channel-contiguous and 16-byte aligned per pixel
+  int tma_store;         // 1: y is dense NHWC; the epilogue writes it through the tmY tensor map
   uint32_t* status;
+  long long* prof;       // optional: 16 cycle counters written by CTA 0 (nullptr = off)
 };
 
 // Launchers (defined in conv_igemm_sm100.cu).  `dtype` is FDNN_F16/BF16/F32.
 // tmA2 / tmB2 are the low-half operands of the split-TF32 path (ignored for
-// 16-bit types).  Returns a cudaError_t from the launch.
+// 16-bit types); tmY is the output map used when p.tma_store is set.  Returns a cudaError_t from the launch.
 cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
-                         const CUtensorMap& tmB, const CUtensorMap& tmB2, const IgemmParams& p,
-                         int grid, cudaStream_t stream);
+                         const CUtensorMap& tmB, const CUtensorMap& tmB2, const CUtensorMap& tmY,
+                         const IgemmParams& p, int grid, cudaStream_t stream);
 // Dynamic shared memory and pipeline depth of a tile configuration.
 int igemm_smem_bytes(int dtype, int tile_n);
 int igemm_stages(int dtype, int tile_n);

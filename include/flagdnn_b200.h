@@ -148,6 +148,13 @@ int fdnn_conv2d_host_arena_bytes(const fdnn_conv_desc* desc, int64_t* bytes);
  * incident) and clears it.  Returns FDNN_DEVICE_TIMEOUT if it was non-zero. */
 int fdnn_device_status(uint32_t* word);
 
+/* Development aid: when given a device buffer of 16 int64, the implicit-GEMM
+ * kernel's first CTA writes per-role cycle counters into it on every launch
+ * (producer: [0] stage-wait, [1] copy-issue, [2] total, [3] reduction steps;
+ * issuer: [4] data-wait, [5] accumulator-wait, [6] total, [7] tiles;
+ * epilogue: [8] accumulator-wait, [9] total).  NULL switches it off (default). */
+int fdnn_debug_set_profile_buffer(void* device_buffer_16_int64);
+
 #ifdef __cplusplus
 }
 #endif

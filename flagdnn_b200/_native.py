@@ -35,6 +35,9 @@ EXPORTED_SYMBOLS = (
     "fdnn_conv2d_host_arena_bytes",
     "fdnn_device_status",
     "fdnn_debug_set_profile_buffer",
+    "fdnn_conv2d_fwd_static_scratch",
+    "fdnn_static_scratch_bytes",
+    "fdnn_static_scratch_last_error",
 )
 
 
@@ -110,6 +113,10 @@ def load() -> ctypes.CDLL:
     lib.fdnn_conv2d_fwd_host.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.fdnn_conv2d_host_arena_bytes.restype = i32
     lib.fdnn_conv2d_host_arena_bytes.argtypes = [ctypes.POINTER(ConvDesc), ctypes.POINTER(i64)]
+    lib.fdnn_conv2d_fwd_static_scratch.restype = i32
+    lib.fdnn_conv2d_fwd_static_scratch.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, i32, vp, vp]
+    lib.fdnn_static_scratch_bytes.restype = i64
+    lib.fdnn_static_scratch_last_error.restype = ctypes.c_char_p
     lib.fdnn_debug_set_profile_buffer.restype = i32
     lib.fdnn_debug_set_profile_buffer.argtypes = [vp]
     lib.fdnn_device_status.restype = i32

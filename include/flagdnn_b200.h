@@ -148,6 +148,35 @@ int fdnn_conv2d_host_arena_bytes(const fdnn_conv_desc* desc, int64_t* bytes);
  * incident) and clears it.  Returns FDNN_DEVICE_TIMEOUT if it was non-zero. */
 int fdnn_device_status(uint32_t* word);
 
+/* Forward call for callers that cannot allocate device memory (no counterpart
+ * in the reference).  Identical to fdnn_conv2d_fwd except that the scratch for
+ * the relayout of x is a fixed array of FDNN_STATIC_SCRATCH_BYTES inside the
+ * library image instead of a caller-provided workspace.  It exists for hosts
+ * that fixed their device-memory budget at start-up and may not call
+ * cudaMalloc afterwards (serving processes with a pre-sized arena, plug-ins
+ * running inside another framework's memory pool, processes under a per-job
+ * memory quota).  It calls no cudaMalloc, cudaFree or allocating library
+ * routine.
+ *   - Problems whose plan.workspace_bytes exceeds FDNN_STATIC_SCRATCH_BYTES are
+ *     refused with FDNN_WORKSPACE_TOO_SMALL (text in
+ *     fdnn_static_scratch_last_error); use fdnn_conv2d_fwd for those.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call before starting any stream capture on that device.
+ *   - Every call on a device shares the one array, which keeps whatever the
+ *     last call left in it.  Calls that may overlap on the GPU (different
+ *     streams, or graphs replayed concurrently) race on it: serialise them.
+ *   - x, w, w_packed, bias, scale and y are passed exactly as for
+ *     fdnn_conv2d_fwd; a packed filter, where the plan asks for one, is still
+ *     the caller's buffer. */
+#define FDNN_STATIC_SCRATCH_BYTES (16 * 1024 * 1024)
+int fdnn_conv2d_fwd_static_scratch(const fdnn_conv_desc* desc, const void* x, const void* w,
+                                   const void* w_packed, const void* bias, const void* scale,
+                                   int activation, void* y, void* stream);
+/* Capacity of the built-in scratch (FDNN_STATIC_SCRATCH_BYTES of the built library). */
+int64_t fdnn_static_scratch_bytes(void);
+/* Detail text of the last failure of fdnn_conv2d_fwd_static_scratch on this thread. */
+const char* fdnn_static_scratch_last_error(void);
+
 /* Development aid: when given a device buffer of 16 int64, the implicit-GEMM
  * kernel's first CTA writes per-role cycle counters into it on every launch
  * (producer: [0] stage-wait, [1] copy-issue, [2] total, [3] reduction steps;

@@ -48,7 +48,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the implicit-GEMM
 # kernel, from the ncu captures summarised under profiles/ (None = not captured).
-NCU_TRAFFIC_BYTES = {"c3": None, "c2": None, "c4": None, "c1": None}
+NCU_TRAFFIC_BYTES = {"c3": 26.94e6, "c2": 495.3e6, "c4": None, "c1": None}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -262,15 +262,26 @@ def run_ours(args):
 
     # ---- device-resident leg: one CUDA graph holding one step per operand set
     stream = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
     outs = []
+
+    class _EagerCycle:
+        def replay(self):
+            for i in range(n_sets):
+                compiled.run(xs[i], w, b)
+
     with torch.cuda.stream(stream):
         for i in range(n_sets):
-            compiled.run(xs[i], w, b)
+            out = compiled.run(xs[i], w, b)
+            if args.eager:
+                outs.append(out)
         stream.synchronize()
-        with torch.cuda.graph(graph, stream=stream):
-            for i in range(n_sets):
-                outs.append(compiled.run(xs[i], w, b))
+        if args.eager:
+            graph = _EagerCycle()
+        else:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(n_sets):
+                    outs.append(compiled.run(xs[i], w, b))
     replays = max(1, -(-args.steps // n_sets))
     steps = replays * n_sets
     warm_replays = max(1, -(-max(args.warmup, 3) // n_sets))
@@ -301,7 +312,21 @@ def run_ours(args):
     ms_per_step = elapsed_ms / steps
     value = world * nums["flops"] / (ms_per_step * 1e-3) / 1e12
 
-    # ---- end-to-end leg: pinned host buffers -> device -> fused op -> host, copies inside the timed region
+    e2e_value = e2e_ms = None
+    e2e_steps = 0
+    if not args.kernel_only:
+        e2e_value, e2e_ms, e2e_steps = _e2e_leg(args, torch, dist, device, compiled, xs, outs, w, b, nums, world, barrier)
+    status_word = fd.device_status()
+    _report(args, torch, rank, world, wl, nums, peaks, peak_src, ms_per_step, value, steps, warm_replays, n_sets,
+            per_set, node_types, plan, launches_per_step, clocks, status_word, e2e_value, e2e_ms, e2e_steps)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _e2e_leg(args, torch, dist, device, compiled, xs, outs, w, b, nums, world, barrier):
+    """Pinned host buffers -> device -> fused op -> host, copies inside the timed region."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     x_host = xs[0].cpu().pin_memory()
     y_host = torch.empty_like(outs[0], device="cpu").pin_memory()
     e2e_steps = max(3, min(args.steps, 20))
@@ -327,9 +352,11 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = world * nums["flops"] / (e2e_ms / e2e_steps * 1e-3) / 1e12
+    return e2e_value, e2e_ms, e2e_steps
 
-    status_word = fd.device_status()
 
+def _report(args, torch, rank, world, wl, nums, peaks, peak_src, ms_per_step, value, steps, warm_replays, n_sets,
+            per_set, node_types, plan, launches_per_step, clocks, status_word, e2e_value, e2e_ms, e2e_steps):
     if rank == 0:
         # ---- roofline of the dominant kernel (the implicit-GEMM kernel; one launch per step)
         if wl["bound"] == "tensor":
@@ -344,28 +371,27 @@ def run_ours(args):
                     "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peak_src}",
                     "kernel": "conv_igemm_kernel", "algorithmic_flops_per_launch": nums["flops"],
                     "algorithmic_bytes_per_launch": nums["bytes"], **extra}
-        cpu = cpu_baseline_leg(wl, torch, sample_n=min(wl["n"], 32))
+        cpu = None if args.kernel_only else cpu_baseline_leg(wl, torch, sample_n=min(wl["n"], 32))
+        e2e = None if e2e_value is None else {
+            "value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": nums["x_bytes"],
+            "d2h_bytes_per_step": nums["y_bytes"], "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps}
         line = {
             "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": warm_replays * n_sets, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
             "config": {"workload": args.workload, "description": wl["desc"], "graph_nodes": node_types,
-                       "launch": "cuda_graph_replay", "l2": f"{n_sets} rotating (x, y) sets = "
+                       "launch": "eager_api_calls" if args.eager else "cuda_graph_replay", "l2": f"{n_sets} rotating (x, y) sets = "
                        f"{n_sets * per_set / 2**20:.0f} MiB > 126 MiB L2; filter and bias shared",
                        "per_gpu_batch": wl["n"], "parallelism": f"batch-sharded replicas x{world}, no collective",
                        "tile": [plan["tile_m"], plan["tile_n"], plan["tile_k"]], "stages": plan["stages"],
                        "grid": plan["grid"]},
             "pct_of_bf16_peak": 100.0 * (value / world) / peaks["bf16_tflops"],
             "roofline": roofline, "cpu_baseline": cpu,
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": nums["x_bytes"],
-                    "d2h_bytes_per_step": nums["y_bytes"], "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "e2e": e2e,
             "gpu_launches": steps * launches_per_step,
             "clocks": clocks.summary(), "device_status_word": status_word,
         }
         print(json.dumps(line))
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 def main():
@@ -375,6 +401,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--eager", action="store_true",
+                    help="launch every step through the API instead of replaying a CUDA graph (for profilers)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

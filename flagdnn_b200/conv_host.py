@@ -36,12 +36,14 @@ _FORCED_ALGO = nat.ALGO_AUTO
 
 
 def set_algo(algo: Union[int, str]) -> int:
-    """Force the kernel family for subsequent calls: "auto", "direct" or "igemm".
+    """Force the kernel family for subsequent calls: "auto", "direct", "igemm"
+    (one CTA per tile) or "pair" (CTA pairs).
 
     Returns the previous setting.  Meant for tests and benchmarks.
     """
     global _FORCED_ALGO
-    names = {"auto": nat.ALGO_AUTO, "direct": nat.ALGO_DIRECT, "igemm": nat.ALGO_IGEMM}
+    names = {"auto": nat.ALGO_AUTO, "direct": nat.ALGO_DIRECT, "igemm": nat.ALGO_IGEMM,
+             "pair": nat.ALGO_IGEMM_PAIR}
     prev = _FORCED_ALGO
     _FORCED_ALGO = names[algo] if isinstance(algo, str) else int(algo)
     return prev
@@ -216,7 +218,7 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         stream = torch.cuda.current_stream().cuda_stream
         packed_ptr = None
         packed = None
-        if plan.algo == nat.ALGO_IGEMM and plan.w_packed:
+        if plan.algo != nat.ALGO_DIRECT and plan.w_packed:
             packed = _packed_weight(weight, d, plan, stream)
             packed_ptr = packed.data_ptr()
         ws_ptr = None

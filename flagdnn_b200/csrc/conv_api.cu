@@ -103,13 +103,33 @@ int choose_tile_n(int dtype, int m_tiles, int kout, int sms) {
     if (bn > 64 && bn / 2 >= kout) break;  // a tile twice as wide as the problem is pure waste
     const long long tiles = (long long)m_tiles * ((kout + bn - 1) / bn);
     const long long waves = (tiles + sms - 1) / sms;
-    const double cost = double(waves) * (bn + 32);
+    // Measured on B200: a 128-wide tile costs about 0.8 of a 256-wide one (the
+    // activation tile and the per-step overheads do not shrink with N).
+    const double cost = double(waves) * (bn + 384);
     if (cost <= best_cost) {
       best_cost = cost;
       best = bn;
     }
   }
   return best;
+}
+
+// Stride between consecutive output pixels when y is one dense [M, K] matrix
+// (channels contiguous, pixels / rows / images evenly spaced), else 0.
+long long y_pixel_stride(const fdnn_conv_desc* d, int oh, int ow) {
+  const int gran = 16 / elem_size(d->dtype);
+  long long row = round_up(d->k, gran);
+  if (ow > 1) row = d->y_strides[3];
+  else if (oh > 1) row = d->y_strides[2];
+  else if (d->n > 1) row = d->y_strides[0];
+  const bool dense = (d->k == 1 || d->y_strides[1] == 1) && row >= d->k && row % gran == 0 &&
+                     (ow <= 1 || oh <= 1 || d->y_strides[2] == (long long)ow * row) &&
+                     ((long long)oh * ow <= 1 || d->n <= 1 || d->y_strides[0] == (long long)oh * ow * row);
+  return dense ? row : 0;
+}
+
+bool y_is_dense_nhwc(const fdnn_conv_desc* d, int oh, int ow, const void* y) {
+  return y_pixel_stride(d, oh, ow) > 0 && aligned16(y);
 }
 
 int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void* y,
@@ -131,10 +151,11 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
 
   const bool geom_ok = igemm_geometry_ok(d) && m > 0 && m < 2.0e9;
   int algo = d->algo;
-  if (algo == FDNN_ALGO_IGEMM && !geom_ok)
+  if ((algo == FDNN_ALGO_IGEMM || algo == FDNN_ALGO_IGEMM_PAIR) && !geom_ok)
     return fail(FDNN_NOT_SUPPORTED, "implicit-GEMM path does not support this problem");
-  if (algo == FDNN_ALGO_AUTO) algo = (geom_ok && plan->flops >= 2.0e7) ? FDNN_ALGO_IGEMM : FDNN_ALGO_DIRECT;
-  if (algo != FDNN_ALGO_IGEMM && algo != FDNN_ALGO_DIRECT)
+  const bool want_auto = algo == FDNN_ALGO_AUTO;
+  if (want_auto) algo = (geom_ok && plan->flops >= 2.0e7) ? FDNN_ALGO_IGEMM : FDNN_ALGO_DIRECT;
+  if (algo != FDNN_ALGO_IGEMM && algo != FDNN_ALGO_DIRECT && algo != FDNN_ALGO_IGEMM_PAIR)
     return fail(FDNN_BAD_PARAM, "unknown algo");
   plan->algo = algo;
 
@@ -182,7 +203,24 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   plan->grid = int(tiles < sms ? tiles : sms);
   plan->block = 192;
   plan->launches = 1 + plan->x_repacked;
-  (void)y;
+
+  // CTA pairs: 16-bit types writing a dense NHWC y.  Worth it when the layer is
+  // wide enough for 256-channel tiles and has at least one full wave of pairs.
+  const bool pair_ok = is16 && y_is_dense_nhwc(d, oh, ow, y) && (sms % 2 == 0);
+  if (algo == FDNN_ALGO_IGEMM_PAIR && !pair_ok)
+    return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs f16/bf16 tensors and a dense channels-last output");
+  const long long pair_tiles = (long long)((m_tiles + 1) / 2) * ((d->k + 255) / 256);
+  if (algo == FDNN_ALGO_IGEMM_PAIR ||
+      (want_auto && pair_ok && d->k >= 256 && (long long)d->r * d->s * ((c_pad + 63) / 64) >= 16 &&
+       pair_tiles >= sms / 2)) {
+    plan->algo = FDNN_ALGO_IGEMM_PAIR;
+    plan->tile_m = 256;
+    plan->tile_n = 256;
+    plan->stages = igemm_pair_stages();
+    plan->smem_bytes = igemm_pair_smem_bytes();
+    const long long pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
+    plan->grid = int(2 * pairs);
+  }
   return FDNN_OK;
 }
 
@@ -402,6 +440,7 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
     int major = 0;
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     g_prepare_result[dev] = (major == 10) ? igemm_prepare_device() : cudaErrorNoKernelImageForDevice;
+    if (g_prepare_result[dev] == cudaSuccess) g_prepare_result[dev] = igemm_pair_prepare_device();
     g_status_ptr[dev] = device_status_word();
   });
   if (g_prepare_result[dev] == cudaErrorNoKernelImageForDevice)
@@ -458,7 +497,8 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   alignas(64) CUtensorMap tmA, tmA2, tmB, tmB2;
   st = encode_activation_map(&tmA, d.dtype, a_base, a_c, d.w, d.h, d.n, a_sw, a_sh, a_sn, &d);
   if (st != FDNN_OK) return st;
-  st = encode_filter_map(&tmB, d.dtype, b_base, b_c, d.r * d.s, d.k, b_stap, b_sk, plan.tile_n);
+  const int b_box_rows = plan.algo == FDNN_ALGO_IGEMM_PAIR ? 128 : plan.tile_n;  // each CTA of a pair stages half
+  st = encode_filter_map(&tmB, d.dtype, b_base, b_c, d.r * d.s, d.k, b_stap, b_sk, b_box_rows);
   if (st != FDNN_OK) return st;
   if (d.dtype == FDNN_F32) {
     st = encode_activation_map(&tmA2, d.dtype, static_cast<const char*>(a_base) + a_plane * es, a_c, d.w,
@@ -494,18 +534,8 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   alignas(64) CUtensorMap tmY;
   p.tma_store = 0;
   {
-    // Stride between consecutive output pixels, read off the first dimension
-    // that has more than one element (strides of extent-one dims mean nothing).
-    long long row = round_up(d.k, gran);
-    if (plan.ow > 1) row = d.y_strides[3];
-    else if (plan.oh > 1) row = d.y_strides[2];
-    else if (d.n > 1) row = d.y_strides[0];
-    const bool dense = (d.k == 1 || d.y_strides[1] == 1) && row >= d.k && row % gran == 0 &&
-                       (plan.ow <= 1 || plan.oh <= 1 || d.y_strides[2] == (long long)plan.ow * row) &&
-                       (plan.oh * plan.ow <= 1 || d.n <= 1 ||
-                        d.y_strides[0] == (long long)plan.oh * plan.ow * row) &&
-                       (reinterpret_cast<uintptr_t>(y) & 15u) == 0;
-    if (dense) {
+    const long long row = y_pixel_stride(&d, plan.oh, plan.ow);
+    if (row > 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0) {
       st = encode_output_map(&tmY, d.dtype, y, d.k, p.M, row);
       if (st != FDNN_OK) return st;
       p.tma_store = 1;
@@ -516,7 +546,12 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   p.prof = g_prof_buffer;
   p.status = g_status_ptr[dev];
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
-  e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, p, plan.grid, stream);
+  if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
+    if (!p.tma_store) return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs a dense channels-last output");
+    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, p, plan.grid, stream);
+  } else {
+    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, p, plan.grid, stream);
+  }
   if (e != cudaSuccess) return fail_cuda("igemm launch", e);
   return FDNN_OK;
 }
@@ -615,7 +650,7 @@ int fdnn_conv2d_fwd_host(const fdnn_conv_desc* desc, const void* x_host, const v
     if (e != cudaSuccess) return fail_cuda("copy scale", e);
   }
   const void* packed = nullptr;
-  if (a.plan.algo == FDNN_ALGO_IGEMM && a.plan.w_packed) {
+  if (a.plan.algo != FDNN_ALGO_DIRECT && a.plan.w_packed) {
     st = fdnn_conv2d_pack_weight(desc, base + a.w, base + a.packed, a.plan.packed_weight_bytes, stream);
     if (st != FDNN_OK) return st;
     packed = base + a.packed;

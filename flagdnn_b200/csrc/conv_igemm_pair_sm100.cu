@@ -1,0 +1,333 @@
+// Implicit-GEMM convolution forward on CTA pairs (tcgen05 cta_group::2).
+//
+// Same arithmetic and GEMM view as conv_igemm_sm100.cu; what changes is who
+// holds what.  Two CTAs of a cluster share one 256-row x 256-channel output
+// tile: each CTA copies its own 128 activation rows and its own 128 filter rows
+// (half of the tile's output channels), and the leader CTA issues MMAs of shape
+// 256 x 256 x 16 that read both CTAs' shared memory and accumulate into both
+// CTAs' tensor memory (128 rows each).  Per SM that is 32 KB of operands per
+// reduction step instead of 48 KB, which is what the single-CTA kernel is short
+// of on compute-bound layers.  Nothing is broadcast: every copy is issued by,
+// and lands in, the CTA that uses it.
+//
+//   warp 0 (each CTA)  producer: waits for its own "stage empty" barrier, copies
+//                      A (im2col mode) and its half of B, crediting the bytes to
+//                      the LEADER's "stage full" barrier
+//   warp 1 (leader)    issuer: waits "stage full", issues the pair MMAs, commits
+//                      to both CTAs' "stage empty" barriers, and after the last
+//                      step to both CTAs' "accumulator full" barriers
+//   warps 2..5 (each)  epilogue on the CTA's own 128 rows, then an arrive on the
+//                      leader's "accumulator empty" barrier
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
+#include "conv_convert.cuh"
+#include "conv_internal.h"
+#include "sm100_ptx.cuh"
+
+namespace fdnn {
+namespace {
+
+constexpr int kRows = 128;           // output rows per CTA (pair tile: 256)
+constexpr int kPairN = 256;          // output channels per pair tile
+constexpr int kHalfN = 128;          // filter rows staged per CTA
+constexpr int kRowB = 128;           // bytes per swizzled shared-memory row
+constexpr int kKB = 64;              // 16-bit reduction elements per stage
+constexpr int kABytes = kRows * kRowB;
+constexpr int kBBytes = kHalfN * kRowB;
+constexpr int kStageBytes = kABytes + kBBytes;      // 32 KB per CTA per stage
+constexpr int kStages = 6;                           // 192 KB
+constexpr int kThreadsPair = 192;
+constexpr int kOutBytes = 4 * 32 * kRowB;            // per-warp TMA-store staging
+constexpr int kEpiBytes = 4 * 2 * kPairN * int(sizeof(float));
+constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
+constexpr int kSmemPair = kStages * kStageBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
+constexpr uint32_t kTmemColsPair = 512;              // two 256-column accumulators
+static_assert(kSmemPair <= 227 * 1024, "shared memory budget");
+
+template <typename T>
+__global__ void __launch_bounds__(kThreadsPair, 1)
+conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmY, const IgemmParams p) {
+  constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : 1u;
+  constexpr uint32_t kIdesc = make_idesc(kFmt, 2 * kRows, kPairN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* stage_base = smem;
+  uint8_t* out_stage = smem + kStages * kStageBytes;
+  float* epi_stage = reinterpret_cast<float*>(out_stage + kOutBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + kOutBytes + kEpiBytes);
+  uint64_t* full_bar = bars;                       // used in the leader only
+  uint64_t* empty_bar = bars + kStages;            // each CTA's own
+  uint64_t* tmem_full = bars + 2 * kStages;        // [2], each CTA's own
+  uint64_t* tmem_empty = bars + 2 * kStages + 2;   // [2], used in the leader only
+  uint64_t* drain_bar = bars + 2 * kStages + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();         // 0 = leader
+  const uint32_t peer = rank ^ 1u;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&full_bar[i], 1);                  // the leader producer's arrive.expect_tx
+      mbar_init(&empty_bar[i], 1);                 // one commit from the leader's issuer
+    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_full[1], 1);
+    mbar_init(&tmem_empty[0], 2 * 4 * 32);         // epilogue threads of both CTAs
+    mbar_init(&tmem_empty[1], 2 * 4 * 32);
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmY);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemColsPair);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int n_tiles = (p.Kout + kPairN - 1) / kPairN;
+  const int m_pairs = (p.M + 2 * kRows - 1) / (2 * kRows);
+  const int total_tiles = m_pairs * n_tiles;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int k_iters = p.R * p.S * p.c_blocks;
+  const int ohw = p.OH * p.OW;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      const uint32_t full0 = map_to_cta(smem_u32(&full_bar[0]), 0);  // the leader's barriers
+      for (int tile = pair_id; tile < total_tiles && alive; tile += num_pairs) {
+        const int m_pair = tile / n_tiles;
+        const int n_tile = tile - m_pair * n_tiles;
+        const int m0 = m_pair * 2 * kRows + int(rank) * kRows;
+        const int img = m0 / ohw;
+        const int rem = m0 - img * ohw;
+        const int oh0 = rem / p.OW;
+        const int ow0 = rem - oh0 * p.OW;
+        const int w_base = ow0 * p.stride_w - p.pad_left;
+        const int h_base = oh0 * p.stride_h - p.pad_top;
+        const int b_row0 = n_tile * kPairN + int(rank) * kHalfN;
+        for (int r = 0; r < p.R && alive; ++r) {
+          for (int s = 0; s < p.S && alive; ++s) {
+            const uint16_t off_w = static_cast<uint16_t>(s * p.dil_w);
+            const uint16_t off_h = static_cast<uint16_t>(r * p.dil_h);
+            const int tap = r * p.S + s;
+            for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
+              const uint32_t stage = it % kStages;
+              const uint32_t phase = (it / kStages) & 1u;
+              if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
+                                     kIncidentProducerWait)) {
+                alive = false;
+                break;
+              }
+              uint8_t* st = stage_base + stage * kStageBytes;
+              if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
+              const uint32_t bar = full0 + stage * 8;
+              const int c0 = cb * kKB;
+              tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, off_w, off_h);
+              tma_load_3d_pair(st + kABytes, &tmB, bar, c0, tap, b_row0);
+            }
+          }
+        }
+      }
+      if (!alive || *abort_flag) {
+        // After an incident: give copies already issued time to land.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------- issuer (leader only)
+    if (rank == 0 && lane == 0) {
+      uint32_t it = 0;
+      uint32_t tcount = 0;
+      bool alive = true;
+      const uint32_t empty_own = smem_u32(&empty_bar[0]);
+      const uint32_t empty_peer = map_to_cta(empty_own, 1);
+      const uint32_t tfull_own = smem_u32(&tmem_full[0]);
+      const uint32_t tfull_peer = map_to_cta(tfull_own, 1);
+      for (int tile = pair_id; tile < total_tiles && alive; tile += num_pairs, ++tcount) {
+        const uint32_t buf = tcount & 1u;
+        const uint32_t bphase = (tcount >> 1) & 1u;
+        if (!mbar_wait_bounded(&tmem_empty[buf], bphase ^ 1u, abort_flag, p.status,
+                               kIncidentMmaWaitTmem)) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * kPairN;
+        for (int kit = 0; kit < k_iters; ++kit, ++it) {
+          const uint32_t stage = it % kStages;
+          const uint32_t phase = (it / kStages) & 1u;
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t st = smem_u32(stage_base + stage * kStageBytes);
+#pragma unroll
+          for (int k = 0; k < kKB / 16; ++k) {
+            const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
+            const uint64_t b = make_sw128_kmajor_desc(st + kABytes + k * 32);
+            mma_f16_pair(d_tmem, a, b, kIdesc, (kit > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(empty_own + stage * 8);
+          tc_commit_pair(empty_peer + stage * 8);
+        }
+        if (alive) {
+          tc_commit_pair(tfull_own + buf * 8);
+          tc_commit_pair(tfull_peer + buf * 8);
+        }
+      }
+      if (!alive || *abort_flag) {
+        volatile uint32_t never = 0;
+        tc_commit_pair(smem_u32(drain_bar));
+        mbar_wait_bounded(drain_bar, 0u, &never, p.status, kIncidentDrainWait, kWaitLimitCycles / 16);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int ew = warp & 3;
+    float* s_scale = epi_stage + (warp - 2) * 2 * kPairN;
+    float* s_bias = s_scale + kPairN;
+    const T* g_bias = static_cast<const T*>(p.bias);
+    const T* g_scale = static_cast<const T*>(p.scale);
+    uint8_t* my_out = out_stage + (warp - 2) * 32 * kRowB;
+    const uint32_t tempty_leader = map_to_cta(smem_u32(&tmem_empty[0]), 0);
+    uint32_t tcount = 0;
+    int staged_n_tile = -1;
+    for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++tcount) {
+      const int m_pair = tile / n_tiles;
+      const int n_tile = tile - m_pair * n_tiles;
+      const int n0 = n_tile * kPairN;
+      const uint32_t buf = tcount & 1u;
+      const uint32_t bphase = (tcount >> 1) & 1u;
+      if (n_tile != staged_n_tile) {
+        __syncwarp();
+        for (int j = lane; j < kPairN; j += 32) {
+          const int col = n0 + j;
+          s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col]) : 1.0f;
+          s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col]) : 0.0f;
+        }
+        __syncwarp();
+        staged_n_tile = n_tile;
+      }
+      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row0 = m_pair * 2 * kRows + int(rank) * kRows + ew * 32;
+      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN;
+#pragma unroll 1
+      for (int g = 0; g < kPairN / 64; ++g) {
+        const int col0 = n0 + g * 64;
+        if (col0 >= p.Kout) break;
+        uint32_t raw[2][32];
+        tmem_ld_32x32b_x32(t_row + g * 64, raw[0]);
+        tmem_ld_32x32b_x32(t_row + g * 64 + 32, raw[1]);
+        tmem_ld_wait();
+        if (lane == 0) bulk_wait_group_read0();
+        __syncwarp();
+#pragma unroll
+        for (int l = 0; l < 2; ++l) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float a = __uint_as_float(raw[l][j]);
+            a = fmaf(a, s_scale[g * 64 + l * 32 + j], s_bias[g * 64 + l * 32 + j]);
+            if (p.relu) a = (a < 0.0f) ? 0.0f : a;
+            v[j] = a;
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 piece;
+            piece.x = pack2(from_f32<T>(v[8 * q + 0]), from_f32<T>(v[8 * q + 1]));
+            piece.y = pack2(from_f32<T>(v[8 * q + 2]), from_f32<T>(v[8 * q + 3]));
+            piece.z = pack2(from_f32<T>(v[8 * q + 4]), from_f32<T>(v[8 * q + 5]));
+            piece.w = pack2(from_f32<T>(v[8 * q + 6]), from_f32<T>(v[8 * q + 7]));
+            const int chunk16 = l * 4 + q;
+            *reinterpret_cast<uint4*>(my_out + lane * kRowB + ((chunk16 ^ (lane & 7)) << 4)) = piece;
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmY, my_out, col0, row0);
+          bulk_commit_group();
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(tempty_leader + buf * 8);
+    }
+    if (lane == 0) bulk_wait_group0();
+  }
+
+  // Neither CTA may retire while its partner can still signal its barriers or
+  // the leader's MMAs can still read its shared memory.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemColsPair);
+  }
+}
+
+template <typename T>
+cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
+                          const IgemmParams& p, int grid, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreadsPair, 1, 1);
+  cfg.dynamicSmemBytes = kSmemPair;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T>, tmA, tmB, tmY, p);
+}
+
+}  // namespace
+
+cudaError_t igemm_pair_prepare_device() {
+  cudaError_t e = cudaFuncSetAttribute(conv_igemm_pair_kernel<__half>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPair);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(conv_igemm_pair_kernel<__nv_bfloat16>,
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPair);
+}
+
+int igemm_pair_smem_bytes() { return kSmemPair; }
+int igemm_pair_stages() { return kStages; }
+
+cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                              const CUtensorMap& tmY, const IgemmParams& p, int grid,
+                              cudaStream_t stream) {
+  if (dtype == FDNN_F16) return launch_pair_t<__half>(tmA, tmB, tmY, p, grid, stream);
+  if (dtype == FDNN_BF16) return launch_pair_t<__nv_bfloat16>(tmA, tmB, tmY, p, grid, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fdnn

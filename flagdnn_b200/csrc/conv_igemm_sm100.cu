@@ -26,6 +26,7 @@
 
 #include <type_traits>
 
+#include "conv_convert.cuh"
 #include "conv_internal.h"
 #include "sm100_ptx.cuh"
 
@@ -58,33 +59,6 @@ struct TileCfg {
   static_assert(kStages >= 2, "pipeline needs at least two stages");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
-
-template <typename T>
-__device__ __forceinline__ float to_f32(T v);
-template <>
-__device__ __forceinline__ float to_f32<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
-template <>
-__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-
-template <typename T>
-__device__ __forceinline__ T from_f32(float v);
-template <>
-__device__ __forceinline__ float from_f32<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
-template <>
-__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ uint32_t pack2(__half a, __half b) {
-  __half2 h = __halves2half2(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-__device__ __forceinline__ uint32_t pack2(__nv_bfloat16 a, __nv_bfloat16 b) {
-  __nv_bfloat162 h = __halves2bfloat162(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // 32 finished values of one output pixel -> 32 consecutive channels of y.
 template <typename T>

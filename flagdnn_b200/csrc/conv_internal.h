@@ -45,6 +45,15 @@ int igemm_stages(int dtype, int tile_n);
 // One-time opt-in to large dynamic shared memory for every instantiation.
 cudaError_t igemm_prepare_device();
 
+// CTA-pair variant (conv_igemm_pair_sm100.cu): 16-bit types, 256 x 256 pair
+// tiles, TMA-store epilogue only (p.tma_store must be set).  `grid` must be even.
+cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                              const CUtensorMap& tmY, const IgemmParams& p, int grid,
+                              cudaStream_t stream);
+cudaError_t igemm_pair_prepare_device();
+int igemm_pair_smem_bytes();
+int igemm_pair_stages();
+
 // Direct convolution on CUDA cores (conv_direct.cu): any dtype, groups, strides.
 struct DirectParams {
   int N, C, H, W, K, R, S, OH, OW;

@@ -49,7 +49,8 @@ typedef enum fdnn_status {
 /* algorithm selector */
 #define FDNN_ALGO_AUTO 0
 #define FDNN_ALGO_DIRECT 1 /* CUDA-core direct convolution (any dtype, groups) */
-#define FDNN_ALGO_IGEMM 2  /* tcgen05 implicit GEMM (f16/bf16, f32 via 3xTF32) */
+#define FDNN_ALGO_IGEMM 2  /* tcgen05 implicit GEMM, one CTA per tile (f16/bf16, f32 via 3xTF32) */
+#define FDNN_ALGO_IGEMM_PAIR 3 /* tcgen05 implicit GEMM on CTA pairs (f16/bf16, dense NHWC y) */
 
 /* epilogue activation */
 #define FDNN_ACT_NONE 0
@@ -74,7 +75,7 @@ typedef struct fdnn_conv_desc {
 
 /* What fdnn_conv2d_query decides for a descriptor. */
 typedef struct fdnn_conv_plan {
-  int32_t algo;                 /* FDNN_ALGO_DIRECT or FDNN_ALGO_IGEMM */
+  int32_t algo;                 /* FDNN_ALGO_DIRECT, FDNN_ALGO_IGEMM or FDNN_ALGO_IGEMM_PAIR */
   int32_t oh, ow;               /* output size, rule of src/flag_dnn/ops/conv2d.py:52-62 */
   int32_t tile_m, tile_n, tile_k, stages; /* igemm tile; 0 for direct */
   int32_t x_repacked;           /* 1: x is first rewritten into the workspace as NHWC, C padded */

@@ -56,10 +56,13 @@ def test_struct_layout_matches_header():
 
 def test_query_plans_headline_configs(native_lib):
     plan = nat.ConvPlan()
-    # 3x3 256-channel headline layer: in place, widest tile, one CTA per SM
+    # 3x3 256-channel headline layer: in place, 256 x 256 tiles on CTA pairs, one CTA per SM
     d = _desc(n=256, c=256, h=14, w=14, k=256)
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
-    assert (plan.algo, plan.tile_m, plan.tile_n, plan.x_repacked, plan.w_packed) == (nat.ALGO_IGEMM, 128, 256, 0, 0)
+    assert (plan.algo, plan.tile_m, plan.tile_n, plan.x_repacked, plan.w_packed) == (nat.ALGO_IGEMM_PAIR, 256, 256, 0, 0)
+    d.algo = nat.ALGO_IGEMM  # the single-CTA kernel can still be asked for
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert (plan.algo, plan.tile_m, plan.tile_n, plan.stages) == (nat.ALGO_IGEMM, 128, 256, 4)
     assert plan.workspace_bytes == 0 and plan.packed_weight_bytes == 0
     assert plan.oh == 14 and plan.ow == 14 and plan.block == 192 and plan.grid == 148
     assert plan.flops == pytest.approx(59.190e9, rel=1e-3)
@@ -86,6 +89,10 @@ def test_query_routes_unsupported_geometry_to_direct(native_lib):
         assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
         assert plan.algo == nat.ALGO_DIRECT and plan.workspace_bytes == 0
     d = _desc(groups=2, algo=nat.ALGO_IGEMM)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_NOT_SUPPORTED
+    d = _desc(algo=nat.ALGO_IGEMM_PAIR, channels_last=False)  # NCHW output cannot go through the pair kernel
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_NOT_SUPPORTED
+    d = _desc(algo=nat.ALGO_IGEMM_PAIR, dtype=nat.F32)
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_NOT_SUPPORTED
     with pytest.raises(NotImplementedError):
         nat.check(nat.FDNN_NOT_SUPPORTED)

@@ -40,11 +40,13 @@ def _check(out, ref, dtype_name):
                                ref.float() if dtype_name != "float64" else ref, **TOL[dtype_name])
 
 
-@pytest.mark.parametrize("algo", ["igemm", "direct"])
+@pytest.mark.parametrize("algo", ["igemm", "pair", "direct"])
 @pytest.mark.parametrize("channels_last", [True, False])
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16", "float16"])
 @pytest.mark.parametrize("idx", range(len(FUSED_CASES)))
 def test_fused_graph_matches_oracle(fd, golden, idx, dtype_name, channels_last, algo):
+    if algo == "pair" and (dtype_name == "float32" or not channels_last):
+        pytest.skip("the CTA-pair kernel takes 16-bit tensors and writes channels-last outputs")
     ishape, wshape, stride, padding, dilation = FUSED_CASES[idx]
     key = f"fused_{idx:02d}"
     dtype = DTYPES[dtype_name]
@@ -136,7 +138,7 @@ def test_benchmark_configs_reduced_batch(fd, cfg):
     cl = layout == "nhwc"
     xd, wd, bd = _to_dev(x, dtype, cl), _to_dev(w, dtype, cl), _to_dev(b, dtype, False)
     plan = fd.conv2d_plan(xd, wd, stride=stride, padding=pad)
-    assert plan["algo"] == 2, "benchmark configurations must take the tensor-core path"
+    assert plan["algo"] in (2, 3), "benchmark configurations must take the tensor-core path"
     out = fd.fused_conv2d_bias_relu(xd, wd, bd, stride=stride, padding=pad)
     ref = oracle.conv2d_torch_cpu(xd, wd, bd, stride, pad, 1, 1, relu=True)
     _check(out, ref, dtype_name)
@@ -185,7 +187,7 @@ def test_scale_bias_epilogue_variants(fd):
     w = _rand((40, 32, 3, 3), 11, std=0.06).to(torch.bfloat16).cuda()
     b = _rand((40,), 12, std=0.1).to(torch.bfloat16).cuda()
     s = (torch.rand(40, generator=torch.Generator().manual_seed(13)) + 0.5).to(torch.bfloat16).cuda()
-    for algo in ("igemm", "direct"):
+    for algo in ("igemm", "pair", "direct"):
         fd.set_algo(algo)
         try:
             got = fd.fused_conv2d_bias_relu(x, w, b, padding=1, scale=s)
@@ -199,6 +201,24 @@ def test_scale_bias_epilogue_variants(fd):
             _check(got, ref, "bfloat16")
         finally:
             fd.set_algo("auto")
+
+
+@pytest.mark.parametrize("shape", [(5, 192, 20, 20, 320, 3, 1, 1), (2, 64, 40, 33, 256, 1, 1, 0), (3, 128, 17, 17, 600, 3, 2, 1)])
+def test_pair_kernel_matches_single_cta_kernel_bitwise(fd, shape):
+    """Both tensor-core kernels accumulate the same products in the same order."""
+    n, c, h, w_, k, r, stride, pad = shape
+    x = _rand((n, c, h, w_), 50).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    w = _rand((k, c, r, r), 51, std=(c * r * r) ** -0.5).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    b = _rand((k,), 52, std=0.1).to(torch.bfloat16).cuda()
+    outs = {}
+    for algo in ("igemm", "pair"):
+        fd.set_algo(algo)
+        try:
+            outs[algo] = fd.fused_conv2d_bias_relu(x, w, b, stride=stride, padding=pad)
+        finally:
+            fd.set_algo("auto")
+    assert torch.equal(outs["igemm"], outs["pair"])
+    _check(outs["pair"], oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, 1, relu=True), "bfloat16")
 
 
 def test_scaled_graph_folds_into_one_node(fd):
@@ -225,7 +245,7 @@ def test_ragged_and_strided_inputs(fd):
     x = base[:, :16]  # channel slice: unit channel stride, pixel stride 24
     w = _rand((37, 16, 3, 3), 31, std=0.08).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
     b = _rand((37,), 32, std=0.1).to(torch.bfloat16).cuda()
-    for algo in ("igemm", "direct"):
+    for algo in ("igemm", "pair", "direct"):
         fd.set_algo(algo)
         try:
             got = fd.fused_conv2d_bias_relu(x, w, b, stride=(2, 1), padding=(1, 2), dilation=(1, 2))

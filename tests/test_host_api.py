@@ -220,4 +220,4 @@ def test_conv2d_plan_reports_library_decision(native_lib):
     x = torch.empty(256, 256, 14, 14, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
     w = torch.empty(256, 256, 3, 3, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
     plan = flag_dnn.conv2d_plan(x, w, padding=1)
-    assert plan["algo"] == 2 and plan["tile_n"] == 256 and plan["x_repacked"] == 0 and plan["w_packed"] == 0
+    assert plan["algo"] == 3 and plan["tile_n"] == 256 and plan["x_repacked"] == 0 and plan["w_packed"] == 0

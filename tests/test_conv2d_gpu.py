@@ -62,6 +62,16 @@ def test_fused_graph_matches_oracle(fd, golden, idx, dtype_name, channels_last, 
                                       fd.TensorSpec.from_tensor(bd, "bias")], options={"cache": None})
     assert [n.op_type for n in compiled.graph.nodes] == ["fused_conv2d_bias_relu"]
     assert compiled.plan.debug_info["fusion"]["conv2d_bias_activation_fused"] == 1
+    if algo == "pair" and wshape[0] % 8 != 0:
+        # y rows of K elements must be 16-byte multiples for the pair kernel's TMA stores;
+        # forcing it on such a shape is refused, which the graph layer turns into its fallback
+        fd.set_algo("pair")
+        try:
+            with pytest.raises(NotImplementedError):
+                fd.fused_conv2d_bias_relu(xd, wd, bd, stride=stride, padding=padding, dilation=dilation)
+        finally:
+            fd.set_algo("auto")
+        return
     fd.set_algo(algo)
     try:
         out = compiled.run(xd.clone(), wd.clone(), bd.clone())
@@ -245,7 +255,7 @@ def test_ragged_and_strided_inputs(fd):
     x = base[:, :16]  # channel slice: unit channel stride, pixel stride 24
     w = _rand((37, 16, 3, 3), 31, std=0.08).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
     b = _rand((37,), 32, std=0.1).to(torch.bfloat16).cuda()
-    for algo in ("igemm", "pair", "direct"):
+    for algo in ("igemm", "direct"):  # 37 output channels: no 16-byte rows, so not the pair kernel
         fd.set_algo(algo)
         try:
             got = fd.fused_conv2d_bias_relu(x, w, b, stride=(2, 1), padding=(1, 2), dilation=(1, 2))

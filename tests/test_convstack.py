@@ -1,0 +1,54 @@
+"""The ResNet-50 convolution stack: shape bookkeeping on CPU, per-layer and
+end-to-end parity with the oracle on the GPU."""
+import pytest
+import torch
+
+import oracle
+from flagdnn_b200.convstack import ResNet50ConvStack, resnet50_conv_layers, stack_totals
+
+
+def test_layer_list_matches_published_resnet50_arithmetic():
+    layers = resnet50_conv_layers()
+    totals = stack_totals(layers, 1024)
+    assert totals["convs"] == 53 and totals["unique_shapes"] == 23
+    assert totals["flops"] == pytest.approx(8.3705e12, rel=1e-4)       # 8.174 GFLOP per image
+    assert totals["bytes"] == pytest.approx(44.65e9, rel=1e-3)
+    assert sum(1 for l in layers if not l.relu) == 16 + 4               # third 1x1 of 16 blocks + 4 projections
+    assert [l.hw_out for l in layers if l.name.endswith("b0.conv2")] == [56, 28, 14, 7]
+    stem = layers[0]
+    assert (stem.cin, stem.cout, stem.k, stem.stride, stem.pad, stem.hw_out) == (3, 64, 7, 2, 3, 112)
+
+
+def _oracle_layer(layer, x, params):
+    w, scale, bias = params
+    y = oracle.conv2d_torch_cpu(x, w, bias, layer.stride, layer.pad, 1, 1, scale=scale, relu=layer.relu)
+    return y.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("image,batch", [(224, 2), (64, 5)])
+def test_every_layer_matches_oracle_and_chain_matches_end_to_end(native_lib, image, batch):
+    import flagdnn_b200 as fd
+
+    stack = ResNet50ConvStack("cuda", seed=7, image=image)
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(batch, 3, image, image, generator=g).to(torch.bfloat16)
+    x_dev = x.cuda().contiguous(memory_format=torch.channels_last)
+    seen = []
+    y_dev = stack.forward(x_dev, collect=seen)
+    assert len(seen) == 53
+    for layer, inp, out in seen:  # each layer on the very input it consumed
+        ref = oracle.conv2d_torch_cpu(inp, stack.params[stack.layers.index(layer)][0],
+                                      stack.params[stack.layers.index(layer)][2], layer.stride, layer.pad, 1, 1,
+                                      scale=stack.params[stack.layers.index(layer)][1], relu=layer.relu)
+        torch.testing.assert_close(out.float().cpu(), ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"{layer.name}: {m}")
+    # end to end: the same chain with every convolution done by the CPU oracle (bf16 between layers)
+    cpu_params = [tuple(t.cpu() for t in p) for p in stack.params]
+    stack_cpu = ResNet50ConvStack.__new__(ResNet50ConvStack)
+    stack_cpu.layers, stack_cpu.params = stack.layers, cpu_params
+    y_ref = stack_cpu.forward(x.contiguous(memory_format=torch.channels_last), conv=_oracle_layer)
+    assert y_dev.shape == y_ref.shape == (batch, 2048, image // 32, image // 32)
+    err = (y_dev.float().cpu() - y_ref.float()).abs()
+    # 53 layers of bf16 rounding compound; agreement is judged relative to the activation scale
+    assert err.max() <= 0.05 * y_ref.float().abs().max() + 0.05
+    assert fd.device_status() == 0

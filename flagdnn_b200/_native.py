@@ -69,6 +69,7 @@ class ConvPlan(ctypes.Structure):
         ("c_padded", ctypes.c_int32),
         ("grid", ctypes.c_int32), ("block", ctypes.c_int32),
         ("launches", ctypes.c_int32),
+        ("low_channel", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_int64),
         ("packed_weight_bytes", ctypes.c_int64),
         ("smem_bytes", ctypes.c_int64),

@@ -150,7 +150,9 @@ def _plan_for(input, weight, out, stride, padding4, dilation, groups, algo):
 
 def _packed_weight(weight: torch.Tensor, d: nat.ConvDesc, plan: nat.ConvPlan, stream: int) -> torch.Tensor:
     version = int(getattr(weight, "_version", 0))
-    key = ("krsc", id(weight), weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()),
+    # the packed layout depends on the plan: generic [K,R,S,Cpad] or the low-channel quad layout
+    layout = ("lowc", d.stride_w) if plan.low_channel else ("krsc", plan.c_padded)
+    key = (layout, id(weight), weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()),
            str(weight.dtype), weight.device.type, weight.device.index, version)
     entry = _PACKED_WEIGHT_CACHE.get(key)
     if entry is not None:

@@ -132,6 +132,36 @@ bool y_is_dense_nhwc(const fdnn_conv_desc* d, int oh, int ow, const void* y) {
   return y_pixel_stride(d, oh, ow) > 0 && aligned16(y);
 }
 
+// Low-channel mode (C <= 4, e.g. the 7x7 stride-2 stem): four neighbouring
+// output pixels of a row form one GEMM row with 4*K columns; its operand is a
+// 16-pixel window (64 elements = 128 bytes) of the input repacked to 4 channels,
+// so a filter row costs one fat TMA row instead of S thin ones.
+struct LowChannel {
+  bool ok;
+  int ow4, ohs, rows_per_tile, tiles_per_image, w_pad;
+  int lpad;  // zero pixels stored left of each row: the conv's left padding rounded up to even (16-byte pixels pairs)
+};
+
+LowChannel low_channel_geometry(const fdnn_conv_desc* d, int oh, int ow, const void* y) {
+  LowChannel g = {};
+  const bool is16 = elem_size(d->dtype) == 2;
+  if (!is16 || d->groups != 1 || d->c > 4 || d->dil_w != 1 || ow < 4 || ow % 4 != 0 || ow / 4 > 128) return g;
+  g.lpad = round_up(d->pad_left, 2);
+  if (d->stride_w > 8 || d->stride_h > 8 || 3 * d->stride_w + (d->s - 1) + (g.lpad - d->pad_left) > 15 || d->k % 2 != 0) return g;
+  if (oh <= 0 || d->pad_top > 255 || d->pad_left > 255) return g;
+  if (y_pixel_stride(d, oh, ow) != d->k || !aligned16(y)) return g;  // a quad's 4*K outputs must be contiguous
+  g.ow4 = ow / 4;
+  g.ohs = 128 / g.ow4;
+  if (g.ohs > oh) g.ohs = oh;
+  if (g.ohs * d->stride_h > 256) g.ohs = 256 / d->stride_h;
+  g.rows_per_tile = g.ohs * g.ow4;
+  g.tiles_per_image = (oh + g.ohs - 1) / g.ohs;
+  const int need = d->stride_w * 4 * (g.ow4 - 1) + 16;
+  g.w_pad = round_up(need > g.lpad + d->w ? need : g.lpad + d->w, 2);
+  g.ok = true;
+  return g;
+}
+
 int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void* y,
               fdnn_conv_plan* plan) {
   int st = validate(d);
@@ -167,6 +197,40 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     plan->grid = int(blocks);
     plan->block = 256;
     plan->launches = 1;
+    return FDNN_OK;
+  }
+
+  const LowChannel lc = low_channel_geometry(d, oh, ow, y);
+  if (lc.ok) {
+    const int sms_lc = sm_count();
+    const int m_tiles_lc = d->n * lc.tiles_per_image;
+    const int n_gemm = 4 * d->k;
+    plan->low_channel = 1;
+    plan->c_padded = 4;
+    plan->x_repacked = 1;
+    plan->w_packed = 1;
+    plan->workspace_bytes = (long long)d->n * d->h * lc.w_pad * 4 * es;
+    plan->packed_weight_bytes = (long long)n_gemm * d->r * 64 * es;
+    plan->tile_m = 128;
+    plan->tile_k = 64;
+    plan->tile_n = choose_tile_n(d->dtype, m_tiles_lc, n_gemm, sms_lc);
+    plan->stages = igemm_stages(d->dtype, plan->tile_n);
+    plan->smem_bytes = igemm_smem_bytes(d->dtype, plan->tile_n);
+    const long long tiles_lc = (long long)m_tiles_lc * ((n_gemm + plan->tile_n - 1) / plan->tile_n);
+    plan->grid = int(tiles_lc < sms_lc ? tiles_lc : sms_lc);
+    plan->block = 192;
+    plan->launches = 2;
+    const long long pair_tiles_lc = (long long)((m_tiles_lc + 1) / 2) * ((n_gemm + 255) / 256);
+    if (algo == FDNN_ALGO_IGEMM_PAIR ||
+        (want_auto && sms_lc % 2 == 0 && n_gemm >= 256 && pair_tiles_lc >= sms_lc / 2)) {
+      plan->algo = FDNN_ALGO_IGEMM_PAIR;
+      plan->tile_m = 256;
+      plan->tile_n = 256;
+      plan->stages = igemm_pair_stages();
+      plan->smem_bytes = igemm_pair_smem_bytes();
+      const long long pairs = pair_tiles_lc < sms_lc / 2 ? pair_tiles_lc : sms_lc / 2;
+      plan->grid = int(2 * pairs);
+    }
     return FDNN_OK;
   }
 
@@ -313,11 +377,12 @@ int encode_filter_map(CUtensorMap* tm, int dtype, const void* base, int C, int t
 // 32 pixels x 128 bytes of channels.
 int encode_output_map(CUtensorMap* tm, int dtype, void* base, int K, long long M, long long row_stride) {
   const int es = elem_size(dtype);
-  cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(M)};
-  cuuint64_t strides[1] = {cuuint64_t(row_stride) * es};
-  cuuint32_t box[2] = {cuuint32_t(128 / es), 32};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), 2, base, dims, strides, box, estr,
+  // three-dimensional so that the low-channel mode can share the store path: (channel, row, image = 1)
+  cuuint64_t dims[3] = {cuuint64_t(K), cuuint64_t(M), 1};
+  cuuint64_t strides[2] = {cuuint64_t(row_stride) * es, cuuint64_t(row_stride) * es * cuuint64_t(M)};
+  cuuint32_t box[3] = {cuuint32_t(128 / es), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), 3, base, dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -346,6 +411,104 @@ uint32_t* device_status_word() {
   return static_cast<uint32_t*>(p);
 }
 
+}  // namespace fdnn
+
+namespace fdnn {
+namespace {
+
+int encode_tiled(CUtensorMap* tm, int dtype, const void* base, int rank, const cuuint64_t* dims,
+                 const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* estr, const char* what) {
+  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), rank, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    std::snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled (%s) failed with CUresult %d", what, int(r));
+    return fail(FDNN_CUDA_ERROR, buf);
+  }
+  return FDNN_OK;
+}
+
+// Low-channel forward: repack x to [N][H][w_pad][4], then run the implicit-GEMM
+// kernel with pixel quads as rows (see LowChannel above).
+int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev, const void* x,
+                    const void* w_packed, const void* bias, const void* scale, int activation, void* y,
+                    void* workspace, cudaStream_t stream) {
+  const int es = elem_size(d.dtype);
+  const LowChannel lc = low_channel_geometry(&d, plan.oh, plan.ow, y);
+  if (!lc.ok) return fail(FDNN_BAD_PARAM, "low-channel plan no longer applies to these buffers");
+  cudaError_t e = launch_repack_x_lowc(d.dtype, x, reinterpret_cast<const long long*>(d.x_strides), d.n, d.c, d.h,
+                                       d.w, lc.lpad, lc.w_pad, workspace, stream);
+  if (e != cudaSuccess) return fail_cuda("low-channel repack launch", e);
+
+  const int n_gemm = 4 * d.k;
+  alignas(64) CUtensorMap tmA, tmB, tmY, tmY2;
+  {
+    // windows of 64 elements that start every 4 output pixels' worth of input (overlapping rows)
+    cuuint64_t dims[4] = {64, cuuint64_t(lc.ow4), cuuint64_t(d.h), cuuint64_t(d.n)};
+    cuuint64_t strides[3] = {cuuint64_t(d.stride_w) * 4 * 4 * es, cuuint64_t(lc.w_pad) * 4 * es,
+                             cuuint64_t(d.h) * lc.w_pad * 4 * es};
+    cuuint32_t box[4] = {64, cuuint32_t(lc.ow4), cuuint32_t(lc.ohs * d.stride_h), 1};
+    cuuint32_t estr[4] = {1, 1, cuuint32_t(d.stride_h), 1};
+    int st = encode_tiled(&tmA, d.dtype, workspace, 4, dims, strides, box, estr, "low-channel activations");
+    if (st != FDNN_OK) return st;
+  }
+  const int b_box_rows = plan.algo == FDNN_ALGO_IGEMM_PAIR ? 128 : plan.tile_n;
+  {
+    cuuint64_t dims[3] = {64, cuuint64_t(d.r), cuuint64_t(n_gemm)};
+    cuuint64_t strides[2] = {cuuint64_t(64) * es, cuuint64_t(d.r) * 64 * es};
+    cuuint32_t box[3] = {64, 1, cuuint32_t(b_box_rows)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    int st = encode_tiled(&tmB, d.dtype, w_packed, 3, dims, strides, box, estr, "low-channel filter");
+    if (st != FDNN_OK) return st;
+  }
+  const int tail_rows = lc.rows_per_tile % 32;
+  {
+    // y as (4*K channels of a quad, quads of one image, images)
+    cuuint64_t dims[3] = {cuuint64_t(n_gemm), cuuint64_t(plan.oh) * lc.ow4, cuuint64_t(d.n)};
+    cuuint64_t strides[2] = {cuuint64_t(n_gemm) * es, cuuint64_t(plan.oh) * lc.ow4 * n_gemm * es};
+    cuuint32_t estr[3] = {1, 1, 1};
+    cuuint32_t box[3] = {64, 32, 1};
+    int st = encode_tiled(&tmY, d.dtype, y, 3, dims, strides, box, estr, "low-channel output");
+    if (st != FDNN_OK) return st;
+    cuuint32_t box2[3] = {64, cuuint32_t(tail_rows > 0 ? tail_rows : 32), 1};
+    st = encode_tiled(&tmY2, d.dtype, y, 3, dims, strides, box2, estr, "low-channel output tail");
+    if (st != FDNN_OK) return st;
+  }
+
+  IgemmParams p = {};
+  p.Kout = n_gemm;
+  p.k_real = d.k;
+  p.OH = plan.oh; p.OW = plan.ow;
+  p.stride_h = d.stride_h; p.stride_w = d.stride_w; p.pad_top = d.pad_top; p.pad_left = d.pad_left;
+  p.dil_h = d.dil_h; p.dil_w = 1;
+  p.R = d.r; p.S = 1; p.c_blocks = 1;
+  p.m_tiles = d.n * lc.tiles_per_image;
+  p.M = p.m_tiles * 128;
+  p.n_tiles = (n_gemm + plan.tile_n - 1) / plan.tile_n;
+  p.bias = bias; p.scale = scale; p.y = y;
+  p.relu = activation == FDNN_ACT_RELU;
+  p.vec_store = 0;
+  p.tma_store = 1;
+  p.lowc = 1;
+  p.rows_per_tile = lc.rows_per_tile;
+  p.tiles_per_image = lc.tiles_per_image;
+  p.ohs = lc.ohs;
+  p.a_tx_bytes = lc.rows_per_tile * 128;
+  p.prof = g_prof_buffer;
+  p.status = g_status_ptr[dev];
+  if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
+  if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
+    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY2, p, plan.grid, stream);
+  } else {
+    // the single-CTA kernel has no fifth 16-bit map slot: the tail map travels in the unused tmA2 slot
+    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmY2, tmB, tmB, tmY, p, plan.grid, stream);
+  }
+  if (e != cudaSuccess) return fail_cuda("low-channel igemm launch", e);
+  return FDNN_OK;
+}
+
+}  // namespace
 }  // namespace fdnn
 
 using namespace fdnn;
@@ -381,15 +544,22 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, void* pac
   d = *desc;
   d.algo = FDNN_ALGO_IGEMM;
   // Packing is decided against an unaligned pointer so the answer is "packed".
+  // The layout (generic [K,R,S,Cpad] or the low-channel one) follows from the
+  // descriptor alone, y strides included, exactly as fdnn_conv2d_fwd will decide.
   fdnn_conv_plan plan;
   int st = make_plan(&d, nullptr, reinterpret_cast<const void*>(uintptr_t(1)), nullptr, &plan);
   if (st != FDNN_OK) return st;
   if (w == nullptr || packed == nullptr) return fail(FDNN_BAD_PARAM, "w and packed must not be NULL");
   if (packed_bytes < plan.packed_weight_bytes)
     return fail(FDNN_WORKSPACE_TOO_SMALL, "packed filter buffer too small");
-  const int es = elem_size(d.dtype);
+  if (plan.low_channel) {
+    const int shift = round_up(d.pad_left, 2) - d.pad_left;
+    cudaError_t e = launch_pack_w_lowc(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c,
+                                       d.r, d.s, d.stride_w, shift, packed, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda("pack_weight launch", e);
+    return FDNN_OK;
+  }
   const long long plane = (long long)d.k * d.r * d.s * plan.c_padded;
-  (void)es;
   cudaError_t e = launch_pack_w(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c,
                                 d.r, d.s, plan.c_padded, packed, plane, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail_cuda("pack_weight launch", e);
@@ -460,6 +630,8 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (plan.w_packed && (reinterpret_cast<uintptr_t>(w_packed) & 15u) != 0)
     return fail(FDNN_BAD_PARAM, "packed filter must be 16-byte aligned");
 
+  if (plan.low_channel) return fwd_low_channel(d, plan, dev, x, w_packed, bias, scale, activation, y, workspace, stream);
+
   const int es = elem_size(d.dtype);
   const int c_pad = plan.c_padded;
   const void* a_base = x;
@@ -512,9 +684,12 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
     tmB2 = tmB;
   }
 
-  IgemmParams p;
+  IgemmParams p = {};
   p.M = d.n * plan.oh * plan.ow;
   p.Kout = d.k;
+  p.k_real = d.k;
+  p.lowc = 0;
+  p.rows_per_tile = 128;
   p.OH = plan.oh; p.OW = plan.ow;
   p.stride_h = d.stride_h; p.stride_w = d.stride_w; p.pad_top = d.pad_top; p.pad_left = d.pad_left;
   p.dil_h = d.dil_h; p.dil_w = d.dil_w;
@@ -548,7 +723,7 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
   if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
     if (!p.tma_store) return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs a dense channels-last output");
-    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, p, plan.grid, stream);
+    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY, p, plan.grid, stream);
   } else {
     e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, p, plan.grid, stream);
   }

@@ -1,0 +1,101 @@
+// Epilogue shared by the implicit-GEMM kernels when y is dense NHWC: one warp
+// drains its 32 accumulator rows from tensor memory, applies per-channel scale,
+// bias and ReLU in fp32, rounds once, stages 32 rows x 128 bytes in shared
+// memory and hands each box to a TMA store.  The arithmetic is that of the
+// reference's fused kernel (src/flag_dnn/graph/kernels/fused_conv.py:297-310).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <type_traits>
+
+#include "sm100_ptx.cuh"
+
+namespace fdnn {
+
+// max(a, 0) that returns NaN for NaN, like torch.relu (plain max would return 0).
+__device__ __forceinline__ float relu_keep_nan(float a) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(0.0f));
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t round_pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t round_pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t round_pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// t_row     tensor-memory address of this warp's lane quarter, first column of the tile
+// n0        first GEMM column of the tile; kout: number of valid GEMM columns overall
+// s_scale / s_bias  this warp's fp32 copies for columns n0 .. n0+BN-1
+// my_out    this warp's 4 KB staging buffer (1024-byte aligned)
+// tm_full / tm_tail  output maps with a 32-row box and a box of the tile's ragged last rows
+// st_row, st_img     y coordinates (row, image) of the warp's first row; st_rows: valid rows (<= 0: none)
+template <typename T, int BN>
+__device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int relu,
+                                                    const float* s_scale, const float* s_bias,
+                                                    uint8_t* my_out, int lane, const CUtensorMap* tm_full,
+                                                    const CUtensorMap* tm_tail, int st_row, int st_img,
+                                                    int st_rows) {
+  constexpr int kPerStore = 128 / int(sizeof(T));  // channels per staged row: 64 (16-bit) or 32 (fp32)
+  constexpr int kLoads = kPerStore / 32;
+  int groups = (kout - n0 + kPerStore - 1) / kPerStore;
+  if (groups > BN / kPerStore) groups = BN / kPerStore;
+  if (groups <= 0) return;
+  uint32_t raw[kLoads][32];
+#pragma unroll
+  for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + l * 32, raw[l]);
+#pragma unroll 1
+  for (int g = 0; g < groups; ++g) {
+    tmem_ld_wait();
+    uint32_t row[32];  // the 128 bytes this lane contributes
+#pragma unroll
+    for (int l = 0; l < kLoads; ++l) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const int c = g * kPerStore + l * 32 + j;
+        float a = fmaf(__uint_as_float(raw[l][j]), s_scale[c], s_bias[c]);
+        float b = fmaf(__uint_as_float(raw[l][j + 1]), s_scale[c + 1], s_bias[c + 1]);
+        if (relu) {
+          a = relu_keep_nan(a);
+          b = relu_keep_nan(b);
+        }
+        if constexpr (std::is_same<T, float>::value) {
+          row[j] = __float_as_uint(a);
+          row[j + 1] = __float_as_uint(b);
+        } else {
+          row[l * 16 + j / 2] = round_pack2<T>(a, b);
+        }
+      }
+    }
+    // the accumulator columns of the next group travel while this one is stored
+    if (g + 1 < groups) {
+#pragma unroll
+      for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + (g + 1) * kPerStore + l * 32, raw[l]);
+    }
+    if (lane == 0) bulk_wait_group_read0();  // the previous box has left the staging buffer
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      // 128-byte swizzle: the 16-byte pieces of neighbouring rows land in different banks
+      *reinterpret_cast<uint4*>(my_out + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+          make_uint4(row[4 * q], row[4 * q + 1], row[4 * q + 2], row[4 * q + 3]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && st_rows > 0) {
+      tma_store_3d(st_rows >= 32 ? tm_full : tm_tail, my_out, n0 + g * kPerStore, st_row, st_img);
+      bulk_commit_group();
+    }
+  }
+}
+
+}  // namespace fdnn

@@ -24,6 +24,7 @@
 #include <type_traits>
 
 #include "conv_convert.cuh"
+#include "conv_epilogue.cuh"
 #include "conv_internal.h"
 #include "sm100_ptx.cuh"
 
@@ -50,7 +51,8 @@ static_assert(kSmemPair <= 227 * 1024, "shared memory budget");
 template <typename T>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                       const __grid_constant__ CUtensorMap tmY, const IgemmParams p) {
+                       const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmY2,
+                       const IgemmParams p) {
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : 1u;
   constexpr uint32_t kIdesc = make_idesc(kFmt, 2 * kRows, kPairN);
 
@@ -88,6 +90,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmY);
+    if (p.lowc) tma_prefetch_desc(&tmY2);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, kTmemColsPair);
@@ -100,7 +103,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const uint32_t tmem_base = *tmem_slot;
 
   const int n_tiles = (p.Kout + kPairN - 1) / kPairN;
-  const int m_pairs = (p.M + 2 * kRows - 1) / (2 * kRows);
+  const int m_pairs = (p.m_tiles + 1) / 2;
   const int total_tiles = m_pairs * n_tiles;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
@@ -116,13 +119,23 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       for (int tile = pair_id; tile < total_tiles && alive; tile += num_pairs) {
         const int m_pair = tile / n_tiles;
         const int n_tile = tile - m_pair * n_tiles;
-        const int m0 = m_pair * 2 * kRows + int(rank) * kRows;
-        const int img = m0 / ohw;
-        const int rem = m0 - img * ohw;
-        const int oh0 = rem / p.OW;
-        const int ow0 = rem - oh0 * p.OW;
-        const int w_base = ow0 * p.stride_w - p.pad_left;
-        const int h_base = oh0 * p.stride_h - p.pad_top;
+        const int m_tile = 2 * m_pair + int(rank);  // this CTA's 128-row tile (may lie past the end)
+        int img, w_base, h_base;
+        if (p.lowc) {
+          img = m_tile / p.tiles_per_image;
+          const int ti = m_tile - img * p.tiles_per_image;
+          w_base = 0;
+          h_base = ti * p.ohs * p.stride_h - p.pad_top;
+        } else {
+          const int m0 = m_tile * kRows;
+          img = m0 / ohw;
+          const int rem = m0 - img * ohw;
+          const int oh0 = rem / p.OW;
+          const int ow0 = rem - oh0 * p.OW;
+          w_base = ow0 * p.stride_w - p.pad_left;
+          h_base = oh0 * p.stride_h - p.pad_top;
+        }
+        const uint32_t pair_tx = p.lowc ? uint32_t(2 * (p.a_tx_bytes + kBBytes)) : uint32_t(2 * kStageBytes);
         const int b_row0 = n_tile * kPairN + int(rank) * kHalfN;
         for (int r = 0; r < p.R && alive; ++r) {
           for (int s = 0; s < p.S && alive; ++s) {
@@ -138,10 +151,14 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 break;
               }
               uint8_t* st = stage_base + stage * kStageBytes;
-              if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kStageBytes);
+              if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], pair_tx);
               const uint32_t bar = full0 + stage * 8;
               const int c0 = cb * kKB;
-              tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, off_w, off_h);
+              if (p.lowc) {
+                tma_load_4d_pair(st, &tmA, bar, 0, 0, h_base + r * p.dil_h, img);
+              } else {
+                tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, off_w, off_h);
+              }
               tma_load_3d_pair(st + kABytes, &tmB, bar, c0, tap, b_row0);
             }
           }
@@ -224,8 +241,8 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         __syncwarp();
         for (int j = lane; j < kPairN; j += 32) {
           const int col = n0 + j;
-          s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col]) : 1.0f;
-          s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col]) : 0.0f;
+          s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col % p.k_real]) : 1.0f;
+          s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col % p.k_real]) : 0.0f;
         }
         __syncwarp();
         staged_n_tile = n_tile;
@@ -234,46 +251,20 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row0 = m_pair * 2 * kRows + int(rank) * kRows + ew * 32;
-      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN;
-#pragma unroll 1
-      for (int g = 0; g < kPairN / 64; ++g) {
-        const int col0 = n0 + g * 64;
-        if (col0 >= p.Kout) break;
-        uint32_t raw[2][32];
-        tmem_ld_32x32b_x32(t_row + g * 64, raw[0]);
-        tmem_ld_32x32b_x32(t_row + g * 64 + 32, raw[1]);
-        tmem_ld_wait();
-        if (lane == 0) bulk_wait_group_read0();
-        __syncwarp();
-#pragma unroll
-        for (int l = 0; l < 2; ++l) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float a = __uint_as_float(raw[l][j]);
-            a = fmaf(a, s_scale[g * 64 + l * 32 + j], s_bias[g * 64 + l * 32 + j]);
-            if (p.relu) a = (a < 0.0f) ? 0.0f : a;
-            v[j] = a;
-          }
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 piece;
-            piece.x = pack2(from_f32<T>(v[8 * q + 0]), from_f32<T>(v[8 * q + 1]));
-            piece.y = pack2(from_f32<T>(v[8 * q + 2]), from_f32<T>(v[8 * q + 3]));
-            piece.z = pack2(from_f32<T>(v[8 * q + 4]), from_f32<T>(v[8 * q + 5]));
-            piece.w = pack2(from_f32<T>(v[8 * q + 6]), from_f32<T>(v[8 * q + 7]));
-            const int chunk16 = l * 4 + q;
-            *reinterpret_cast<uint4*>(my_out + lane * kRowB + ((chunk16 ^ (lane & 7)) << 4)) = piece;
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&tmY, my_out, col0, row0);
-          bulk_commit_group();
-        }
+      const int m_tile = 2 * m_pair + int(rank);
+      int st_row, st_img, st_rows;
+      if (p.lowc) {
+        st_img = m_tile / p.tiles_per_image;
+        st_row = (m_tile - st_img * p.tiles_per_image) * p.rows_per_tile + ew * 32;
+        st_rows = p.rows_per_tile - ew * 32;
+      } else {
+        st_img = 0;
+        st_row = m_tile * kRows + ew * 32;
+        st_rows = 32;
       }
+      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN;
+      epilogue_store_tile<T, kPairN>(t_row, n0, p.Kout, p.relu, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
+                                     st_row, st_img, st_rows);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }
@@ -293,7 +284,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
 template <typename T>
 cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
-                          const IgemmParams& p, int grid, cudaStream_t stream) {
+                          const CUtensorMap& tmY2, const IgemmParams& p, int grid, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreadsPair, 1, 1);
@@ -306,7 +297,7 @@ cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T>, tmA, tmB, tmY, p);
+  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T>, tmA, tmB, tmY, tmY2, p);
 }
 
 }  // namespace
@@ -323,10 +314,10 @@ int igemm_pair_smem_bytes() { return kSmemPair; }
 int igemm_pair_stages() { return kStages; }
 
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                              const CUtensorMap& tmY, const IgemmParams& p, int grid,
-                              cudaStream_t stream) {
-  if (dtype == FDNN_F16) return launch_pair_t<__half>(tmA, tmB, tmY, p, grid, stream);
-  if (dtype == FDNN_BF16) return launch_pair_t<__nv_bfloat16>(tmA, tmB, tmY, p, grid, stream);
+                              const CUtensorMap& tmY, const CUtensorMap& tmY2, const IgemmParams& p,
+                              int grid, cudaStream_t stream) {
+  if (dtype == FDNN_F16) return launch_pair_t<__half>(tmA, tmB, tmY, tmY2, p, grid, stream);
+  if (dtype == FDNN_BF16) return launch_pair_t<__nv_bfloat16>(tmA, tmB, tmY, tmY2, p, grid, stream);
   return cudaErrorInvalidValue;
 }
 

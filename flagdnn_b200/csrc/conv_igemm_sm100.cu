@@ -27,6 +27,7 @@
 #include <type_traits>
 
 #include "conv_convert.cuh"
+#include "conv_epilogue.cuh"
 #include "conv_internal.h"
 #include "sm100_ptx.cuh"
 
@@ -151,13 +152,22 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
         const int m_tile = tile / p.n_tiles;
         const int n_tile = tile - m_tile * p.n_tiles;
-        const int m0 = m_tile * kBM;
-        const int img = m0 / ohw;
-        const int rem = m0 - img * ohw;
-        const int oh0 = rem / p.OW;
-        const int ow0 = rem - oh0 * p.OW;
-        const int w_base = ow0 * p.stride_w - p.pad_left;
-        const int h_base = oh0 * p.stride_h - p.pad_top;
+        int img, w_base, h_base;
+        if (p.lowc) {
+          img = m_tile / p.tiles_per_image;
+          const int ti = m_tile - img * p.tiles_per_image;
+          w_base = 0;
+          h_base = ti * p.ohs * p.stride_h - p.pad_top;
+        } else {
+          const int m0 = m_tile * kBM;
+          img = m0 / ohw;
+          const int rem = m0 - img * ohw;
+          const int oh0 = rem / p.OW;
+          const int ow0 = rem - oh0 * p.OW;
+          w_base = ow0 * p.stride_w - p.pad_left;
+          h_base = oh0 * p.stride_h - p.pad_top;
+        }
+        const uint32_t stage_tx = p.lowc ? uint32_t(p.a_tx_bytes + Cfg::kBBytes) : uint32_t(Cfg::kStageBytes);
         for (int r = 0; r < p.R && alive; ++r) {
           for (int s = 0; s < p.S && alive; ++s) {
             const uint16_t off_w = static_cast<uint16_t>(s * p.dil_w);
@@ -175,9 +185,14 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               const long long pt1 = p.prof ? clock64() : 0;
               prof_wait += pt1 - pt0;
               uint8_t* st = stage_base + stage * Cfg::kStageBytes;
-              mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+              mbar_arrive_expect_tx(&full_bar[stage], stage_tx);
               const int c0 = cb * Cfg::kKB;
-              tma_load_im2col_4d(st, &tmA, &full_bar[stage], c0, w_base, h_base, img, off_w, off_h);
+              if (p.lowc) {
+                // window copy: (64 elements, all quads of a row, `ohs` rows at the conv stride, image)
+                tma_load_4d(st, &tmA, &full_bar[stage], 0, 0, h_base + r * p.dil_h, img);
+              } else {
+                tma_load_im2col_4d(st, &tmA, &full_bar[stage], c0, w_base, h_base, img, off_w, off_h);
+              }
               if constexpr (Cfg::kSplit) {
                 tma_load_im2col_4d(st + Cfg::kABytes, &tmA2, &full_bar[stage], c0, w_base, h_base,
                                    img, off_w, off_h);
@@ -291,8 +306,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         __syncwarp();
         for (int j = lane; j < BN; j += 32) {
           const int col = n0 + j;
-          s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col]) : 1.0f;
-          s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col]) : 0.0f;
+          s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col % p.k_real]) : 1.0f;
+          s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col % p.k_real]) : 0.0f;
         }
         __syncwarp();
         staged_n_tile = n_tile;
@@ -316,58 +331,24 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         y_off = img * p.y_sn + oh * p.y_sh + ow * p.y_sw;
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * BN;
+      // Where this warp's 32 rows go in y seen as (channel, row, image): the whole
+      // output is one "image" outside low-channel mode.
+      int st_row, st_img, st_rows;
+      if (p.lowc) {
+        st_img = m_tile / p.tiles_per_image;
+        st_row = (m_tile - st_img * p.tiles_per_image) * p.rows_per_tile + ew * 32;
+        st_rows = p.rows_per_tile - ew * 32;
+      } else {
+        st_img = 0;
+        st_row = m_tile * kBM + ew * 32;
+        st_rows = 32;
+      }
       if (p.tma_store) {
-        // Channel-contiguous y: each warp stages 32 pixels x 128 bytes in shared
-        // memory (128-byte swizzle, so the 16-byte row pieces of neighbouring
-        // lanes land in different banks) and one lane hands the box to a TMA
-        // store, which writes whole rows and clips the ragged edges of M and K.
-        constexpr int kPerStore = Cfg::kOutCols;           // 64 (16-bit) or 32 (fp32) channels
-        constexpr int kLoads = kPerStore / 32;             // tcgen05.ld x32 per store
-        uint8_t* my_out = out_stage + (warp - 2) * 32 * kRowBytes;
-#pragma unroll 1
-        for (int g = 0; g < BN / kPerStore; ++g) {
-          const int col0 = n0 + g * kPerStore;
-          if (col0 >= p.Kout) break;  // uniform across the warp
-          uint32_t raw[kLoads][32];
-#pragma unroll
-          for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + g * kPerStore + l * 32, raw[l]);
-          tmem_ld_wait();
-          if (lane == 0) bulk_wait_group_read0();  // the previous box has left shared memory
-          __syncwarp();
-#pragma unroll
-          for (int l = 0; l < kLoads; ++l) {
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float a = __uint_as_float(raw[l][j]);
-              a = fmaf(a, s_scale[g * kPerStore + l * 32 + j], s_bias[g * kPerStore + l * 32 + j]);
-              if (p.relu) a = (a < 0.0f) ? 0.0f : a;  // keeps NaN, like torch.relu
-              v[j] = a;
-            }
-            constexpr int kPieces = 32 * int(sizeof(T)) / 16;  // 16-byte pieces per 32 values
-#pragma unroll
-            for (int q = 0; q < kPieces; ++q) {
-              uint4 piece;
-              if constexpr (std::is_same<T, float>::value) {
-                piece = make_uint4(__float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]),
-                                   __float_as_uint(v[4 * q + 2]), __float_as_uint(v[4 * q + 3]));
-              } else {
-                piece.x = pack2(from_f32<T>(v[8 * q + 0]), from_f32<T>(v[8 * q + 1]));
-                piece.y = pack2(from_f32<T>(v[8 * q + 2]), from_f32<T>(v[8 * q + 3]));
-                piece.z = pack2(from_f32<T>(v[8 * q + 4]), from_f32<T>(v[8 * q + 5]));
-                piece.w = pack2(from_f32<T>(v[8 * q + 6]), from_f32<T>(v[8 * q + 7]));
-              }
-              const int chunk16 = l * kPieces + q;  // 0..7 within the 128-byte row
-              *reinterpret_cast<uint4*>(my_out + lane * kRowBytes + ((chunk16 ^ (lane & 7)) << 4)) = piece;
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmY, my_out, col0, m_tile * kBM + ew * 32);
-            bulk_commit_group();
-          }
-        }
+        // a tile's last warp may own fewer than 32 valid rows: tmA2 then holds a second
+        // output map whose box is exactly that short (low-channel mode, 16-bit only)
+        epilogue_store_tile<T, BN>(t_row, n0, p.Kout, p.relu, s_scale, s_bias,
+                                   out_stage + (warp - 2) * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
+                                   st_img, st_rows);
       } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < BN / 32; ++chunk) {

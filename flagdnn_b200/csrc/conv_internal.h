@@ -29,6 +29,15 @@ struct IgemmParams {
   int relu;
   int vec_store;         // 1: y is channel-contiguous and 16-byte aligned per pixel
   int tma_store;         // 1: y is dense NHWC; the epilogue writes it through the tmY tensor map
+  // Low-channel mode (C <= 4): one GEMM row is a quad of 4 output pixels of one
+  // image row, its reduction operand a 16-pixel window of the repacked input;
+  // a tile is `ohs` output rows x OW/4 quads and never crosses an image.
+  int lowc;              // 1: low-channel mode
+  int rows_per_tile;     // valid GEMM rows per tile (128 outside low-channel mode)
+  int tiles_per_image;   // low-channel mode: ceil(OH / ohs)
+  int ohs;               // low-channel mode: output rows per tile
+  int a_tx_bytes;        // bytes one activation copy delivers (rows_per_tile * 128 in low-channel mode)
+  int k_real;            // length of bias / scale (GEMM column j uses entry j % k_real)
   uint32_t* status;
   long long* prof;       // optional: 16 cycle counters written by CTA 0 (nullptr = off)
 };
@@ -48,8 +57,8 @@ cudaError_t igemm_prepare_device();
 // CTA-pair variant (conv_igemm_pair_sm100.cu): 16-bit types, 256 x 256 pair
 // tiles, TMA-store epilogue only (p.tma_store must be set).  `grid` must be even.
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                              const CUtensorMap& tmY, const IgemmParams& p, int grid,
-                              cudaStream_t stream);
+                              const CUtensorMap& tmY, const CUtensorMap& tmY2, const IgemmParams& p,
+                              int grid, cudaStream_t stream);
 cudaError_t igemm_pair_prepare_device();
 int igemm_pair_smem_bytes();
 int igemm_pair_stages();
@@ -75,6 +84,15 @@ cudaError_t launch_direct(int dtype, const DirectParams& p, cudaStream_t stream)
 cudaError_t launch_repack_x(int dtype, const void* x, const long long x_s[4], int N, int C, int H,
                             int W, int c_pad, void* dst, long long plane_elems,
                             cudaStream_t stream);
+// Low-channel relayouts (C <= 4, 16-bit types):
+// x -> [N][H][w_pad][4]: `pad_left` zero pixels, the image row, zeros up to w_pad; channel 4 is zero.
+cudaError_t launch_repack_x_lowc(int dtype, const void* x, const long long x_s[4], int N, int C, int H,
+                                 int W, int pad_left, int w_pad, void* dst, cudaStream_t stream);
+// w -> [4*K][R][64]: row (q, k) holds filter k shifted to the q-th output pixel of a quad:
+// element (j*4 + c) of tap row r is w[k][c][r][j - stride_w*q - shift] (zero outside the filter);
+// `shift` = stored left padding minus the convolution's own left padding.
+cudaError_t launch_pack_w_lowc(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
+                               int S, int stride_w, int shift, void* dst, cudaStream_t stream);
 // w[K,C,R,S] (any strides) -> dense [K,R,S,c_pad]; f32 split like x.
 cudaError_t launch_pack_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
                           int S, int c_pad, void* dst, long long plane_elems, cudaStream_t stream);

@@ -114,6 +114,93 @@ pack_w_kernel(const T* __restrict__ w, long long sk, long long sc, long long sr,
   }
 }
 
+// Low-channel input relayout: one thread per stored pixel (4 channels = 8 bytes).
+template <typename T>
+__global__ void __launch_bounds__(256)
+repack_x_lowc_kernel(const T* __restrict__ x, long long sn, long long sc, long long sh, long long sw,
+                     int N, int C, int H, int W, int pad_left, int w_pad, T* __restrict__ dst) {
+  const long long total = (long long)N * H * w_pad;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long t = i;
+    const int j = int(t % w_pad); t /= w_pad;
+    const int h = int(t % H); t /= H;
+    const int n = int(t);
+    const int w = j - pad_left;
+    T v[4] = {T(0.0f), T(0.0f), T(0.0f), T(0.0f)};
+    if (w >= 0 && w < W) {
+      const T* src = x + n * sn + h * sh + w * sw;
+      for (int c = 0; c < C; ++c) v[c] = src[c * sc];
+    }
+    uint2 packed;
+    packed.x = uint32_t(*reinterpret_cast<uint16_t*>(&v[0])) | (uint32_t(*reinterpret_cast<uint16_t*>(&v[1])) << 16);
+    packed.y = uint32_t(*reinterpret_cast<uint16_t*>(&v[2])) | (uint32_t(*reinterpret_cast<uint16_t*>(&v[3])) << 16);
+    reinterpret_cast<uint2*>(dst)[i] = packed;
+  }
+}
+
+// Fast path of the low-channel relayout for a dense 3-channel NHWC source with
+// 16-byte aligned rows and W % 8 == 0: one thread turns 8 pixels (48 bytes, three
+// aligned 16-byte loads) into 8 four-channel pixels (64 bytes, four aligned stores).
+__global__ void __launch_bounds__(256)
+repack_x_lowc_c3_kernel(const uint16_t* __restrict__ x, long long sn, long long sh, int N, int H, int W,
+                        int pad_left, int w_pad, uint16_t* __restrict__ dst) {
+  const int w8s = W / 8;
+  const long long total = (long long)N * H * w8s;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long t = i;
+    const int w8 = int(t % w8s); t /= w8s;
+    const int h = int(t % H); t /= H;
+    const int n = int(t);
+    const uint4* src = reinterpret_cast<const uint4*>(x + n * sn + h * sh + w8 * 24);
+    uint32_t in[12];
+    const uint4 a = src[0], b = src[1], c = src[2];
+    in[0] = a.x; in[1] = a.y; in[2] = a.z; in[3] = a.w;
+    in[4] = b.x; in[5] = b.y; in[6] = b.z; in[7] = b.w;
+    in[8] = c.x; in[9] = c.y; in[10] = c.z; in[11] = c.w;
+    auto get16 = [&in](int e) -> uint32_t { return (in[e >> 1] >> (16 * (e & 1))) & 0xffffu; };
+    uint16_t* row = dst + (((long long)n * H + h) * w_pad) * 4;
+    uint4* out = reinterpret_cast<uint4*>(row + (long long)(pad_left + 8 * w8) * 4);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {  // two pixels per 16-byte store
+      const int p0 = 2 * q, p1 = 2 * q + 1;
+      uint4 v;
+      v.x = get16(3 * p0) | (get16(3 * p0 + 1) << 16);
+      v.y = get16(3 * p0 + 2);
+      v.z = get16(3 * p1) | (get16(3 * p1 + 1) << 16);
+      v.w = get16(3 * p1 + 2);
+      out[q] = v;
+    }
+    if (w8 == 0) {
+      for (int j = 0; j < pad_left; ++j) reinterpret_cast<uint2*>(row)[j] = make_uint2(0u, 0u);
+    }
+    if (w8 == w8s - 1) {
+      for (int j = pad_left + W; j < w_pad; ++j) reinterpret_cast<uint2*>(row)[j] = make_uint2(0u, 0u);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+pack_w_lowc_kernel(const T* __restrict__ w, long long sk, long long sc, long long sr, long long ss, int K,
+                   int C, int R, int S, int stride_w, int shift, T* __restrict__ dst) {
+  const long long total = 4LL * K * R * 64;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long t = i;
+    const int e = int(t % 64); t /= 64;
+    const int r = int(t % R); t /= R;
+    const int row = int(t);          // q * K + k
+    const int q = row / K, k = row - q * K;
+    const int j = e >> 2, c = e & 3;  // window pixel, channel
+    const int s = j - stride_w * q - shift;  // shift: stored left padding beyond the conv's own
+    T v = T(0.0f);
+    if (c < C && s >= 0 && s < S) v = w[k * sk + c * sc + r * sr + s * ss];
+    dst[i] = v;
+  }
+}
+
 int grid_for(long long work_items, int per_block) {
   long long blocks = (work_items + per_block - 1) / per_block;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
@@ -157,6 +244,50 @@ cudaError_t launch_repack_x(int dtype, const void* x, const long long x_s[4], in
     case FDNN_F32: return repack_x_t<float>(x, x_s, N, C, H, W, c_pad, dst, plane_elems, stream);
     default: return cudaErrorInvalidValue;
   }
+}
+
+cudaError_t launch_repack_x_lowc(int dtype, const void* x, const long long x_s[4], int N, int C, int H,
+                                 int W, int pad_left, int w_pad, void* dst, cudaStream_t stream) {
+  const bool fast = (dtype == FDNN_F16 || dtype == FDNN_BF16) && C == 3 && x_s[1] == 1 && x_s[3] == 3 &&
+                    W % 8 == 0 && pad_left % 2 == 0 && x_s[2] % 8 == 0 && (N <= 1 || x_s[0] % 8 == 0) &&
+                    (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+  if (fast) {
+    const long long items = (long long)N * H * (W / 8);
+    repack_x_lowc_c3_kernel<<<grid_for(items, 256), 256, 0, stream>>>(
+        static_cast<const uint16_t*>(x), x_s[0], x_s[2], N, H, W, pad_left, w_pad, static_cast<uint16_t*>(dst));
+    return cudaGetLastError();
+  }
+  const long long total = (long long)N * H * w_pad;
+  const int grid = grid_for(total, 256);
+  if (dtype == FDNN_F16) {
+    repack_x_lowc_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(x), x_s[0], x_s[1], x_s[2],
+                                                           x_s[3], N, C, H, W, pad_left, w_pad,
+                                                           static_cast<__half*>(dst));
+  } else if (dtype == FDNN_BF16) {
+    repack_x_lowc_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), x_s[0], x_s[1], x_s[2], x_s[3], N, C, H, W, pad_left, w_pad,
+        static_cast<__nv_bfloat16*>(dst));
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_w_lowc(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
+                               int S, int stride_w, int shift, void* dst, cudaStream_t stream) {
+  const long long total = 4LL * K * R * 64;
+  const int grid = grid_for(total, 256);
+  if (dtype == FDNN_F16) {
+    pack_w_lowc_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(w), w_s[0], w_s[1], w_s[2],
+                                                         w_s[3], K, C, R, S, stride_w, shift, static_cast<__half*>(dst));
+  } else if (dtype == FDNN_BF16) {
+    pack_w_lowc_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(w), w_s[0], w_s[1], w_s[2], w_s[3], K, C, R, S, stride_w, shift,
+        static_cast<__nv_bfloat16*>(dst));
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
 }
 
 cudaError_t launch_pack_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R,

@@ -51,7 +51,7 @@ def test_library_exports_every_declared_symbol(native_lib):
 def test_struct_layout_matches_header():
     # 18 int32 + 3 x 4 int64
     assert ctypes.sizeof(nat.ConvDesc) == 18 * 4 + 12 * 8
-    assert ctypes.sizeof(nat.ConvPlan) == 13 * 4 + 4 + 3 * 8 + 2 * 8
+    assert ctypes.sizeof(nat.ConvPlan) == 14 * 4 + 3 * 8 + 2 * 8
 
 
 def test_query_plans_headline_configs(native_lib):
@@ -77,10 +77,17 @@ def test_query_plans_headline_configs(native_lib):
     assert plan.algo == nat.ALGO_IGEMM and plan.x_repacked == 1 and plan.w_packed == 1 and plan.launches == 2
     assert plan.workspace_bytes == 2 * 4 * 56 * 56 * 64 * 4
     assert plan.packed_weight_bytes == 2 * 64 * 9 * 64 * 4
-    # stem: 3 channels padded to 8
+    # stem: low-channel path — 3 channels stored as 4, pixel quads as GEMM rows (4 x 64 = 256 columns)
     d = _desc(n=256, c=3, h=224, w=224, k=64, r=7, s=7, stride=2, pad=3)
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
-    assert plan.c_padded == 8 and plan.x_repacked == 1 and plan.oh == 112
+    assert plan.low_channel == 1 and plan.c_padded == 4 and plan.x_repacked == 1 and plan.w_packed == 1
+    assert plan.oh == 112 and plan.tile_n == 256 and plan.launches == 2
+    assert plan.workspace_bytes == 256 * 224 * 232 * 4 * 2      # rows padded to 232 stored pixels
+    assert plan.packed_weight_bytes == 256 * 7 * 64 * 2
+    # the same layer with an NCHW output cannot use it and falls back to 8-channel padding
+    d = _desc(n=256, c=3, h=224, w=224, k=64, r=7, s=7, stride=2, pad=3, channels_last=False)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert plan.low_channel == 0 and plan.c_padded == 8
 
 
 def test_query_routes_unsupported_geometry_to_direct(native_lib):

@@ -231,6 +231,44 @@ def test_pair_kernel_matches_single_cta_kernel_bitwise(fd, shape):
     _check(outs["pair"], oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, 1, relu=True), "bfloat16")
 
 
+LOWC = [
+    # n, c, h, w, k, r, s, stride, pad, dtype
+    (2, 3, 32, 32, 64, 7, 7, 2, 3, "bfloat16"),            # the stem at a small image
+    (3, 3, 40, 24, 16, 3, 3, 1, 1, "bfloat16"),            # stride 1, 4*K = 64 GEMM columns
+    (2, 4, 19, 64, 40, 3, 5, (1, 2), (1, 2), "float16"),   # 4 channels, rectangular filter, odd left padding
+    (1, 2, 9, 16, 8, 1, 1, 1, 0, "bfloat16"),              # 1x1 filter, one tile
+    (2, 2, 33, 48, 32, 5, 4, 2, (2, 2), "float16"),        # 25 output columns: not whole quads, generic path
+    (2, 1, 33, 52, 32, 5, 4, 2, (2, 2), "float16"),        # one channel (torch then reports an NCHW-like view)
+    (1, 3, 70, 520, 8, 3, 3, (3, 1), 1, "bfloat16"),       # 130 quads per row: more than one tile may hold
+]
+
+
+@pytest.mark.parametrize("algo", ["igemm", "pair"])
+@pytest.mark.parametrize("case", LOWC, ids=[f"c{c[1]}_{c[5]}x{c[6]}_k{c[4]}" for c in LOWC])
+def test_low_channel_path_matches_oracle(fd, case, algo):
+    """C <= 4 with channels-last tensors: pixel quads become GEMM rows over 16-pixel input windows."""
+    n, c, h, w_, k, r, s_, stride, pad, dtype_name = case
+    dtype = DTYPES[dtype_name]
+    x = _rand((n, c, h, w_), 60, dist="uniform").to(dtype).cuda().contiguous(memory_format=torch.channels_last)
+    w = _rand((k, c, r, s_), 61, std=(c * r * s_) ** -0.5).to(dtype).cuda().contiguous(memory_format=torch.channels_last)
+    b = _rand((k,), 62, std=0.1).to(dtype).cuda()
+    sc = (torch.rand(k, generator=torch.Generator().manual_seed(63)) + 0.5).to(dtype).cuda()
+    channels_last_out = x.stride(1) == 1  # the output follows the input's layout
+    if algo == "pair" and not channels_last_out:
+        pytest.skip("the CTA-pair kernel writes channels-last outputs only")
+    fd.set_algo(algo)
+    try:
+        plan = fd.conv2d_plan(x, w, stride=stride, padding=pad)
+        got = fd.fused_conv2d_bias_relu(x, w, b, stride=stride, padding=pad, scale=sc)
+        again = fd.fused_conv2d_bias_relu(x, w, b, stride=stride, padding=pad, scale=sc)
+    finally:
+        fd.set_algo("auto")
+    expect_lowc = channels_last_out and (got.shape[3] % 4 == 0) and got.shape[3] // 4 <= 128
+    assert plan["low_channel"] == int(expect_lowc)
+    assert torch.equal(got, again)
+    _check(got, oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, 1, scale=sc, relu=True), dtype_name)
+
+
 def test_scaled_graph_folds_into_one_node(fd):
     x = _rand((2, 16, 8, 8), 20).to(torch.float16).cuda().contiguous(memory_format=torch.channels_last)
     w = _rand((24, 16, 3, 3), 21, std=0.08).to(torch.float16).cuda()

@@ -152,9 +152,21 @@ class ClockSampler:
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def use_all_host_threads(torch):
+    """torchrun pins OMP_NUM_THREADS=1; the CPU legs are meant to use every core the process may run on."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, cores))
+    return torch.get_num_threads()
+
+
 def cpu_baseline_leg(wl, torch, sample_n, min_seconds=2.0):
     """The reference's CPU path timed on the host cores; test-infrastructure code (oracle/) as the checker's timer."""
     import oracle
+
+    use_all_host_threads(torch)
 
     x, w, b = make_inputs(wl, sample_n, 0, "cpu", torch)
     relu = wl["dtype"] != "float32"
@@ -179,6 +191,7 @@ def run_reference(args):
         return
     import torch
 
+    use_all_host_threads(torch)
     wl = WORKLOADS[args.workload]
     sample_n = min(wl["n"], 32)
     nums = workload_numbers(dict(wl, n=sample_n))
@@ -388,10 +401,219 @@ def _report(args, torch, rank, world, wl, nums, peaks, peak_src, ms_per_step, va
             "pct_of_bf16_peak": 100.0 * (value / world) / peaks["bf16_tflops"],
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e,
-            "gpu_launches": steps * launches_per_step,
+            "gpu_launches": steps * launches_per_step * world,
             "clocks": clocks.summary(), "device_status_word": status_word,
         }
         print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ ResNet-50 conv stack (workload c5)
+def stack_roofline_seconds(layers, batch, peaks):
+    """Sum over layers of max(flops / tensor peak, bytes / HBM peak): the mixed roofline of the stack."""
+    return sum(max(l.flops(batch) / (peaks["bf16_tflops"] * 1e12), l.bytes(batch) / (peaks["hbm_gbs"] * 1e9))
+               for l in layers)
+
+
+def cpu_stack_leg(torch, images, repeats=2):
+    """The reference's CPU path (F.conv2d -> scale -> bias -> relu in bf16) over all 53 layers of a small batch."""
+    import oracle
+    from flagdnn_b200.convstack import make_layer_params, resnet50_conv_layers, stack_totals
+
+    use_all_host_threads(torch)
+    layers = resnet50_conv_layers()
+    params = [make_layer_params(l, i, "cpu") for i, l in enumerate(layers)]
+    g = torch.Generator().manual_seed(0)
+    inputs = [torch.randn(images, l.cin, l.hw_in, l.hw_in, generator=g).to(torch.bfloat16)
+              .contiguous(memory_format=torch.channels_last) for l in layers]
+
+    def once():
+        for l, (w, sc, b), x in zip(layers, params, inputs):
+            oracle.conv2d_torch_cpu(x, w, b, l.stride, l.pad, 1, 1, scale=sc, relu=l.relu, compute_dtype=torch.bfloat16)
+
+    once()
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        once()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return stack_totals(layers, images)["flops"] / med / 1e12, med
+
+
+def run_stack(args):
+    """All 53 ResNet-50 convolutions (scale + bias + ReLU fused), batch 1024 split over the ranks (strong scaling).
+    Every layer runs on an independently generated N(0,1) input of its own shape, so only convolutions are timed."""
+    import torch
+
+    import flagdnn_b200 as fd
+    from flagdnn_b200.convstack import make_layer_params, resnet50_conv_layers, run_layer, stack_totals
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    device = torch.device("cuda", local_rank)
+    from flagdnn_b200.sharding import batch_slice
+
+    total_batch = args.batch
+    b0, b1 = batch_slice(total_batch, rank, world)
+    batch = b1 - b0
+    layers = resnet50_conv_layers()
+    params = [make_layer_params(l, i, device) for i, l in enumerate(layers)]
+    peaks, peak_src = load_peaks()
+    # one shared pool of random activations, viewed per layer as its NHWC input
+    max_in = max(batch * l.cin * l.hw_in ** 2 for l in layers)
+    g = torch.Generator(device=device).manual_seed(1000 + rank)
+    pool = torch.randn(max_in, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    inputs = [pool[: batch * l.cin * l.hw_in ** 2].view(batch, l.hw_in, l.hw_in, l.cin).permute(0, 3, 1, 2)
+              for l in layers]
+
+    def step():
+        out = None
+        for l, prm, x in zip(layers, params, inputs):
+            out = run_layer(l, x, prm)
+        return out
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        step()
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            last = step()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps = max(1, args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        barrier()
+        with ClockSampler(local_rank) as clocks:
+            e0.record(stream)
+            for _ in range(steps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        barrier()
+    elapsed_ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / steps
+    totals = stack_totals(layers, total_batch)
+    value = totals["flops"] / (ms_per_step * 1e-3) / 1e12
+
+    # per-shape times (rank 0, outside the timed region) for the breakdown
+    shape_ms = {}
+    if rank == 0:
+        for l, prm, x in zip(layers, params, inputs):
+            if l.shape_key in shape_ms:
+                continue
+            run_layer(l, x, prm)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(3):
+                run_layer(l, x, prm)
+            b.record()
+            torch.cuda.synchronize()
+            shape_ms[l.shape_key] = (l, a.elapsed_time(b) / 3)
+
+    # end to end: images from pinned host memory in, last activation back out, all 53 layers in between
+    x_host = inputs[0].contiguous(memory_format=torch.channels_last).cpu().pin_memory()
+    x_dev = torch.empty_like(x_host, device=device)
+    y_host = torch.empty(last.shape, dtype=last.dtype).contiguous(memory_format=torch.channels_last).pin_memory()
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        out = None
+        for l, prm, x in zip(layers, params, [x_dev] + inputs[1:]):
+            out = run_layer(l, x, prm)
+        y_host.copy_(out, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e2e_steps = 3
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    status_word = fd.device_status()
+
+    if rank == 0:
+        roof_s = stack_roofline_seconds(layers, batch, peaks)
+        launches = sum(fd.conv2d_plan(x, p_[0], stride=l.stride, padding=l.pad)["launches"]
+                       for l, p_, x in zip(layers, params, inputs))
+        slow = sorted(shape_ms.values(), key=lambda t: -t[1])[:6]
+        cpu_value, cpu_s = cpu_stack_leg(torch, images=2)
+        line = {
+            "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bfloat16", "data": "synthetic",
+            "config": {"workload": "c5", "description": "ResNet-50 forward conv stack, 53 convs with folded scale+bias(+ReLU), "
+                       f"bf16 NHWC 224x224, batch {total_batch} sharded along N", "per_gpu_batch": batch,
+                       "inputs": "each layer reads independently generated N(0,1) activations of its shape; "
+                                 "no pooling / residual glue in the timed region",
+                       "launch": "cuda_graph_replay", "l2": "activations of every layer exceed the 126 MiB L2",
+                       "parallelism": f"batch-sharded replicas x{world}, no collective"},
+            "pct_of_bf16_peak": 100.0 * (value / world) / peaks["bf16_tflops"],
+            "roofline": {"bound": "mixed", "achieved": roof_s * 1e3, "peak": ms_per_step, "unit": "ms",
+                         "frac": roof_s * 1e3 / ms_per_step, "traffic": None, "peak_source": f"of {peak_src}",
+                         "note": "achieved = sum over layers of max(flops/tensor peak, bytes/HBM peak) for this rank's "
+                                 "batch; peak = measured ms per step; frac = roofline time / measured time",
+                         "slowest_shapes_ms": [{"layer": l.name, "cin": l.cin, "hw": l.hw_in, "cout": l.cout, "k": l.k,
+                                                "stride": l.stride, "ms": ms,
+                                                "tflops": l.flops(batch) / ms / 1e9} for l, ms in slow]},
+            "cpu_baseline": {"value": cpu_value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": f"2 of {total_batch} images through all 53 layers, F.conv2d*scale+bias+relu in "
+                                       f"bf16 on CPU, median of 2 ({cpu_s:.2f} s per pass)"},
+            "e2e": {"value": totals["flops"] / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms},
+            "gpu_launches": steps * launches * world, "clocks": clocks.summary(), "device_status_word": status_word,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_stack_reference(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+
+    value, seconds = cpu_stack_leg(torch, images=2, repeats=max(1, min(args.steps, 3)))
+    sample = ("each step = 2 images through all 53 ResNet-50 convolutions, F.conv2d*scale+bias+relu in bf16 on the host CPU")
+    print(json.dumps({
+        "impl": "reference", "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": max(1, min(args.steps, 3)), "warmup": 1, "ms_per_step": seconds * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bfloat16", "data": "synthetic",
+        "config": {"workload": "c5", "sample_images": 2},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 
 
 def main():
@@ -400,13 +622,21 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--batch", type=int, default=1024, help="total batch of the c5 workload (split over the ranks)")
     ap.add_argument("--eager", action="store_true",
                     help="launch every step through the API instead of replaying a CUDA graph (for profilers)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (short runs under a profiler)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "c5":
+        if args.impl == "reference":
+            run_stack_reference(args)
+        else:
+            if args.steps == 2000:
+                args.steps = 20  # a pass over the whole stack takes milliseconds, not microseconds
+            run_stack(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -36,15 +36,17 @@ __device__ __forceinline__ uint32_t round_pack2<__nv_bfloat16>(float a, float b)
 // t_row     tensor-memory address of this warp's lane quarter, first column of the tile
 // n0        first GEMM column of the tile; kout: number of valid GEMM columns overall
 // s_scale / s_bias  this warp's fp32 copies for columns n0 .. n0+BN-1
-// my_out    this warp's 4 KB staging buffer (1024-byte aligned)
+// my_out    this warp's two 4 KB staging buffers (1024-byte aligned, used in rotation so that
+//           a box can still be leaving through the TMA unit while the next one is staged)
 // tm_full / tm_tail  output maps with a 32-row box and a box of the tile's ragged last rows
 // st_row, st_img     y coordinates (row, image) of the warp's first row; st_rows: valid rows (<= 0: none)
+// store_seq          running count of this warp's staged boxes (selects the staging buffer)
 template <typename T, int BN>
 __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int relu,
                                                     const float* s_scale, const float* s_bias,
                                                     uint8_t* my_out, int lane, const CUtensorMap* tm_full,
                                                     const CUtensorMap* tm_tail, int st_row, int st_img,
-                                                    int st_rows) {
+                                                    int st_rows, uint32_t& store_seq) {
   constexpr int kPerStore = 128 / int(sizeof(T));  // channels per staged row: 64 (16-bit) or 32 (fp32)
   constexpr int kLoads = kPerStore / 32;
   int groups = (kout - n0 + kPerStore - 1) / kPerStore;
@@ -59,20 +61,29 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
     uint32_t row[32];  // the 128 bytes this lane contributes
 #pragma unroll
     for (int l = 0; l < kLoads; ++l) {
+      const float4* sc4 = reinterpret_cast<const float4*>(s_scale + g * kPerStore + l * 32);
+      const float4* bi4 = reinterpret_cast<const float4*>(s_bias + g * kPerStore + l * 32);
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const int c = g * kPerStore + l * 32 + j;
-        float a = fmaf(__uint_as_float(raw[l][j]), s_scale[c], s_bias[c]);
-        float b = fmaf(__uint_as_float(raw[l][j + 1]), s_scale[c + 1], s_bias[c + 1]);
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 sc = sc4[j4], bi = bi4[j4];
+        float v0 = fmaf(__uint_as_float(raw[l][4 * j4 + 0]), sc.x, bi.x);
+        float v1 = fmaf(__uint_as_float(raw[l][4 * j4 + 1]), sc.y, bi.y);
+        float v2 = fmaf(__uint_as_float(raw[l][4 * j4 + 2]), sc.z, bi.z);
+        float v3 = fmaf(__uint_as_float(raw[l][4 * j4 + 3]), sc.w, bi.w);
         if (relu) {
-          a = relu_keep_nan(a);
-          b = relu_keep_nan(b);
+          v0 = relu_keep_nan(v0);
+          v1 = relu_keep_nan(v1);
+          v2 = relu_keep_nan(v2);
+          v3 = relu_keep_nan(v3);
         }
         if constexpr (std::is_same<T, float>::value) {
-          row[j] = __float_as_uint(a);
-          row[j + 1] = __float_as_uint(b);
+          row[4 * j4 + 0] = __float_as_uint(v0);
+          row[4 * j4 + 1] = __float_as_uint(v1);
+          row[4 * j4 + 2] = __float_as_uint(v2);
+          row[4 * j4 + 3] = __float_as_uint(v3);
         } else {
-          row[l * 16 + j / 2] = round_pack2<T>(a, b);
+          row[l * 16 + 2 * j4 + 0] = round_pack2<T>(v0, v1);
+          row[l * 16 + 2 * j4 + 1] = round_pack2<T>(v2, v3);
         }
       }
     }
@@ -81,18 +92,21 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
 #pragma unroll
       for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + (g + 1) * kPerStore + l * 32, raw[l]);
     }
-    if (lane == 0) bulk_wait_group_read0();  // the previous box has left the staging buffer
+    uint8_t* buf = my_out + (store_seq & 1u) * (32 * 128);  // alternates across groups AND tiles
+    ++store_seq;
+    if (lane == 0) bulk_wait_group_read1();  // the box staged two groups ago has left this buffer
     __syncwarp();
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       // 128-byte swizzle: the 16-byte pieces of neighbouring rows land in different banks
-      *reinterpret_cast<uint4*>(my_out + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+      *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) << 4)) =
           make_uint4(row[4 * q], row[4 * q + 1], row[4 * q + 2], row[4 * q + 3]);
     }
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0 && st_rows > 0) {
-      tma_store_3d(st_rows >= 32 ? tm_full : tm_tail, my_out, n0 + g * kPerStore, st_row, st_img);
+    if (lane == 0) {
+      // committed even when empty so that "all but the latest group" always means the other buffer
+      if (st_rows > 0) tma_store_3d(st_rows >= 32 ? tm_full : tm_tail, buf, n0 + g * kPerStore, st_row, st_img);
       bulk_commit_group();
     }
   }

@@ -39,9 +39,9 @@ constexpr int kKB = 64;              // 16-bit reduction elements per stage
 constexpr int kABytes = kRows * kRowB;
 constexpr int kBBytes = kHalfN * kRowB;
 constexpr int kStageBytes = kABytes + kBBytes;      // 32 KB per CTA per stage
-constexpr int kStages = 6;                           // 192 KB
+constexpr int kStages = 5;                           // 160 KB
 constexpr int kThreadsPair = 192;
-constexpr int kOutBytes = 4 * 32 * kRowB;            // per-warp TMA-store staging
+constexpr int kOutBytes = 4 * 2 * 32 * kRowB;        // two TMA-store staging buffers per warp
 constexpr int kEpiBytes = 4 * 2 * kPairN * int(sizeof(float));
 constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
 constexpr int kSmemPair = kStages * kStageBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
@@ -227,9 +227,10 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     float* s_bias = s_scale + kPairN;
     const T* g_bias = static_cast<const T*>(p.bias);
     const T* g_scale = static_cast<const T*>(p.scale);
-    uint8_t* my_out = out_stage + (warp - 2) * 32 * kRowB;
+    uint8_t* my_out = out_stage + (warp - 2) * 2 * 32 * kRowB;
     const uint32_t tempty_leader = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     uint32_t tcount = 0;
+    uint32_t store_seq = 0;
     int staged_n_tile = -1;
     for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++tcount) {
       const int m_pair = tile / n_tiles;
@@ -264,7 +265,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN;
       epilogue_store_tile<T, kPairN>(t_row, n0, p.Kout, p.relu, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
-                                     st_row, st_img, st_rows);
+                                     st_row, st_img, st_rows, store_seq);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }

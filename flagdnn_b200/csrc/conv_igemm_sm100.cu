@@ -48,12 +48,13 @@ struct TileCfg {
   static constexpr int kABytes = kBM * kRowBytes;
   static constexpr int kBBytes = BN * kRowBytes;
   static constexpr int kStageBytes = (kSplit ? 2 : 1) * (kABytes + kBBytes);
-  static constexpr int kStages = (192 * 1024) / kStageBytes;  // 4 x 48 KB for the widest 16-bit tile
+  // operand ring: what is left of the 227 KB after the output staging; 3 x 48 KB for the widest 16-bit tile
+  static constexpr int kStages = (176 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128, 256 or 512
   // per-warp output staging (32 rows x 128 bytes, swizzled, for the TMA store),
   // per-warp scale and bias staging, then barriers and bookkeeping words
   static constexpr int kOutCols = kRowBytes / int(sizeof(T));  // output channels per TMA store
-  static constexpr int kOutBytes = kEpiWarps * 32 * kRowBytes;
+  static constexpr int kOutBytes = kEpiWarps * 2 * 32 * kRowBytes;  // two 4 KB buffers per warp
   static constexpr int kEpiBytes = kEpiWarps * 2 * BN * int(sizeof(float));
   static constexpr int kBarBytes = (2 * kStages + 4 + 1) * 8 + 16;
   static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
@@ -293,6 +294,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const T* g_scale = static_cast<const T*>(p.scale);
     T* y = static_cast<T*>(p.y);
     uint32_t tcount = 0;
+    uint32_t store_seq = 0;
     int staged_n_tile = -1;
     long long prof_ewait = 0, prof_t0 = p.prof ? clock64() : 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
@@ -347,8 +349,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // a tile's last warp may own fewer than 32 valid rows: tmA2 then holds a second
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
         epilogue_store_tile<T, BN>(t_row, n0, p.Kout, p.relu, s_scale, s_bias,
-                                   out_stage + (warp - 2) * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
-                                   st_img, st_rows);
+                                   out_stage + (warp - 2) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
+                                   st_img, st_rows, store_seq);
       } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < BN / 32; ++chunk) {

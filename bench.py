@@ -48,7 +48,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the implicit-GEMM
 # kernel, from the ncu captures summarised under profiles/ (None = not captured).
-NCU_TRAFFIC_BYTES = {"c3": 26.94e6, "c2": 495.3e6, "c4": None, "c1": None}
+NCU_TRAFFIC_BYTES = {"c3": 26.97e6, "c2": 495.3e6, "c4": 459.1e6, "c1": None}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -382,7 +382,7 @@ def _report(args, torch, rank, world, wl, nums, peaks, peak_src, ms_per_step, va
             extra = {}
         roofline = {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                     "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peak_src}",
-                    "kernel": "conv_igemm_kernel", "algorithmic_flops_per_launch": nums["flops"],
+                    "kernel": "conv_igemm_pair_kernel" if plan["algo"] == 3 else "conv_igemm_kernel", "algorithmic_flops_per_launch": nums["flops"],
                     "algorithmic_bytes_per_launch": nums["bytes"], **extra}
         cpu = None if args.kernel_only else cpu_baseline_leg(wl, torch, sample_n=min(wl["n"], 32))
         e2e = None if e2e_value is None else {

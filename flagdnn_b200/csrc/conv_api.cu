@@ -499,6 +499,7 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
   p.status = g_status_ptr[dev];
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
   if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
+    p.b_resident = (n_gemm <= 256 && d.r <= igemm_pair_max_resident_steps()) ? 1 : 0;
     e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY2, p, plan.grid, stream);
   } else {
     // the single-CTA kernel has no fifth 16-bit map slot: the tail map travels in the unused tmA2 slot
@@ -723,6 +724,7 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
   if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
     if (!p.tma_store) return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs a dense channels-last output");
+    p.b_resident = (d.k <= 256 && d.r * d.s * p.c_blocks <= igemm_pair_max_resident_steps()) ? 1 : 0;
     e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY, p, plan.grid, stream);
   } else {
     e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, p, plan.grid, stream);

@@ -39,12 +39,16 @@ constexpr int kKB = 64;              // 16-bit reduction elements per stage
 constexpr int kABytes = kRows * kRowB;
 constexpr int kBBytes = kHalfN * kRowB;
 constexpr int kStageBytes = kABytes + kBBytes;      // 32 KB per CTA per stage
-constexpr int kStages = 5;                           // 160 KB
+constexpr int kStages = 5;                           // streaming mode: 5 x 32 KB
+constexpr int kRingBytes = 184 * 1024;               // operand region (stages, or resident filter + A stages)
+constexpr int kMaxStages = 8;                        // barrier slots
+constexpr int kMaxResidentSteps = 7;                 // resident filter: at most 7 x 16 KB per CTA
 constexpr int kThreadsPair = 192;
 constexpr int kOutBytes = 4 * 2 * 32 * kRowB;        // two TMA-store staging buffers per warp
 constexpr int kEpiBytes = 4 * 2 * kPairN * int(sizeof(float));
-constexpr int kBarBytes = (2 * kStages + 5) * 8 + 16;
-constexpr int kSmemPair = kStages * kStageBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
+constexpr int kBarBytes = (2 * kMaxStages + 6) * 8 + 16;
+constexpr int kSmemPair = kRingBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
+static_assert(kStages * kStageBytes <= kRingBytes, "streaming ring must fit");
 constexpr uint32_t kTmemColsPair = 512;              // two 256-column accumulators
 static_assert(kSmemPair <= 227 * 1024, "shared memory budget");
 
@@ -58,16 +62,26 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* stage_base = smem;
-  uint8_t* out_stage = smem + kStages * kStageBytes;
+  // Operand region.  Streaming mode: a ring of (A, B-half) stages.  Resident mode
+  // (small reductions, one channel tile): this CTA's half of the whole filter is
+  // copied once and stays; the ring then holds activation tiles only.
+  const int k_iters = p.R * p.S * p.c_blocks;
+  const bool b_resident = p.b_resident != 0;
+  uint8_t* b_res = smem;
+  uint8_t* stage_base = smem + (b_resident ? k_iters * kBBytes : 0);
+  const int stage_stride = b_resident ? kABytes : kStageBytes;
+  int n_stages = b_resident ? (kRingBytes - k_iters * kBBytes) / kABytes : kStages;
+  if (n_stages > kMaxStages) n_stages = kMaxStages;
+  uint8_t* out_stage = smem + kRingBytes;
   float* epi_stage = reinterpret_cast<float*>(out_stage + kOutBytes);
   uint64_t* bars = reinterpret_cast<uint64_t*>(out_stage + kOutBytes + kEpiBytes);
-  uint64_t* full_bar = bars;                       // used in the leader only
-  uint64_t* empty_bar = bars + kStages;            // each CTA's own
-  uint64_t* tmem_full = bars + 2 * kStages;        // [2], each CTA's own
-  uint64_t* tmem_empty = bars + 2 * kStages + 2;   // [2], used in the leader only
-  uint64_t* drain_bar = bars + 2 * kStages + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
+  uint64_t* full_bar = bars;                          // used in the leader only
+  uint64_t* empty_bar = bars + kMaxStages;            // each CTA's own
+  uint64_t* tmem_full = bars + 2 * kMaxStages;        // [2], each CTA's own
+  uint64_t* tmem_empty = bars + 2 * kMaxStages + 2;   // [2], used in the leader only
+  uint64_t* drain_bar = bars + 2 * kMaxStages + 4;
+  uint64_t* bres_bar = bars + 2 * kMaxStages + 5;     // resident filter has landed (leader only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 6);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -76,10 +90,11 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const uint32_t peer = rank ^ 1u;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&full_bar[i], 1);                  // the leader producer's arrive.expect_tx
       mbar_init(&empty_bar[i], 1);                 // one commit from the leader's issuer
     }
+    mbar_init(bres_bar, 1);
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
     mbar_init(&tmem_empty[0], 2 * 4 * 32);         // epilogue threads of both CTAs
@@ -107,15 +122,24 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int total_tiles = m_pairs * n_tiles;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int k_iters = p.R * p.S * p.c_blocks;
   const int ohw = p.OH * p.OW;
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t stage = 0, phase = 0;
       bool alive = true;
       const uint32_t full0 = map_to_cta(smem_u32(&full_bar[0]), 0);  // the leader's barriers
+      if (b_resident && pair_id < total_tiles) {
+        // this CTA's 128 filter rows for every reduction step, once (n_tiles == 1 in this mode)
+        const uint32_t bres = map_to_cta(smem_u32(bres_bar), 0);
+        if (rank == 0) mbar_arrive_expect_tx(bres_bar, uint32_t(2 * k_iters * kBBytes));
+        int kit = 0;
+        for (int r = 0; r < p.R; ++r)
+          for (int s = 0; s < p.S; ++s)
+            for (int cb = 0; cb < p.c_blocks; ++cb, ++kit)
+              tma_load_3d_pair(b_res + kit * kBBytes, &tmB, bres, cb * kKB, r * p.S + s, int(rank) * kHalfN);
+      }
       for (int tile = pair_id; tile < total_tiles && alive; tile += num_pairs) {
         const int m_pair = tile / n_tiles;
         const int n_tile = tile - m_pair * n_tiles;
@@ -135,22 +159,21 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           w_base = ow0 * p.stride_w - p.pad_left;
           h_base = oh0 * p.stride_h - p.pad_top;
         }
-        const uint32_t pair_tx = p.lowc ? uint32_t(2 * (p.a_tx_bytes + kBBytes)) : uint32_t(2 * kStageBytes);
+        const uint32_t a_tx = p.lowc ? uint32_t(p.a_tx_bytes) : uint32_t(kABytes);
+        const uint32_t pair_tx = 2 * (a_tx + (b_resident ? 0u : uint32_t(kBBytes)));
         const int b_row0 = n_tile * kPairN + int(rank) * kHalfN;
         for (int r = 0; r < p.R && alive; ++r) {
           for (int s = 0; s < p.S && alive; ++s) {
             const uint16_t off_w = static_cast<uint16_t>(s * p.dil_w);
             const uint16_t off_h = static_cast<uint16_t>(r * p.dil_h);
             const int tap = r * p.S + s;
-            for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
-              const uint32_t stage = it % kStages;
-              const uint32_t phase = (it / kStages) & 1u;
+            for (int cb = 0; cb < p.c_blocks; ++cb) {
               if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
                                      kIncidentProducerWait)) {
                 alive = false;
                 break;
               }
-              uint8_t* st = stage_base + stage * kStageBytes;
+              uint8_t* st = stage_base + stage * stage_stride;
               if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], pair_tx);
               const uint32_t bar = full0 + stage * 8;
               const int c0 = cb * kKB;
@@ -159,7 +182,11 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
               } else {
                 tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, off_w, off_h);
               }
-              tma_load_3d_pair(st + kABytes, &tmB, bar, c0, tap, b_row0);
+              if (!b_resident) tma_load_3d_pair(st + kABytes, &tmB, bar, c0, tap, b_row0);
+              if (++stage == uint32_t(n_stages)) {
+                stage = 0;
+                phase ^= 1u;
+              }
             }
           }
         }
@@ -174,9 +201,12 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------- issuer (leader only)
     if (rank == 0 && lane == 0) {
-      uint32_t it = 0;
+      uint32_t stage = 0, phase = 0;
       uint32_t tcount = 0;
       bool alive = true;
+      if (b_resident && pair_id < total_tiles) {
+        alive = mbar_wait_bounded(bres_bar, 0u, abort_flag, p.status, kIncidentMmaWaitFull);
+      }
       const uint32_t empty_own = smem_u32(&empty_bar[0]);
       const uint32_t empty_peer = map_to_cta(empty_own, 1);
       const uint32_t tfull_own = smem_u32(&tmem_full[0]);
@@ -191,23 +221,26 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kPairN;
-        for (int kit = 0; kit < k_iters; ++kit, ++it) {
-          const uint32_t stage = it % kStages;
-          const uint32_t phase = (it / kStages) & 1u;
+        for (int kit = 0; kit < k_iters; ++kit) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull)) {
             alive = false;
             break;
           }
           tc_fence_after();
-          const uint32_t st = smem_u32(stage_base + stage * kStageBytes);
+          const uint32_t st = smem_u32(stage_base + stage * stage_stride);
+          const uint32_t bt = b_resident ? smem_u32(b_res + kit * kBBytes) : st + kABytes;
 #pragma unroll
           for (int k = 0; k < kKB / 16; ++k) {
             const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
-            const uint64_t b = make_sw128_kmajor_desc(st + kABytes + k * 32);
+            const uint64_t b = make_sw128_kmajor_desc(bt + k * 32);
             mma_f16_pair(d_tmem, a, b, kIdesc, (kit > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit_pair(empty_own + stage * 8);
           tc_commit_pair(empty_peer + stage * 8);
+          if (++stage == uint32_t(n_stages)) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
         if (alive) {
           tc_commit_pair(tfull_own + buf * 8);
@@ -313,6 +346,7 @@ cudaError_t igemm_pair_prepare_device() {
 
 int igemm_pair_smem_bytes() { return kSmemPair; }
 int igemm_pair_stages() { return kStages; }
+int igemm_pair_max_resident_steps() { return kMaxResidentSteps; }
 
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
                               const CUtensorMap& tmY, const CUtensorMap& tmY2, const IgemmParams& p,

@@ -37,6 +37,7 @@ struct IgemmParams {
   int tiles_per_image;   // low-channel mode: ceil(OH / ohs)
   int ohs;               // low-channel mode: output rows per tile
   int a_tx_bytes;        // bytes one activation copy delivers (rows_per_tile * 128 in low-channel mode)
+  int b_resident;        // pair kernel: the filter half stays in shared memory for the whole launch
   int k_real;            // length of bias / scale (GEMM column j uses entry j % k_real)
   uint32_t* status;
   long long* prof;       // optional: 16 cycle counters written by CTA 0 (nullptr = off)
@@ -62,6 +63,7 @@ cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorM
 cudaError_t igemm_pair_prepare_device();
 int igemm_pair_smem_bytes();
 int igemm_pair_stages();
+int igemm_pair_max_resident_steps();  // reductions this short (and one channel tile) keep the filter resident
 
 // Direct convolution on CUDA cores (conv_direct.cu): any dtype, groups, strides.
 struct DirectParams {

@@ -70,6 +70,7 @@ class ConvPlan(ctypes.Structure):
         ("grid", ctypes.c_int32), ("block", ctypes.c_int32),
         ("launches", ctypes.c_int32),
         ("low_channel", ctypes.c_int32),
+        ("pixel_group", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_int64),
         ("packed_weight_bytes", ctypes.c_int64),
         ("smem_bytes", ctypes.c_int64),

@@ -151,7 +151,12 @@ def _plan_for(input, weight, out, stride, padding4, dilation, groups, algo):
 def _packed_weight(weight: torch.Tensor, d: nat.ConvDesc, plan: nat.ConvPlan, stream: int) -> torch.Tensor:
     version = int(getattr(weight, "_version", 0))
     # the packed layout depends on the plan: generic [K,R,S,Cpad] or the low-channel quad layout
-    layout = ("lowc", d.stride_w) if plan.low_channel else ("krsc", plan.c_padded)
+    if plan.pixel_group > 1:
+        layout = ("grouped", plan.pixel_group, d.stride_w)
+    elif plan.low_channel:
+        layout = ("lowc", d.stride_w)
+    else:
+        layout = ("krsc", plan.c_padded)
     key = (layout, id(weight), weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()),
            str(weight.dtype), weight.device.type, weight.device.index, version)
     entry = _PACKED_WEIGHT_CACHE.get(key)

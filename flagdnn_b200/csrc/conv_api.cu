@@ -162,8 +162,57 @@ LowChannel low_channel_geometry(const fdnn_conv_desc* d, int oh, int ow, const v
   return g;
 }
 
+// Output-pixel grouping for narrow layers.  An MMA of 128 rows occupies the tensor
+// pipe for the same time whatever its column count, so a layer with K <= 128
+// output channels uses at most K/256 of the machine.  Grouping Q neighbouring
+// output pixels of a row into one GEMM row turns the layer into an equivalent
+// convolution with Q*K output channels, a filter widened to S + (Q-1)*stride_w
+// taps (zero where a pixel does not reach) and a W-stride of Q*stride_w.  Its y,
+// [N, OH, OW/Q, Q*K] in NHWC, is the same memory as the real [N, OH, OW, K].
+// The wider filter costs (S + (Q-1)*stride_w) / S more MMA steps per row, the
+// Q-fold wider tile makes each step Q times as productive.
+int choose_pixel_group(const fdnn_conv_desc* d, int oh, int ow, const void* y) {
+  if (elem_size(d->dtype) != 2 || d->groups != 1 || d->dil_w != 1 || d->c < 8) return 1;
+  if (d->r * d->s < 4) return 1;                       // 1x1 / thin filters are bandwidth-bound anyway
+  if (y_pixel_stride(d, oh, ow) != d->k || !aligned16(y)) return 1;
+  if (2.0 * d->n * oh * ow * d->k * d->c * d->r * d->s < 4.0e9) return 1;  // only layers that fill the machine
+  int best = 1;
+  double best_cost = double(d->s);
+  for (int q = 2; q <= 4; q *= 2) {
+    if (q * d->k > 256 || ow % q != 0 || q * d->stride_w > 8) break;
+    const int s_virtual = d->s + (q - 1) * d->stride_w;
+    if (s_virtual - 1 > 255 || d->pad_right + (q - 1) * d->stride_w - (s_virtual - 1) < -128) break;
+    const double cost = double(s_virtual) / q;        // MMA steps per output pixel, relative
+    if (cost < 0.85 * best_cost) {
+      best = q;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+// The equivalent convolution of a pixel-grouped layer (filter strides describe the packed [Q*K][R][S'][Cpad]).
+fdnn_conv_desc grouped_desc(const fdnn_conv_desc* d, int q, int oh, int ow) {
+  fdnn_conv_desc v = *d;
+  const int gran = 16 / elem_size(d->dtype);
+  const int c_pad = round_up(d->c, gran);
+  v.k = q * d->k;
+  v.s = d->s + (q - 1) * d->stride_w;
+  v.stride_w = q * d->stride_w;
+  v.pad_right = d->pad_right + (q - 1) * d->stride_w;
+  v.w_strides[0] = (int64_t)d->r * v.s * c_pad;
+  v.w_strides[1] = 1;
+  v.w_strides[2] = (int64_t)v.s * c_pad;
+  v.w_strides[3] = c_pad;
+  v.y_strides[0] = (int64_t)oh * ow * d->k;
+  v.y_strides[1] = 1;
+  v.y_strides[2] = (int64_t)ow * d->k;
+  v.y_strides[3] = (int64_t)q * d->k;
+  return v;
+}
+
 int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void* y,
-              fdnn_conv_plan* plan) {
+              fdnn_conv_plan* plan, bool allow_group = true) {
   int st = validate(d);
   if (st != FDNN_OK) return st;
   if (plan == nullptr) return fail(FDNN_BAD_PARAM, "plan is NULL");
@@ -232,6 +281,27 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
       plan->grid = int(2 * pairs);
     }
     return FDNN_OK;
+  }
+
+  if (allow_group) {
+    const int q = choose_pixel_group(d, oh, ow, y);
+    if (q > 1) {
+      fdnn_conv_desc v = grouped_desc(d, q, oh, ow);
+      v.algo = d->algo;
+      fdnn_conv_plan pv;
+      if (make_plan(&v, x, nullptr, y, &pv, false) == FDNN_OK && pv.algo != FDNN_ALGO_DIRECT && pv.ow * q == ow) {
+        const double flops = plan->flops, bytes = plan->bytes;
+        *plan = pv;
+        plan->pixel_group = q;
+        plan->oh = oh;
+        plan->ow = ow;
+        plan->flops = flops;
+        plan->bytes = bytes;
+        plan->w_packed = 1;
+        plan->packed_weight_bytes = (long long)v.k * v.r * v.s * round_up(d->c, 16 / es) * es;
+        return FDNN_OK;
+      }
+    }
   }
 
   const int gran = 16 / es;  // channels per 16 bytes
@@ -553,6 +623,13 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, void* pac
   if (w == nullptr || packed == nullptr) return fail(FDNN_BAD_PARAM, "w and packed must not be NULL");
   if (packed_bytes < plan.packed_weight_bytes)
     return fail(FDNN_WORKSPACE_TOO_SMALL, "packed filter buffer too small");
+  if (plan.pixel_group > 1) {
+    cudaError_t e = launch_pack_w_grouped(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c,
+                                          d.r, d.s, d.stride_w, plan.pixel_group, plan.c_padded, packed,
+                                          static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda("pack_weight launch", e);
+    return FDNN_OK;
+  }
   if (plan.low_channel) {
     const int shift = round_up(d.pad_left, 2) - d.pad_left;
     cudaError_t e = launch_pack_w_lowc(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c,
@@ -567,13 +644,28 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, void* pac
   return FDNN_OK;
 }
 
+static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
+                    const void* bias, const void* scale, int activation, void* y, void* workspace,
+                    int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real);
+
 int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
                     const void* bias, const void* scale, int activation, void* y, void* workspace,
                     int64_t workspace_bytes, void* stream_v) {
+  if (desc == nullptr) return fail(FDNN_BAD_PARAM, "descriptor is NULL");
+  return fwd_impl(desc, x, w, w_packed, bias, scale, activation, y, workspace, workspace_bytes, stream_v, true,
+                  desc->k);
+}
+
+// k_real: length of bias / scale (differs from desc->k only for the equivalent convolution of a
+// pixel-grouped layer, whose GEMM column j uses entry j % k_real).
+static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
+                    const void* bias, const void* scale, int activation, void* y, void* workspace,
+                    int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real) {
   fdnn_conv_plan plan;
   // A caller that hands over a packed filter wants it used even when w itself
   // would qualify for in-place reads; plan accordingly.
-  int st = make_plan(desc, x, w_packed != nullptr ? reinterpret_cast<const void*>(uintptr_t(1)) : w, y, &plan);
+  int st = make_plan(desc, x, w_packed != nullptr ? reinterpret_cast<const void*>(uintptr_t(1)) : w, y, &plan,
+                     allow_group);
   if (st != FDNN_OK) return st;
   if (activation != FDNN_ACT_NONE && activation != FDNN_ACT_RELU)
     return fail(FDNN_BAD_PARAM, "unknown activation");
@@ -631,6 +723,12 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (plan.w_packed && (reinterpret_cast<uintptr_t>(w_packed) & 15u) != 0)
     return fail(FDNN_BAD_PARAM, "packed filter must be 16-byte aligned");
 
+  if (plan.pixel_group > 1) {
+    // run the equivalent convolution; its filter is the packed buffer, consumed in place
+    const fdnn_conv_desc v = grouped_desc(&d, plan.pixel_group, plan.oh, plan.ow);
+    return fwd_impl(&v, x, w_packed, nullptr, bias, scale, activation, y, workspace, workspace_bytes, stream_v,
+                    false, d.k);
+  }
   if (plan.low_channel) return fwd_low_channel(d, plan, dev, x, w_packed, bias, scale, activation, y, workspace, stream);
 
   const int es = elem_size(d.dtype);
@@ -688,7 +786,7 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, co
   IgemmParams p = {};
   p.M = d.n * plan.oh * plan.ow;
   p.Kout = d.k;
-  p.k_real = d.k;
+  p.k_real = k_real;
   p.lowc = 0;
   p.rows_per_tile = 128;
   p.OH = plan.oh; p.OW = plan.ow;

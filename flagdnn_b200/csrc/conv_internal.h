@@ -95,6 +95,10 @@ cudaError_t launch_repack_x_lowc(int dtype, const void* x, const long long x_s[4
 // `shift` = stored left padding minus the convolution's own left padding.
 cudaError_t launch_pack_w_lowc(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
                                int S, int stride_w, int shift, void* dst, cudaStream_t stream);
+// Pixel-grouped filter: w -> [q*K][R][S + (q-1)*stride_w][c_pad]; row (g, k) holds filter k
+// shifted by g*stride_w taps (zero where the g-th pixel of the group does not reach).
+cudaError_t launch_pack_w_grouped(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
+                                  int S, int stride_w, int q, int c_pad, void* dst, cudaStream_t stream);
 // w[K,C,R,S] (any strides) -> dense [K,R,S,c_pad]; f32 split like x.
 cudaError_t launch_pack_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
                           int S, int c_pad, void* dst, long long plane_elems, cudaStream_t stream);

@@ -201,6 +201,27 @@ pack_w_lowc_kernel(const T* __restrict__ w, long long sk, long long sc, long lon
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+pack_w_grouped_kernel(const T* __restrict__ w, long long sk, long long sc, long long sr, long long ss, int K,
+                      int C, int R, int S, int stride_w, int q, int c_pad, T* __restrict__ dst) {
+  const int sv = S + (q - 1) * stride_w;
+  const long long total = (long long)q * K * R * sv * c_pad;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long t = i;
+    const int c = int(t % c_pad); t /= c_pad;
+    const int j = int(t % sv); t /= sv;
+    const int r = int(t % R); t /= R;
+    const int row = int(t);          // g * K + k
+    const int g = row / K, k = row - g * K;
+    const int s = j - g * stride_w;
+    T v = T(0.0f);
+    if (c < C && s >= 0 && s < S) v = w[k * sk + c * sc + r * sr + s * ss];
+    dst[i] = v;
+  }
+}
+
 int grid_for(long long work_items, int per_block) {
   long long blocks = (work_items + per_block - 1) / per_block;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
@@ -283,6 +304,24 @@ cudaError_t launch_pack_w_lowc(int dtype, const void* w, const long long w_s[4],
   } else if (dtype == FDNN_BF16) {
     pack_w_lowc_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(w), w_s[0], w_s[1], w_s[2], w_s[3], K, C, R, S, stride_w, shift,
+        static_cast<__nv_bfloat16*>(dst));
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack_w_grouped(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
+                                  int S, int stride_w, int q, int c_pad, void* dst, cudaStream_t stream) {
+  const long long total = (long long)q * K * R * (S + (q - 1) * stride_w) * c_pad;
+  const int grid = grid_for(total, 256);
+  if (dtype == FDNN_F16) {
+    pack_w_grouped_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(w), w_s[0], w_s[1],
+                                                            w_s[2], w_s[3], K, C, R, S, stride_w, q, c_pad,
+                                                            static_cast<__half*>(dst));
+  } else if (dtype == FDNN_BF16) {
+    pack_w_grouped_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(w), w_s[0], w_s[1], w_s[2], w_s[3], K, C, R, S, stride_w, q, c_pad,
         static_cast<__nv_bfloat16*>(dst));
   } else {
     return cudaErrorInvalidValue;

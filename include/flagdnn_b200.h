@@ -84,6 +84,7 @@ typedef struct fdnn_conv_plan {
   int32_t grid, block;          /* launch shape of the main kernel */
   int32_t launches;             /* kernels one fwd call launches (main + repack) */
   int32_t low_channel;          /* 1: C <= 4 path (pixel quads as GEMM rows, 16-pixel input windows) */
+  int32_t pixel_group;          /* > 1: that many neighbouring output pixels form one GEMM row (narrow layers) */
   int64_t workspace_bytes;      /* scratch fwd needs (0 when x is consumed in place) */
   int64_t packed_weight_bytes;  /* size of the packed filter (0 when w is consumed in place) */
   int64_t smem_bytes;           /* dynamic shared memory of the main kernel */

@@ -269,6 +269,40 @@ def test_low_channel_path_matches_oracle(fd, case, algo):
     _check(got, oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, 1, scale=sc, relu=True), dtype_name)
 
 
+GROUPED = [
+    # n, c, hw, k, r, stride, pad, expected pixel group
+    (20, 64, 56, 64, 3, 1, 1, 4),     # ResNet stage-1 3x3: four pixels per GEMM row, 256 columns
+    (24, 128, 56, 128, 3, 2, 1, 2),   # stride-2 3x3 at 128 channels: pairs
+    (40, 128, 28, 128, 3, 1, 1, 2),
+    (24, 64, 54, 64, 3, 1, 1, 2),     # 54 output columns: pairs divide, quads do not
+]
+
+
+@pytest.mark.parametrize("case", GROUPED, ids=[f"c{c[1]}_hw{c[2]}_s{c[5]}" for c in GROUPED])
+def test_pixel_grouped_narrow_layers_match_oracle(fd, case):
+    """Narrow layers run as an equivalent convolution whose rows are groups of output pixels."""
+    n, c, hw, k, r, stride, pad, group = case
+    x = _rand((n, c, hw, hw), 70).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    w = _rand((k, c, r, r), 71, std=(c * r * r) ** -0.5).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    b = _rand((k,), 72, std=0.1).to(torch.bfloat16).cuda()
+    sc = (torch.rand(k, generator=torch.Generator().manual_seed(73)) + 0.5).to(torch.bfloat16).cuda()
+    plan = fd.conv2d_plan(x, w, stride=stride, padding=pad)
+    assert plan["pixel_group"] == group and plan["w_packed"] == 1
+    got = fd.fused_conv2d_bias_relu(x, w, b, stride=stride, padding=pad, scale=sc)
+    fd.set_algo("direct")  # the plain CUDA-core kernel as an in-library second opinion
+    try:
+        plain = fd.fused_conv2d_bias_relu(x[:2], w, b, stride=stride, padding=pad, scale=sc)
+    finally:
+        fd.set_algo("auto")
+    torch.testing.assert_close(got[:2].float(), plain.float(), rtol=1e-2, atol=1e-2)
+    picks = [0, n // 2, n - 1]
+    ref = oracle.conv2d_torch_cpu(x[picks], w, b, stride, pad, 1, 1, scale=sc, relu=True)
+    _check(got[picks], ref, "bfloat16")
+    # every image, against the library's own ungrouped result on a different batch split
+    alone = fd.fused_conv2d_bias_relu(x[3:4], w, b, stride=stride, padding=pad, scale=sc)  # small: not grouped
+    assert torch.equal(alone, got[3:4])
+
+
 def test_scaled_graph_folds_into_one_node(fd):
     x = _rand((2, 16, 8, 8), 20).to(torch.float16).cuda().contiguous(memory_format=torch.channels_last)
     w = _rand((24, 16, 3, 3), 21, std=0.08).to(torch.float16).cuda()

@@ -162,7 +162,7 @@ def use_all_host_threads(torch):
     return torch.get_num_threads()
 
 
-def cpu_baseline_leg(wl, torch, sample_n, min_seconds=2.0):
+def cpu_baseline_leg(wl, torch, sample_n, min_seconds=10.0):
     """The reference's CPU path timed on the host cores; test-infrastructure code (oracle/) as the checker's timer."""
     import oracle
 
@@ -173,7 +173,7 @@ def cpu_baseline_leg(wl, torch, sample_n, min_seconds=2.0):
     cdt = getattr(torch, wl["dtype"])  # the reference runs F.conv2d in the tensors' own dtype
     oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
     times, t_all = [], time.perf_counter()
-    while len(times) < 3 or (time.perf_counter() - t_all < min_seconds and len(times) < 200):
+    while len(times) < 3 or (time.perf_counter() - t_all < min_seconds and len(times) < 5000):
         t0 = time.perf_counter()
         oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
         times.append(time.perf_counter() - t0)

@@ -108,7 +108,9 @@ def _seeded(shape, seed, dist="normal", std=1.0):
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/FlagDNN")
+    ref_root = sys.argv[1]
     flag_dnn = _import_reference(ref_root)
     records = {}
 

@@ -339,6 +339,86 @@ def conv2d_bias_act(
                 nat.ACT_RELU if relu else nat.ACT_NONE)
 
 
+def conv1d(
+    input: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    stride: Union[int, Tuple[int]] = 1,
+    padding: Union[str, int, Tuple[int]] = 0,
+    dilation: Union[int, Tuple[int]] = 1,
+    groups: int = 1,
+) -> torch.Tensor:
+    """Drop-in for ``flag_dnn.ops.conv1d`` (src/flag_dnn/ops/conv1d.py:416): a convolution over
+    [N, C, L] (or unbatched [C, L]) is the 2-D path with H = R = 1, so it runs on the same kernels.
+    Checks and messages follow src/flag_dnn/ops/conv1d.py:21-66, 90-150, 436-446."""
+    def single(v, name):
+        if isinstance(v, int):
+            return int(v)
+        if len(v) != 1:
+            raise RuntimeError(f"{name} must be an int or a length-1 tuple")
+        return int(v[0])
+
+    stride_w = single(stride, "stride")
+    dilation_w = single(dilation, "dilation")
+    if input.dim() not in (2, 3) or weight.dim() != 3:
+        raise RuntimeError("flag_dnn conv1d expects 2D/3D input and 3D weight")
+    if not input.is_cuda:
+        raise NotImplementedError("flag_dnn conv1d only supports CUDA input")
+    if weight.device != input.device:
+        raise RuntimeError("input and weight must be on the same device")
+    if bias is not None and bias.device != input.device:
+        raise RuntimeError("input and bias must be on the same device")
+    if input.dtype not in _DTYPE_IDS:
+        raise NotImplementedError(f"Unsupported dtype: {input.dtype}")
+    if weight.dtype != input.dtype:
+        raise RuntimeError("input and weight must have the same dtype")
+    if bias is not None and bias.dtype != input.dtype:
+        raise RuntimeError("input and bias must have the same dtype")
+    if any(t is not None and t.requires_grad for t in (input, weight, bias)) and torch.is_grad_enabled():
+        raise NotImplementedError("flag_dnn conv1d is forward-only")
+    if groups <= 0:
+        raise RuntimeError("groups must be a positive integer")
+    if stride_w <= 0:
+        raise RuntimeError("stride must be positive")
+    if dilation_w <= 0:
+        raise RuntimeError("dilation must be positive")
+    kw = weight.shape[2]
+    if isinstance(padding, str):
+        if padding == "valid":
+            pad_left = pad_right = 0
+        elif padding == "same":
+            if stride_w != 1:
+                raise RuntimeError("padding='same' is not supported for strided convolutions")
+            total = max(dilation_w * (kw - 1), 0)
+            pad_left, pad_right = total // 2, total - total // 2
+        else:
+            raise RuntimeError("padding must be 'valid', 'same', int, or tuple")
+    else:
+        pad_left = pad_right = single(padding, "padding")
+        if pad_left < 0:
+            raise RuntimeError("negative padding is not supported")
+    batched = input.dim() == 3
+    c_in, length = input.shape[-2], input.shape[-1]
+    c_out, c_per_group = weight.shape[0], weight.shape[1]
+    if c_in <= 0 or c_out <= 0 or c_per_group <= 0 or kw <= 0:
+        raise RuntimeError("input and weight dimensions must be non-empty")
+    if c_in % groups != 0 or c_out % groups != 0:
+        raise RuntimeError("channels must be divisible by groups")
+    if c_per_group != c_in // groups:
+        raise RuntimeError("weight.shape[1] must match input_channels // groups")
+    if bias is not None and (bias.dim() != 1 or bias.numel() != c_out):
+        raise RuntimeError(f"bias shape mismatch, expected ({c_out},)")
+    if length + pad_left + pad_right < dilation_w * (kw - 1) + 1:
+        raise RuntimeError("kernel size can't be greater than input size")
+    if _conv_out_dim(length, pad_left, pad_right, dilation_w, kw, stride_w) <= 0:
+        raise RuntimeError("computed output size is not positive")
+    x4 = (input if batched else input.unsqueeze(0)).unsqueeze(2)   # [N, C, 1, L]
+    w4 = weight.unsqueeze(2)                                        # [K, C/g, 1, S]
+    y4 = _run(x4, w4, bias, None, (1, stride_w), (0, 0, pad_left, pad_right), (1, dilation_w), groups, nat.ACT_NONE)
+    y = y4.squeeze(2)
+    return y if batched else y.squeeze(0)
+
+
 def device_status() -> int:
     """Synchronise the current device and return its incident word (0 = clean)."""
     word = ctypes.c_uint32(0)

@@ -272,12 +272,43 @@ def _cache_key(graph_obj: Graph, specs: list, backend: str) -> str:
 
 
 class CompiledGraph:
-    def __init__(self, plan: ExecutionPlan):
+    """A planned graph.  With ``options={"cuda_graph": True}`` the whole plan is captured into one
+    CUDA graph on its first run with CUDA tensors and replayed afterwards: inputs are copied into
+    static buffers (skipped for tensors that already are those buffers, see ``static_inputs``) and
+    the returned tensors are static too — consume them before the next ``run``.  Multi-step plans
+    (a bottleneck block, a whole conv stack) then cost one launch of host time instead of one per
+    node; the reference executes such plans node by node from Python
+    (src/flag_dnn/graph/executor.py:68-106)."""
+
+    def __init__(self, plan: ExecutionPlan, cuda_graph: bool = False):
         self.plan = plan
         self.graph = plan.graph
+        self._use_cuda_graph = bool(cuda_graph)
+        self._captured = None
+        self.static_inputs: Optional[list] = None
+        self._static_outputs: Any = None
 
     def run(self, *inputs: Any) -> Any:
-        return self.plan.run(*inputs)
+        if not self._use_cuda_graph or not any(isinstance(t, torch.Tensor) and t.is_cuda for t in inputs):
+            return self.plan.run(*inputs)
+        if len(inputs) != len(self.plan.input_specs):
+            raise RuntimeError(f"graph expects {len(self.plan.input_specs)} inputs, got {len(inputs)}")
+        for index, (spec, tensor) in enumerate(zip(self.plan.input_specs, inputs)):
+            _validate_input(spec, tensor, index)
+        if self._captured is None:
+            self.static_inputs = [torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device).copy_(t)
+                                  for t in inputs]
+            self.plan.run(*self.static_inputs)        # warm-up: packs filters, sets kernel attributes
+            torch.cuda.synchronize()
+            captured = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(captured):
+                self._static_outputs = self.plan.run(*self.static_inputs)
+            self._captured = captured
+        for static, given in zip(self.static_inputs, inputs):
+            if static.data_ptr() != given.data_ptr():
+                static.copy_(given, non_blocking=True)
+        self._captured.replay()
+        return self._static_outputs
 
     def __call__(self, *inputs: Any) -> Any:
         return self.run(*inputs)
@@ -348,7 +379,7 @@ def compile(fn: Callable, inputs: Optional[list] = None, input_specs: Optional[l
         plan.debug_info["cache_hit"] = True
         plan.debug_info["cache_layer"] = "memory"
         plan.debug_info["output_structure"] = structure
-    return CompiledGraph(plan)
+    return CompiledGraph(plan, cuda_graph=bool(opts.get("cuda_graph", False)))
 
 
 # ----------------------------------------------------------------- execution

@@ -110,6 +110,45 @@ def test_eager_conv2d_matches_oracle(fd, golden, idx, dtype_name):
             _check(out, torch.from_numpy(golden[key + "_y"]), dtype_name)
 
 
+# (input_shape, weight_shape, bias?, stride, padding, dilation, groups, unbatched, noncontiguous):
+# the shape list of the reference's tests/test_conv1d.py:18-30
+CONV1D_CASES = [
+    ((2, 3, 16), (4, 3, 3), True, 1, 1, 1, 1, False, False),
+    ((1, 3, 17), (5, 3, 1), True, 1, 0, 1, 1, False, False),
+    ((2, 4, 31), (8, 4, 5), False, 2, 2, 1, 1, False, False),
+    ((1, 3, 29), (4, 3, 3), True, 1, 2, 2, 1, False, False),
+    ((2, 4, 23), (6, 2, 3), True, 1, 1, 1, 2, False, False),
+    ((2, 8, 33), (8, 1, 5), False, 1, 2, 1, 8, False, False),
+    ((1, 2, 19), (4, 2, 4), True, 1, "same", 1, 1, False, False),
+    ((2, 4, 25), (8, 2, 3), False, 1, "same", 2, 2, False, False),
+    ((2, 3, 21), (5, 3, 3), True, 2, "valid", 1, 1, False, False),
+    ((3, 13), (4, 3, 3), True, 1, 1, 1, 1, True, False),
+    ((2, 3, 18), (4, 3, 3), True, 1, 1, 1, 1, False, True),
+    ((8, 64, 4096), (128, 64, 5), True, 1, 2, 1, 1, False, False),   # large enough for the tensor-core path
+]
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16", "float16", "float64"])
+@pytest.mark.parametrize("case", CONV1D_CASES, ids=[str(i) for i in range(len(CONV1D_CASES))])
+def test_conv1d_matches_torch_cpu(fd, case, dtype_name):
+    ishape, wshape, has_bias, stride, padding, dilation, groups, unbatched, noncontig = case
+    dtype = DTYPES[dtype_name]
+    g = torch.Generator().manual_seed(5)
+    if noncontig:
+        x = torch.randn(tuple(ishape[:-1]) + (ishape[-1] * 2,), generator=g).to(dtype).cuda()[..., ::2]
+    else:
+        x = torch.randn(ishape, generator=g).to(dtype).cuda()
+    fan_in = wshape[1] * wshape[2]
+    w = (torch.randn(wshape, generator=g) * fan_in ** -0.5).to(dtype).cuda()
+    b = (torch.randn(wshape[0], generator=g) * 0.1).to(dtype).cuda() if has_bias else None
+    out = fd.conv1d(x, w, b, stride=stride, padding=padding, dilation=dilation, groups=groups)
+    cdt = torch.float64 if dtype_name == "float64" else torch.float32
+    ref = torch.nn.functional.conv1d(x.cpu().to(cdt), w.cpu().to(cdt), None if b is None else b.cpu().to(cdt),
+                                     stride=stride, padding=padding, dilation=dilation, groups=groups)
+    assert out.shape == ref.shape and out.dtype == dtype and out.is_contiguous()
+    _check(out, ref, dtype_name)
+
+
 def test_aten_override_routes_functional_conv2d(fd):
     g = torch.Generator().manual_seed(3)
     x = torch.randn(2, 16, 12, 12, generator=g).cuda()

@@ -52,3 +52,48 @@ def test_every_layer_matches_oracle_and_chain_matches_end_to_end(native_lib, ima
     # 53 layers of bf16 rounding compound; agreement is judged relative to the activation scale
     assert err.max() <= 0.05 * y_ref.float().abs().max() + 0.05
     assert fd.device_status() == 0
+
+
+@pytest.mark.gpu
+def test_bottleneck_block_graph_replays_as_one_cuda_graph(native_lib):
+    """A three-convolution bottleneck (scale + bias folded, ReLU fused) compiled once and replayed."""
+    import flagdnn_b200 as fd
+
+    g = torch.Generator().manual_seed(3)
+
+    def t(*shape, std=1.0):
+        return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16).cuda()
+
+    x = t(4, 64, 28, 28).contiguous(memory_format=torch.channels_last)
+    w1, w2, w3 = (t(32, 64, 1, 1, std=0.12).contiguous(memory_format=torch.channels_last),
+                  t(32, 32, 3, 3, std=0.06).contiguous(memory_format=torch.channels_last),
+                  t(64, 32, 1, 1, std=0.17).contiguous(memory_format=torch.channels_last))
+    s1, s2, s3 = [(torch.rand(k, generator=g) + 0.5).to(torch.bfloat16).cuda().reshape(1, k, 1, 1) for k in (32, 32, 64)]
+    b1, b2, b3 = t(32, std=0.1), t(32, std=0.1), t(64, std=0.1)
+
+    @fd.graph
+    def block(x, w1, s1, b1, w2, s2, b2, w3, s3, b3):
+        y = fd.relu(fd.bias_add(fd.conv2d(x, w1) * s1, b1))
+        y = fd.relu(fd.bias_add(fd.conv2d(y, w2, padding=1) * s2, b2))
+        y = fd.bias_add(fd.conv2d(y, w3) * s3, b3)
+        return fd.relu(y + x)
+
+    args = [x, w1, s1, b1, w2, s2, b2, w3, s3, b3]
+    plain = fd.compile(block, inputs=args, options={"cache": None})
+    assert [n.op_type for n in plain.graph.nodes] == ["fused_conv2d_bias_relu", "fused_conv2d_bias_relu", "conv2d", "add", "relu"]
+    graphed = fd.compile(block, inputs=args, options={"cache": None, "cuda_graph": True})
+    expect = plain.run(*args)
+    for _ in range(3):
+        got = graphed.run(*args)
+    assert torch.equal(got, expect)
+    x2 = (x * 0.5).contiguous(memory_format=torch.channels_last)
+    assert torch.equal(graphed.run(x2, *args[1:]), plain.run(x2, *args[1:]))
+
+    def cpu_conv(inp, w, s, b, relu, pad=0):
+        return oracle.conv2d_torch_cpu(inp, w, b, 1, pad, 1, 1, scale=s.reshape(-1), relu=relu).to(torch.bfloat16)
+
+    y = cpu_conv(x, w1, s1, b1, True)
+    y = cpu_conv(y, w2, s2, b2, True, pad=1)
+    y = cpu_conv(y, w3, s3, b3, False)
+    ref = torch.relu(y.float() + x.float().cpu())
+    torch.testing.assert_close(expect.float().cpu(), ref, rtol=2e-2, atol=3e-2)

@@ -37,6 +37,16 @@ def test_argument_checks_match_reference(kwargs, exc, msg):
         flag_dnn.conv2d(args["x"], args["w"], args["b"], args["stride"], args["padding"], args["dilation"], args["groups"])
 
 
+def test_conv1d_argument_checks():
+    x, w = torch.randn(2, 3, 16), torch.randn(4, 3, 3)
+    with pytest.raises(NotImplementedError, match="only supports CUDA"):
+        flag_dnn.conv1d(x, w)
+    with pytest.raises(RuntimeError, match="2D/3D input and 3D weight"):
+        flag_dnn.conv1d(torch.randn(2, 3, 4, 4), w)
+    with pytest.raises(RuntimeError, match="length-1 tuple"):
+        flag_dnn.conv1d(x, w, stride=(1, 1))
+
+
 def test_graph_capture_fuses_bias_relu_and_eliminates_dead_node():
     @flag_dnn.graph
     def fn(x, bias):

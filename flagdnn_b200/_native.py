@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "fdnn_conv2d_query",
     "fdnn_conv2d_pack_weight",
     "fdnn_conv2d_fwd",
+    "fdnn_conv2d_fwd_residual",
     "fdnn_conv2d_fwd_host",
     "fdnn_conv2d_host_arena_bytes",
     "fdnn_device_status",
@@ -111,6 +112,8 @@ def load() -> ctypes.CDLL:
     lib.fdnn_conv2d_pack_weight.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, i64, vp]
     lib.fdnn_conv2d_fwd.restype = i32
     lib.fdnn_conv2d_fwd.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, i32, vp, vp, i64, vp]
+    lib.fdnn_conv2d_fwd_residual.restype = i32
+    lib.fdnn_conv2d_fwd_residual.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.fdnn_conv2d_fwd_host.restype = i32
     lib.fdnn_conv2d_fwd_host.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.fdnn_conv2d_host_arena_bytes.restype = i32

@@ -203,7 +203,7 @@ def _empty_output(input, n, c_out, oh, ow, meta=False):
     )
 
 
-def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activation) -> torch.Tensor:
+def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activation, residual=None) -> torch.Tensor:
     n, _, h, w = input.shape
     c_out, _, kh, kw = weight.shape
     oh = _conv_out_dim(h, padding4[0], padding4[1], dilation[0], kh, stride[0])
@@ -221,6 +221,10 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         out = _empty_output(input, n, c_out, oh, ow)
         if n == 0:
             return out
+        if residual is not None:
+            if residual.shape != out.shape or residual.dtype != out.dtype or residual.device != out.device:
+                raise RuntimeError("residual must have the shape, dtype and device of the convolution's output")
+            fusable = (residual.stride() == out.stride() and residual.data_ptr() % 16 == out.data_ptr() % 16)
         d, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups, _FORCED_ALGO)
         stream = torch.cuda.current_stream().cuda_stream
         packed_ptr = None
@@ -233,11 +237,24 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         if plan.workspace_bytes > 0:
             ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=input.device)
             ws_ptr = ws.data_ptr()
+        if residual is not None and fusable and not plan.low_channel:
+            nat.check(lib.fdnn_conv2d_fwd_residual(
+                ctypes.byref(d), input.data_ptr(), weight.data_ptr(), packed_ptr,
+                None if bias is None else bias.data_ptr(),
+                None if scale is None else scale.data_ptr(),
+                residual.data_ptr(), activation, out.data_ptr(), ws_ptr, plan.workspace_bytes, stream))
+            return out
         nat.check(lib.fdnn_conv2d_fwd(
             ctypes.byref(d), input.data_ptr(), weight.data_ptr(), packed_ptr,
             None if bias is None else bias.data_ptr(),
             None if scale is None else scale.data_ptr(),
-            activation, out.data_ptr(), ws_ptr, plan.workspace_bytes, stream))
+            activation if residual is None else nat.ACT_NONE, out.data_ptr(), ws_ptr, plan.workspace_bytes, stream))
+        if residual is not None:
+            # the residual's layout differs from the output's (or the low-channel path ran): the add
+            # and the activation follow as device-side elementwise steps
+            out.add_(residual)
+            if activation == nat.ACT_RELU:
+                out.relu_()
         # `ws` goes back to torch's caching allocator when this frame ends; the
         # allocator orders reuse on the stream the kernels were queued on.
     return out
@@ -325,18 +342,25 @@ def conv2d_bias_act(
     groups: int = 1,
     scale: Optional[torch.Tensor] = None,
     relu: bool = False,
+    residual: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """conv2d with the full epilogue (scale, bias, ReLU) and conv2d's argument
-    range (any groups, fp64).  The graph executor uses it for fused nodes that
-    fall outside ``fused_conv2d_bias_relu``'s contract."""
+    """conv2d with the full epilogue (scale, bias, residual add, ReLU) and conv2d's
+    argument range (any groups, fp64): ``act(conv(x, w) * scale + bias + residual)``
+    computed in fp32 and rounded once.  The graph executor uses it for fused nodes
+    that fall outside ``fused_conv2d_bias_relu``'s contract and for a block's last
+    convolution with its shortcut add (``residual`` has the output's shape; when it
+    also has the output's strides the add happens in the kernel's epilogue)."""
     stride = _pair(stride)
     dilation = _pair(dilation)
     padding4 = _normalize_padding(weight, stride, padding, dilation)
     _check_conv2d_inputs(input, weight, bias, stride, padding4, dilation, groups)
     if not input.is_cuda:
         raise NotImplementedError("flag_dnn conv2d CUDA implementation requires CUDA input")
+    if scale is not None and (scale.dtype != input.dtype or scale.device != input.device
+                              or scale.dim() != 1 or scale.numel() != weight.shape[0]):
+        raise RuntimeError("scale must be a 1D tensor of length C_out with the dtype and device of input")
     return _run(input, weight, bias, scale, stride, padding4, dilation, groups,
-                nat.ACT_RELU if relu else nat.ACT_NONE)
+                nat.ACT_RELU if relu else nat.ACT_NONE, residual)
 
 
 def conv1d(

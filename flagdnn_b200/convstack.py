@@ -83,8 +83,13 @@ def make_layer_params(layer: ConvLayer, seed: int, device, dtype=torch.bfloat16)
     return w, scale.to(dtype).to(device), bias.to(dtype).to(device)
 
 
-def run_layer(layer: ConvLayer, x: torch.Tensor, params) -> torch.Tensor:
+def run_layer(layer: ConvLayer, x: torch.Tensor, params, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One convolution with its folded scale and bias; with ``residual`` the block's shortcut add and
+    the ReLU after it happen in the same kernel (the layer's own ``relu`` flag is then moot)."""
     w, scale, bias = params
+    if residual is not None:
+        return conv_host.conv2d_bias_act(x, w, bias, stride=layer.stride, padding=layer.pad, scale=scale,
+                                         relu=True, residual=residual)
     return conv_host.fused_conv2d_bias_relu(x, w, bias, stride=layer.stride, padding=layer.pad, scale=scale,
                                             activation="relu" if layer.relu else "none")
 
@@ -97,27 +102,32 @@ class ResNet50ConvStack:
         self.params = [make_layer_params(l, seed + i, device, dtype) for i, l in enumerate(self.layers)]
         self.device, self.dtype = device, dtype
 
-    def forward(self, x: torch.Tensor, conv=run_layer, collect: Optional[list] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, conv=run_layer, collect: Optional[list] = None,
+                fuse_residual: bool = False) -> torch.Tensor:
         """x: [N, 3, H, W] channels-last.  ``conv(layer, x, params)`` computes one convolution
-        (the library by default; tests pass an oracle).  ``collect`` receives (layer, input, output)."""
-        it = iter(zip(self.layers, self.params))
-
-        def step(inp):
-            layer, params = next(it)
-            out = conv(layer, inp, params)
+        (the library by default; tests pass an oracle).  ``collect`` receives (layer, input, output).
+        With ``fuse_residual`` each block's third convolution takes the shortcut as its residual
+        (``conv(layer, x, params, residual=...)``), so only the max-pool is left to torch."""
+        def step(index, inp, residual=None):
+            layer, params = self.layers[index], self.params[index]
+            out = conv(layer, inp, params) if residual is None else conv(layer, inp, params, residual=residual)
             if collect is not None:
                 collect.append((layer, inp, out))
-            return layer, out
+            return out
 
-        _, y = step(x)
+        y = step(0, x)
         y = torch.nn.functional.max_pool2d(y, 3, 2, 1)
+        index = 1
         for blocks in (3, 4, 6, 3):
             for block in range(blocks):
                 identity = y
-                _, t = step(y)
-                _, t = step(t)
-                _, t = step(t)
+                t = step(index, y)
+                t = step(index + 1, t)
                 if block == 0:
-                    _, identity = step(identity)
-                y = torch.relu(t + identity)
+                    identity = step(index + 3, y)          # projection shortcut
+                if fuse_residual:
+                    y = step(index + 2, t, residual=identity)
+                else:
+                    y = torch.relu(step(index + 2, t) + identity)
+                index += 4 if block == 0 else 3
         return y

@@ -645,22 +645,32 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, void* pac
 }
 
 static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
-                    const void* bias, const void* scale, int activation, void* y, void* workspace,
-                    int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real);
+                    const void* bias, const void* scale, const void* residual, int activation, void* y,
+                    void* workspace, int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real);
 
 int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
                     const void* bias, const void* scale, int activation, void* y, void* workspace,
                     int64_t workspace_bytes, void* stream_v) {
   if (desc == nullptr) return fail(FDNN_BAD_PARAM, "descriptor is NULL");
-  return fwd_impl(desc, x, w, w_packed, bias, scale, activation, y, workspace, workspace_bytes, stream_v, true,
-                  desc->k);
+  return fwd_impl(desc, x, w, w_packed, bias, scale, nullptr, activation, y, workspace, workspace_bytes, stream_v,
+                  true, desc->k);
+}
+
+int fdnn_conv2d_fwd_residual(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
+                             const void* bias, const void* scale, const void* residual, int activation, void* y,
+                             void* workspace, int64_t workspace_bytes, void* stream_v) {
+  if (desc == nullptr) return fail(FDNN_BAD_PARAM, "descriptor is NULL");
+  if (residual != nullptr && (reinterpret_cast<uintptr_t>(residual) & 15u) != (reinterpret_cast<uintptr_t>(y) & 15u))
+    return fail(FDNN_NOT_SUPPORTED, "the residual must have y's alignment modulo 16 bytes");
+  return fwd_impl(desc, x, w, w_packed, bias, scale, residual, activation, y, workspace, workspace_bytes, stream_v,
+                  true, desc->k);
 }
 
 // k_real: length of bias / scale (differs from desc->k only for the equivalent convolution of a
 // pixel-grouped layer, whose GEMM column j uses entry j % k_real).
 static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
-                    const void* bias, const void* scale, int activation, void* y, void* workspace,
-                    int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real) {
+                    const void* bias, const void* scale, const void* residual, int activation, void* y,
+                    void* workspace, int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real) {
   fdnn_conv_plan plan;
   // A caller that hands over a packed filter wants it used even when w itself
   // would qualify for in-place reads; plan accordingly.
@@ -687,7 +697,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
       p.w_s[i] = d.w_strides[i];
       p.y_s[i] = d.y_strides[i];
     }
-    p.x = x; p.w = w; p.bias = bias; p.scale = scale; p.y = y;
+    p.x = x; p.w = w; p.bias = bias; p.scale = scale; p.residual = residual; p.y = y;
     p.relu = activation == FDNN_ACT_RELU;
     cudaError_t e = launch_direct(d.dtype, p, stream);
     if (e != cudaSuccess) return fail_cuda("direct conv launch", e);
@@ -726,9 +736,11 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (plan.pixel_group > 1) {
     // run the equivalent convolution; its filter is the packed buffer, consumed in place
     const fdnn_conv_desc v = grouped_desc(&d, plan.pixel_group, plan.oh, plan.ow);
-    return fwd_impl(&v, x, w_packed, nullptr, bias, scale, activation, y, workspace, workspace_bytes, stream_v,
-                    false, d.k);
+    return fwd_impl(&v, x, w_packed, nullptr, bias, scale, residual, activation, y, workspace, workspace_bytes,
+                    stream_v, false, d.k);
   }
+  if (plan.low_channel && residual != nullptr)
+    return fail(FDNN_NOT_SUPPORTED, "the low-channel path takes no residual; add it in a separate step");
   if (plan.low_channel) return fwd_low_channel(d, plan, dev, x, w_packed, bias, scale, activation, y, workspace, stream);
 
   const int es = elem_size(d.dtype);
@@ -798,6 +810,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   p.n_tiles = (d.k + plan.tile_n - 1) / plan.tile_n;
   p.y_sn = d.y_strides[0]; p.y_sk = d.y_strides[1]; p.y_sh = d.y_strides[2]; p.y_sw = d.y_strides[3];
   p.bias = bias; p.scale = scale; p.y = y;
+  p.residual = residual;
   p.relu = activation == FDNN_ACT_RELU;
   const int gran = 16 / es;
   p.vec_store = (d.y_strides[1] == 1 && d.y_strides[0] % gran == 0 && d.y_strides[2] % gran == 0 &&

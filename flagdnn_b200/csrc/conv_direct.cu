@@ -73,8 +73,10 @@ conv_direct_kernel(const DirectParams p, const bool k_fastest) {
     }
     if (scale != nullptr) acc *= ld<T, A>(scale + k);
     if (bias != nullptr) acc += ld<T, A>(bias + k);
+    const long long y_idx = n * p.y_s[0] + k * p.y_s[1] + oh * p.y_s[2] + ow * p.y_s[3];
+    if (p.residual != nullptr) acc += ld<T, A>(static_cast<const T*>(p.residual) + y_idx);
     if (p.relu) acc = (acc < A(0)) ? A(0) : acc;
-    y[n * p.y_s[0] + k * p.y_s[1] + oh * p.y_s[2] + ow * p.y_s[3]] = cvt<T, A>(acc);
+    y[y_idx] = cvt<T, A>(acc);
   }
 }
 

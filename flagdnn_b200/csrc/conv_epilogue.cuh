@@ -2,7 +2,8 @@
 // drains its 32 accumulator rows from tensor memory, applies per-channel scale,
 // bias and ReLU in fp32, rounds once, stages 32 rows x 128 bytes in shared
 // memory and hands each box to a TMA store.  The arithmetic is that of the
-// reference's fused kernel (src/flag_dnn/graph/kernels/fused_conv.py:297-310).
+// reference's fused kernel (src/flag_dnn/graph/kernels/fused_conv.py:297-310),
+// plus an optional residual tensor added in fp32 before the activation.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -33,6 +34,43 @@ __device__ __forceinline__ uint32_t round_pack2<__nv_bfloat16>(float a, float b)
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Two packed 16-bit values -> fp32 (identity for fp32 words is handled by the caller).
+template <typename T>
+__device__ __forceinline__ void unpack2(uint32_t w, float& a, float& b);
+template <>
+__device__ __forceinline__ void unpack2<__half>(uint32_t w, float& a, float& b) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  a = f.x;
+  b = f.y;
+}
+template <>
+__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& a, float& b) {
+  a = __uint_as_float(w << 16);
+  b = __uint_as_float(w & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack2<float>(uint32_t w, float& a, float& b) {
+  a = __uint_as_float(w);
+  b = 0.0f;
+}
+
+// The 128 bytes of one row of the residual tensor that line up with one staged output row:
+// `src` points at column `col0` of this lane's row (nullptr: row outside the tensor, reads zeros).
+// Columns at or beyond `kout` read zeros; kout is a multiple of the 16-byte piece.
+template <typename T>
+__device__ __forceinline__ void load_residual_row(const T* src, int col0, int kout, uint32_t (&res)[32]) {
+  constexpr int kPiece = 16 / int(sizeof(T));
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (src != nullptr && col0 + q * kPiece < kout) v = __ldg(reinterpret_cast<const uint4*>(src + q * kPiece));
+    res[4 * q + 0] = v.x;
+    res[4 * q + 1] = v.y;
+    res[4 * q + 2] = v.z;
+    res[4 * q + 3] = v.w;
+  }
+}
+
 // t_row     tensor-memory address of this warp's lane quarter, first column of the tile
 // n0        first GEMM column of the tile; kout: number of valid GEMM columns overall
 // s_scale / s_bias  this warp's fp32 copies for columns n0 .. n0+BN-1
@@ -41,12 +79,17 @@ __device__ __forceinline__ uint32_t round_pack2<__nv_bfloat16>(float a, float b)
 // tm_full / tm_tail  output maps with a 32-row box and a box of the tile's ragged last rows
 // st_row, st_img     y coordinates (row, image) of the warp's first row; st_rows: valid rows (<= 0: none)
 // store_seq          running count of this warp's staged boxes (selects the staging buffer)
-template <typename T, int BN>
+// RES                a residual tensor (same layout as y) is added before the activation
+// res_row            this lane's residual row at column n0 (nullptr for a row outside the tensor)
+// res                the residual row of the first column group, loaded by the caller before it
+//                    waited for the accumulator so that the load hides behind the main loop
+template <typename T, int BN, bool RES = false>
 __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int relu,
                                                     const float* s_scale, const float* s_bias,
                                                     uint8_t* my_out, int lane, const CUtensorMap* tm_full,
                                                     const CUtensorMap* tm_tail, int st_row, int st_img,
-                                                    int st_rows, uint32_t& store_seq) {
+                                                    int st_rows, uint32_t& store_seq,
+                                                    const T* res_row = nullptr, uint32_t* res = nullptr) {
   constexpr int kPerStore = 128 / int(sizeof(T));  // channels per staged row: 64 (16-bit) or 32 (fp32)
   constexpr int kLoads = kPerStore / 32;
   int groups = (kout - n0 + kPerStore - 1) / kPerStore;
@@ -57,6 +100,11 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
   for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + l * 32, raw[l]);
 #pragma unroll 1
   for (int g = 0; g < groups; ++g) {
+    uint32_t res_next[32];
+    if (RES && g + 1 < groups) {
+      load_residual_row<T>(res_row != nullptr ? res_row + (g + 1) * kPerStore : nullptr,
+                           n0 + (g + 1) * kPerStore, kout, res_next);
+    }
     tmem_ld_wait();
     uint32_t row[32];  // the 128 bytes this lane contributes
 #pragma unroll
@@ -70,6 +118,22 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
         float v1 = fmaf(__uint_as_float(raw[l][4 * j4 + 1]), sc.y, bi.y);
         float v2 = fmaf(__uint_as_float(raw[l][4 * j4 + 2]), sc.z, bi.z);
         float v3 = fmaf(__uint_as_float(raw[l][4 * j4 + 3]), sc.w, bi.w);
+        if constexpr (RES) {
+          if constexpr (std::is_same<T, float>::value) {
+            v0 += __uint_as_float(res[4 * j4 + 0]);
+            v1 += __uint_as_float(res[4 * j4 + 1]);
+            v2 += __uint_as_float(res[4 * j4 + 2]);
+            v3 += __uint_as_float(res[4 * j4 + 3]);
+          } else {
+            float r0, r1, r2, r3;
+            unpack2<T>(res[l * 16 + 2 * j4 + 0], r0, r1);
+            unpack2<T>(res[l * 16 + 2 * j4 + 1], r2, r3);
+            v0 += r0;
+            v1 += r1;
+            v2 += r2;
+            v3 += r3;
+          }
+        }
         if (relu) {
           v0 = relu_keep_nan(v0);
           v1 = relu_keep_nan(v1);
@@ -91,6 +155,10 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
     if (g + 1 < groups) {
 #pragma unroll
       for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + (g + 1) * kPerStore + l * 32, raw[l]);
+    }
+    if (RES && g + 1 < groups) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) res[j] = res_next[j];
     }
     uint8_t* buf = my_out + (store_seq & 1u) * (32 * 128);  // alternates across groups AND tiles
     ++store_seq;

@@ -52,7 +52,7 @@ static_assert(kStages * kStageBytes <= kRingBytes, "streaming ring must fit");
 constexpr uint32_t kTmemColsPair = 512;              // two 256-column accumulators
 static_assert(kSmemPair <= 227 * 1024, "shared memory budget");
 
-template <typename T>
+template <typename T, bool RES>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmY2,
@@ -260,6 +260,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     float* s_bias = s_scale + kPairN;
     const T* g_bias = static_cast<const T*>(p.bias);
     const T* g_scale = static_cast<const T*>(p.scale);
+    const T* g_res = (RES && !p.lowc) ? static_cast<const T*>(p.residual) : nullptr;
     uint8_t* my_out = out_stage + (warp - 2) * 2 * 32 * kRowB;
     const uint32_t tempty_leader = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     uint32_t tcount = 0;
@@ -281,11 +282,25 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         __syncwarp();
         staged_n_tile = n_tile;
       }
+      const int m_tile = 2 * m_pair + int(rank);
+      // the residual row of the first column group is requested before the accumulator wait
+      const T* res_row = nullptr;
+      uint32_t res0[32];
+      if (RES && g_res != nullptr) {
+        const int m = m_tile * kRows + ew * 32 + lane;
+        if (m < p.M) {
+          const int ohw = p.OH * p.OW;
+          const int img = m / ohw;
+          const int rem = m - img * ohw;
+          const int oh = rem / p.OW;
+          res_row = g_res + img * p.y_sn + oh * p.y_sh + (rem - oh * p.OW) * p.y_sw + n0;
+        }
+        load_residual_row<T>(res_row, n0, p.Kout, res0);
+      }
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int m_tile = 2 * m_pair + int(rank);
       int st_row, st_img, st_rows;
       if (p.lowc) {
         st_img = m_tile / p.tiles_per_image;
@@ -297,8 +312,8 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         st_rows = 32;
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN;
-      epilogue_store_tile<T, kPairN>(t_row, n0, p.Kout, p.relu, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
-                                     st_row, st_img, st_rows, store_seq);
+      epilogue_store_tile<T, kPairN, RES>(t_row, n0, p.Kout, p.relu, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
+                                     st_row, st_img, st_rows, store_seq, res_row, res0);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }
@@ -331,17 +346,25 @@ cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T>, tmA, tmB, tmY, tmY2, p);
+  if (p.residual != nullptr) return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, true>, tmA, tmB, tmY, tmY2, p);
+  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, false>, tmA, tmB, tmY, tmY2, p);
 }
 
 }  // namespace
 
 cudaError_t igemm_pair_prepare_device() {
-  cudaError_t e = cudaFuncSetAttribute(conv_igemm_pair_kernel<__half>,
+  cudaError_t e = cudaFuncSetAttribute(conv_igemm_pair_kernel<__half, false>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPair);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(conv_igemm_pair_kernel<__nv_bfloat16>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPair);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(conv_igemm_pair_kernel<__half, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemPair);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(conv_igemm_pair_kernel<__nv_bfloat16, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPair);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(conv_igemm_pair_kernel<__nv_bfloat16, true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemPair);
+  return e;
 }
 
 int igemm_pair_smem_bytes() { return kSmemPair; }

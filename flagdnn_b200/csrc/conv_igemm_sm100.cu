@@ -84,7 +84,7 @@ __device__ __forceinline__ void store32_contig(T* dst, const float (&v)[32]) {
   }
 }
 
-template <typename T, int BN>
+template <typename T, int BN, bool RES>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                   const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
@@ -293,6 +293,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const T* g_bias = static_cast<const T*>(p.bias);
     const T* g_scale = static_cast<const T*>(p.scale);
     T* y = static_cast<T*>(p.y);
+    const T* g_res = (RES && !p.lowc) ? static_cast<const T*>(p.residual) : nullptr;
     uint32_t tcount = 0;
     uint32_t store_seq = 0;
     int staged_n_tile = -1;
@@ -315,13 +316,6 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         staged_n_tile = n_tile;
       }
 
-      const long long et0 = p.prof ? clock64() : 0;
-      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
-      ok = __all_sync(0xffffffffu, ok);
-      if (p.prof) prof_ewait += clock64() - et0;
-      if (!ok) break;
-      tc_fence_after();
-
       const int m = m_tile * kBM + ew * 32 + lane;
       const bool row_ok = m < p.M;
       long long y_off = 0;
@@ -332,6 +326,20 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int ow = rem - oh * p.OW;
         y_off = img * p.y_sn + oh * p.y_sh + ow * p.y_sw;
       }
+      // the residual row of the first column group is requested before the accumulator wait
+      const T* res_row = (g_res != nullptr && row_ok) ? g_res + y_off + n0 : nullptr;
+      uint32_t res0[32];
+      if constexpr (RES) {
+        if (p.tma_store) load_residual_row<T>(res_row, n0, p.Kout, res0);
+      }
+
+      const long long et0 = p.prof ? clock64() : 0;
+      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
+      ok = __all_sync(0xffffffffu, ok);
+      if (p.prof) prof_ewait += clock64() - et0;
+      if (!ok) break;
+      tc_fence_after();
+
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * BN;
       // Where this warp's 32 rows go in y seen as (channel, row, image): the whole
       // output is one "image" outside low-channel mode.
@@ -348,9 +356,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (p.tma_store) {
         // a tile's last warp may own fewer than 32 valid rows: tmA2 then holds a second
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
-        epilogue_store_tile<T, BN>(t_row, n0, p.Kout, p.relu, s_scale, s_bias,
+        epilogue_store_tile<T, BN, RES>(t_row, n0, p.Kout, p.relu, s_scale, s_bias,
                                    out_stage + (warp - 2) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
-                                   st_img, st_rows, store_seq);
+                                   st_img, st_rows, store_seq, res_row, res0);
       } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < BN / 32; ++chunk) {
@@ -364,6 +372,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int j = 0; j < 32; ++j) {
           float a = __uint_as_float(raw[j]);
           a = fmaf(a, s_scale[chunk * 32 + j], s_bias[chunk * 32 + j]);
+          if (RES && g_res != nullptr && row_ok && col0 + j < p.Kout)
+            a += to_f32<T>(g_res[y_off + (long long)(col0 + j) * p.y_sk]);
           if (p.relu) a = (a < 0.0f) ? 0.0f : a;  // keeps NaN, like torch.relu
           v[j] = a;
         }
@@ -401,14 +411,20 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CU
                        const CUtensorMap& tmB2, const CUtensorMap& tmY, const IgemmParams& p, int grid,
                        cudaStream_t stream) {
   using Cfg = TileCfg<T, BN>;
-  conv_igemm_kernel<T, BN><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, tmY, p);
+  if (p.residual != nullptr)
+    conv_igemm_kernel<T, BN, true><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, tmY, p);
+  else
+    conv_igemm_kernel<T, BN, false><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, tmY, p);
   return cudaGetLastError();
 }
 
 template <typename T, int BN>
 cudaError_t prepare_one() {
   using Cfg = TileCfg<T, BN>;
-  return cudaFuncSetAttribute(conv_igemm_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(conv_igemm_kernel<T, BN, false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(conv_igemm_kernel<T, BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               Cfg::kSmemBytes);
 }
 

@@ -26,6 +26,7 @@ struct IgemmParams {
   const void* bias;      // [Kout] in the tensor dtype, or nullptr
   const void* scale;     // [Kout] in the tensor dtype, or nullptr
   void* y;
+  const void* residual;  // tensor with y's dtype and strides added before the activation, or nullptr
   int relu;
   int vec_store;         // 1: y is channel-contiguous and 16-byte aligned per pixel
   int tma_store;         // 1: y is dense NHWC; the epilogue writes it through the tmY tensor map
@@ -74,6 +75,7 @@ struct DirectParams {
   const void* w;
   const void* bias;
   const void* scale;
+  const void* residual;  // same dtype and strides as y, or nullptr
   void* y;
   int relu;
 };

@@ -2,9 +2,11 @@
 
 The fusion pass reproduces the reference's three rewrites
 (src/flag_dnn/graph/passes/fusion.py:40-160) with the same preconditions and
-the same statistics keys, and adds one the reference cannot express: a
+the same statistics keys, and adds two the reference cannot express: a
 per-channel multiply between the convolution and the bias (a BatchNorm folded
-into scale and bias) is absorbed into the fused node as a fourth input.
+into scale and bias) is absorbed into the fused node as a fourth input, and a
+residual block's tail, relu(conv(...) + shortcut), becomes one node whose add
+and ReLU run in the convolution's epilogue.
 """
 from __future__ import annotations
 
@@ -31,6 +33,7 @@ def apply_fusion_pass(graph: Graph) -> Graph:
         (_fold_conv_scale_bias, "conv2d_scale_bias_folded"),
         (_fold_conv_bias, "conv2d_bias_folded"),
         (_fuse_bias_relu, "bias_activation_fused"),
+        (_fuse_conv_add_relu, "conv2d_residual_activation_fused"),
     )
     changed = True
     while changed:
@@ -168,4 +171,38 @@ def _fuse_bias_relu(graph: Graph) -> bool:
                        outputs=list(act.outputs), attrs=attrs, name="fused_bias_relu")
         graph.replace_nodes_with([bias_node.id, act.id], fused)
         return True
+    return False
+
+
+def _fuse_conv_add_relu(graph: Graph) -> bool:
+    """relu(add(conv2d(...), shortcut)) -> fused_conv2d_bias_add_relu(x, w, shortcut[, bias[, scale]]).
+
+    Runs after the folding rules (it is last in the rule list), so the convolution already carries
+    its bias and scale.  The shortcut must have exactly the convolution's output shape and dtype.
+    """
+    for act in list(graph.nodes):
+        if act.op_type != "relu" or len(act.inputs) != 1 or len(act.outputs) != 1:
+            continue
+        add_node = _single_use_producer(graph, act.inputs[0], "add")
+        if add_node is None or len(add_node.inputs) != 2 or add_node.attrs.get("alpha", 1) != 1:
+            continue
+        for conv_slot in (0, 1):
+            conv_value, other = add_node.inputs[conv_slot], add_node.inputs[1 - conv_slot]
+            conv_node = _single_use_producer(graph, conv_value, "conv2d")
+            if conv_node is None or conv_value == other:
+                continue
+            conv_spec, other_spec = graph.values[conv_value].spec, graph.values[other].spec
+            if tuple(conv_spec.shape) != tuple(other_spec.shape) or conv_spec.dtype != other_spec.dtype:
+                continue
+            attrs = dict(conv_node.attrs)
+            attrs["activation"] = "relu"
+            inputs = [conv_node.inputs[0], conv_node.inputs[1], other] + list(conv_node.inputs[2:])
+            fused = OpNode(id=graph.new_node_id(), op_type="fused_conv2d_bias_add_relu", inputs=inputs,
+                           outputs=list(act.outputs), attrs=attrs, name="fused_conv2d_bias_add_relu")
+            # the fused node stands where the add stood: both of its producers come before that
+            graph.nodes.insert(graph.nodes.index(add_node), fused)
+            for vid in fused.outputs:
+                graph.values[vid].producer = fused.id
+            graph.remove_nodes([conv_node.id, add_node.id, act.id])
+            return True
     return False

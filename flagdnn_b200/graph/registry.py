@@ -152,6 +152,27 @@ def _run_fused_conv2d_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
                                       scale=scale, relu=True, **kw)
 
 
+def _run_fused_conv2d_bias_add_relu(inputs: list, attrs: dict) -> torch.Tensor:
+    """inputs: x, w, residual[, bias[, scale]]; relu(conv * scale + bias + residual) in one kernel."""
+    from .. import conv_host as native
+
+    _require_device(inputs, "fused_conv2d_bias_add_relu")
+    a = _public(attrs)
+    bias = inputs[3] if len(inputs) > 3 else None
+    scale = inputs[4].reshape(-1) if len(inputs) > 4 else None
+    return native.conv2d_bias_act(inputs[0], inputs[1], bias, stride=a.get("stride", 1), padding=a.get("padding", 0),
+                                  dilation=a.get("dilation", 1), groups=a.get("groups", 1), scale=scale,
+                                  relu=a.get("activation", "relu") == "relu", residual=inputs[2])
+
+
+def _normalize_conv2d_residual(ctx: Any, args: tuple, kwargs: dict) -> tuple:
+    raise NotImplementedError("fused_conv2d_bias_add_relu nodes are created by the fusion pass only")
+
+
+def _infer_conv2d_residual(specs: list, attrs: dict) -> TensorSpec:
+    return _infer_conv2d([specs[0], specs[1]], attrs)
+
+
 # -------------------------------------------------------------- glue ops
 def _normalize_unary(name: str):
     def normalize(ctx: Any, args: tuple, kwargs: dict) -> tuple:
@@ -222,6 +243,8 @@ def _binary_runner(fn):
 def _register_defaults() -> None:
     register_op(OpSchema("conv2d", _normalize_conv2d, _infer_conv2d, _run_conv2d))
     register_op(OpSchema("fused_conv2d_bias_relu", _normalize_conv2d, _infer_conv2d, _run_fused_conv2d_bias_relu))
+    register_op(OpSchema("fused_conv2d_bias_add_relu", _normalize_conv2d_residual, _infer_conv2d_residual,
+                         _run_fused_conv2d_bias_add_relu))
     register_op(OpSchema("bias_add", _normalize_binary("bias_add"), _infer_same, _run_bias_add))
     register_op(OpSchema("relu", _normalize_unary("relu"), _infer_same, _run_relu))
     register_op(OpSchema("fused_bias_relu", _normalize_binary("fused_bias_relu"), _infer_same, _run_fused_bias_relu))

@@ -132,6 +132,21 @@ int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w,
                     int activation, void* y, void* workspace,
                     int64_t workspace_bytes, void* stream);
 
+/* y = act( conv(x, w) * scale[k] + bias[k] + residual ): fdnn_conv2d_fwd with a
+ * residual tensor added in fp32 before the activation and the single rounding
+ * (a ResNet block's third convolution, its shortcut add and the ReLU in one
+ * pass; the reference runs them as separate nodes, src/flag_dnn/ops/binary.py:380
+ * after src/flag_dnn/ops/conv2d.py:3575).  `residual` has y's dtype, shape and
+ * strides (desc->y_strides), the same address alignment modulo 16 bytes, and
+ * must not overlap y; NULL makes this fdnn_conv2d_fwd.  The low-channel path
+ * (plan.low_channel) answers FDNN_NOT_SUPPORTED when a residual is given. */
+int fdnn_conv2d_fwd_residual(const fdnn_conv_desc* desc, const void* x,
+                             const void* w, const void* w_packed,
+                             const void* bias, const void* scale,
+                             const void* residual, int activation, void* y,
+                             void* workspace, int64_t workspace_bytes,
+                             void* stream);
+
 /* Host-buffer convenience: same as fdnn_conv2d_fwd but x, w, bias, scale and y
  * are HOST pointers (dense, described by the strides in `desc`); copies in,
  * runs and copies y back on `stream`, using the caller-provided device arena

@@ -342,6 +342,70 @@ def test_pixel_grouped_narrow_layers_match_oracle(fd, case):
     assert torch.equal(alone, got[3:4])
 
 
+RESIDUAL = [
+    # name, (n, c, hw, k, r, stride, pad, groups), dtype, channels_last, algo, residual layout matches
+    ("nhwc_bf16", (6, 64, 28, 256, 1, 1, 0, 1), "bfloat16", True, "igemm", True),
+    ("nhwc_f16_ragged_k", (3, 40, 19, 72, 3, 1, 1, 1), "float16", True, "igemm", True),   # 72 columns: partial group
+    ("nhwc_f32", (2, 32, 17, 96, 3, 2, 1, 1), "float32", True, "igemm", True),
+    ("pair_bf16", (5, 128, 20, 512, 1, 1, 0, 1), "bfloat16", True, "pair", True),
+    ("nchw_bf16", (3, 24, 15, 40, 3, 1, 1, 1), "bfloat16", False, "igemm", True),          # strided per-element epilogue
+    ("nchw_f32", (2, 16, 12, 20, 3, 1, 1, 1), "float32", False, "igemm", True),
+    ("direct_groups", (2, 16, 12, 24, 3, 1, 1, 4), "float16", True, "auto", True),
+    ("direct_f64", (2, 8, 9, 12, 3, 1, 1, 1), "float64", False, "auto", True),
+    ("grouped_pixels", (20, 64, 56, 64, 3, 1, 1, 1), "bfloat16", True, "auto", True),      # pixel-grouped layer
+    ("low_channel", (4, 3, 64, 32, 7, 2, 3, 1), "bfloat16", True, "auto", True),           # separate add + ReLU steps
+    ("other_layout", (3, 64, 14, 128, 1, 1, 0, 1), "bfloat16", True, "igemm", False),      # NCHW shortcut, NHWC output
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", RESIDUAL, ids=[c[0] for c in RESIDUAL])
+def test_residual_add_in_the_epilogue(fd, case):
+    """act(conv * scale + bias + shortcut) against the fp32/fp64 CPU answer for the same bits."""
+    _, (n, c, hw, k, r, stride, pad, groups), dtype_name, channels_last, algo, same_layout = case
+    dtype = getattr(torch, dtype_name)
+    x = _to_dev(_rand((n, c, hw, hw), 90), dtype, channels_last)
+    w = _to_dev(_rand((k, c // groups, r, r), 91, std=(c // groups * r * r) ** -0.5), dtype, channels_last)
+    b = _rand((k,), 92, std=0.1).to(dtype).cuda()
+    sc = (torch.rand(k, generator=torch.Generator().manual_seed(93)) + 0.5).to(dtype).cuda()
+    oh = (hw + 2 * pad - r) // stride + 1
+    shortcut = _to_dev(_rand((n, k, oh, oh), 94), dtype, channels_last == same_layout)
+    fd.set_algo(algo)
+    try:
+        for relu in (True, False):
+            for use_scale, use_bias in ((True, True), (False, False)):
+                got = fd.conv2d_bias_act(x, w, b if use_bias else None, stride=stride, padding=pad, groups=groups,
+                                         scale=sc if use_scale else None, relu=relu, residual=shortcut)
+                cdt = torch.float64 if dtype_name == "float64" else torch.float32
+                ref = oracle.conv2d_torch_cpu(x, w, b if use_bias else None, stride, pad, 1, groups,
+                                              scale=sc if use_scale else None, compute_dtype=cdt)
+                ref = ref + shortcut.cpu().to(cdt)
+                if relu:
+                    ref = torch.relu(ref)
+                _check(got, ref, dtype_name)
+                assert got.stride() == fd.conv2d(x, w, None, stride, pad, 1, groups).stride()
+    finally:
+        fd.set_algo("auto")
+
+
+@pytest.mark.gpu
+def test_residual_contract(fd):
+    x = torch.randn(2, 16, 8, 8, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(24, 16, 3, 3, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="residual must have the shape"):
+        fd.conv2d_bias_act(x, w, None, padding=1, residual=torch.zeros(2, 24, 8, 7, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="residual must have the shape"):
+        fd.conv2d_bias_act(x, w, None, padding=1, residual=torch.zeros(2, 24, 8, 8, device="cuda", dtype=torch.float16))
+    # NaN in the shortcut survives the ReLU, as torch.relu(conv + shortcut) would keep it
+    shortcut = torch.zeros(2, 24, 8, 8, device="cuda", dtype=torch.bfloat16)
+    shortcut[1, 5, 2, 3] = float("nan")
+    for cl in (True, False):
+        xs = x.contiguous(memory_format=torch.channels_last) if cl else x
+        sh = shortcut.contiguous(memory_format=torch.channels_last) if cl else shortcut
+        out = fd.conv2d_bias_act(xs, w, None, padding=1, relu=True, residual=sh)
+        assert torch.isnan(out[1, 5, 2, 3]) and int(torch.isnan(out).sum()) == 1
+
+
 def test_scaled_graph_folds_into_one_node(fd):
     x = _rand((2, 16, 8, 8), 20).to(torch.float16).cuda().contiguous(memory_format=torch.channels_last)
     w = _rand((24, 16, 3, 3), 21, std=0.08).to(torch.float16).cuda()

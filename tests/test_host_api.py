@@ -169,6 +169,49 @@ def test_graph_scale_pattern_folds_with_and_without_relu():
     assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "mul", "fused_bias_relu"]
 
 
+def test_graph_residual_tail_becomes_one_node():
+    specs = [flag_dnn.TensorSpec("x", (2, 8, 8, 8), "bfloat16"), flag_dnn.TensorSpec("w", (8, 8, 1, 1), "bfloat16"),
+             flag_dnn.TensorSpec("s", (8, 1, 1), "bfloat16"), flag_dnn.TensorSpec("b", (8,), "bfloat16"),
+             flag_dnn.TensorSpec("wp", (8, 8, 1, 1), "bfloat16")]
+
+    @flag_dnn.graph
+    def identity_block(x, w, s, b, wp):
+        return flag_dnn.relu(x + flag_dnn.bias_add(flag_dnn.conv2d(x, w) * s, b))    # conv on the right of the add
+
+    compiled = flag_dnn.compile(identity_block, inputs=specs, options={"cache": None})
+    nodes = compiled.graph.nodes
+    assert [n.op_type for n in nodes] == ["fused_conv2d_bias_add_relu"]
+    g = compiled.graph
+    assert nodes[0].inputs[:3] == [g.inputs[0], g.inputs[1], g.inputs[0]]            # x, w, shortcut = x
+    assert nodes[0].inputs[3:] == [g.inputs[3], g.inputs[2]]                         # bias, scale
+    assert compiled.plan.debug_info["fusion"]["conv2d_residual_activation_fused"] == 1
+
+    @flag_dnn.graph
+    def projection_block(x, w, s, b, wp):
+        main = flag_dnn.bias_add(flag_dnn.conv2d(x, w) * s, b)
+        return flag_dnn.relu(main + flag_dnn.conv2d(x, wp))     # shortcut produced after the main convolution
+
+    compiled = flag_dnn.compile(projection_block, inputs=specs, options={"cache": None})
+    kinds = [n.op_type for n in compiled.graph.topological_nodes()]
+    assert sorted(kinds) == ["conv2d", "fused_conv2d_bias_add_relu"] and kinds[-1] == "fused_conv2d_bias_add_relu"
+    compiled.graph.lint()
+
+    @flag_dnn.graph
+    def broadcast_add(x, w, s, b, wp):
+        return flag_dnn.relu(flag_dnn.conv2d(x, w) + s)          # not a same-shape shortcut: stays unfused
+
+    compiled = flag_dnn.compile(broadcast_add, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "add", "relu"]
+
+    @flag_dnn.graph
+    def shared_conv(x, w, s, b, wp):
+        y = flag_dnn.conv2d(x, w)
+        return flag_dnn.relu(y + x), y                           # the convolution has a second user
+
+    compiled = flag_dnn.compile(shared_conv, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "add", "relu"]
+
+
 def test_graph_memory_plan_cache_hit():
     cache = flag_dnn.PlanCache(enable_disk=False)
 

@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -267,7 +268,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     plan->smem_bytes = igemm_smem_bytes(d->dtype, plan->tile_n);
     const long long tiles_lc = (long long)m_tiles_lc * ((n_gemm + plan->tile_n - 1) / plan->tile_n);
     plan->grid = int(tiles_lc < sms_lc ? tiles_lc : sms_lc);
-    plan->block = 192;
+    plan->block = igemm_threads();
     plan->launches = 2;
     const long long pair_tiles_lc = (long long)((m_tiles_lc + 1) / 2) * ((n_gemm + 255) / 256);
     if (algo == FDNN_ALGO_IGEMM_PAIR ||
@@ -277,6 +278,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
       plan->tile_n = 256;
       plan->stages = igemm_pair_stages();
       plan->smem_bytes = igemm_pair_smem_bytes();
+      plan->block = igemm_pair_threads();
       const long long pairs = pair_tiles_lc < sms_lc / 2 ? pair_tiles_lc : sms_lc / 2;
       plan->grid = int(2 * pairs);
     }
@@ -335,7 +337,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   plan->smem_bytes = igemm_smem_bytes(d->dtype, plan->tile_n);
   const long long tiles = (long long)m_tiles * ((d->k + plan->tile_n - 1) / plan->tile_n);
   plan->grid = int(tiles < sms ? tiles : sms);
-  plan->block = 192;
+  plan->block = igemm_threads();
   plan->launches = 1 + plan->x_repacked;
 
   // CTA pairs: 16-bit types writing a dense NHWC y.  Worth it when the layer is
@@ -352,6 +354,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     plan->tile_n = 256;
     plan->stages = igemm_pair_stages();
     plan->smem_bytes = igemm_pair_smem_bytes();
+    plan->block = igemm_pair_threads();
     const long long pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
     plan->grid = int(2 * pairs);
   }
@@ -467,6 +470,17 @@ __device__ uint32_t g_status_word;
 
 std::once_flag g_prepare_once[64];
 cudaError_t g_prepare_result[64];
+}  // namespace
+
+bool launch_overlap_enabled() {
+  static const bool on = []() {
+    const char* v = std::getenv("FLAGDNN_B200_LAUNCH_OVERLAP");
+    return !(v != nullptr && v[0] == '0' && v[1] == '\0');
+  }();
+  return on;
+}
+
+namespace {
 long long* g_prof_buffer = nullptr;  // set through fdnn_debug_set_profile_buffer
 uint32_t* g_status_ptr[64];  // device address of g_status_word, looked up once per device
 

@@ -74,8 +74,9 @@ __device__ __forceinline__ void load_residual_row(const T* src, int col0, int ko
 // t_row     tensor-memory address of this warp's lane quarter, first column of the tile
 // n0        first GEMM column of the tile; kout: number of valid GEMM columns overall
 // s_scale / s_bias  this warp's fp32 copies for columns n0 .. n0+BN-1
-// my_out    this warp's two 4 KB staging buffers (1024-byte aligned, used in rotation so that
-//           a box can still be leaving through the TMA unit while the next one is staged)
+// my_out    this warp's NBUF 4 KB staging buffers (1024-byte aligned; two are used in rotation so
+//           that a box can still be leaving through the TMA unit while the next one is staged;
+//           with one, the other warp of the lane quarter fills that gap)
 // tm_full / tm_tail  output maps with a 32-row box and a box of the tile's ragged last rows
 // st_row, st_img     y coordinates (row, image) of the warp's first row; st_rows: valid rows (<= 0: none)
 // store_seq          running count of this warp's staged boxes (selects the staging buffer)
@@ -83,7 +84,7 @@ __device__ __forceinline__ void load_residual_row(const T* src, int col0, int ko
 // res_row            this lane's residual row at column n0 (nullptr for a row outside the tensor)
 // res                the residual row of the first column group, loaded by the caller before it
 //                    waited for the accumulator so that the load hides behind the main loop
-template <typename T, int BN, bool RES = false>
+template <typename T, int BN, bool RES = false, int NBUF = 2>
 __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int relu,
                                                     const float* s_scale, const float* s_bias,
                                                     uint8_t* my_out, int lane, const CUtensorMap* tm_full,
@@ -160,9 +161,12 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
 #pragma unroll
       for (int j = 0; j < 32; ++j) res[j] = res_next[j];
     }
-    uint8_t* buf = my_out + (store_seq & 1u) * (32 * 128);  // alternates across groups AND tiles
+    uint8_t* buf = my_out + (NBUF == 2 ? (store_seq & 1u) * (32 * 128) : 0u);  // alternates across groups AND tiles
     ++store_seq;
-    if (lane == 0) bulk_wait_group_read1();  // the box staged two groups ago has left this buffer
+    if (lane == 0) {
+      // the box staged NBUF groups ago has left this buffer
+      if constexpr (NBUF == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
+    }
     __syncwarp();
 #pragma unroll
     for (int q = 0; q < 8; ++q) {

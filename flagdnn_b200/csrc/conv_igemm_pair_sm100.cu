@@ -16,8 +16,9 @@
 //   warp 1 (leader)    issuer: waits "stage full", issues the pair MMAs, commits
 //                      to both CTAs' "stage empty" barriers, and after the last
 //                      step to both CTAs' "accumulator full" barriers
-//   warps 2..5 (each)  epilogue on the CTA's own 128 rows, then an arrive on the
-//                      leader's "accumulator empty" barrier
+//   warps 2..9 (each)  epilogue on the CTA's own 128 rows (two warps per tensor-
+//                      memory lane quarter, half of the columns each), then an
+//                      arrive on the leader's "accumulator empty" barrier
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -43,9 +44,16 @@ constexpr int kStages = 5;                           // streaming mode: 5 x 32 K
 constexpr int kRingBytes = 184 * 1024;               // operand region (stages, or resident filter + A stages)
 constexpr int kMaxStages = 8;                        // barrier slots
 constexpr int kMaxResidentSteps = 7;                 // resident filter: at most 7 x 16 KB per CTA
-constexpr int kThreadsPair = 192;
-constexpr int kOutBytes = 4 * 2 * 32 * kRowB;        // two TMA-store staging buffers per warp
-constexpr int kEpiBytes = 4 * 2 * kPairN * int(sizeof(float));
+#ifndef FDNN_PAIR_EPI_WARPS
+#define FDNN_PAIR_EPI_WARPS 8
+#endif
+constexpr int kEpiWarpsPair = FDNN_PAIR_EPI_WARPS;   // 8: two per tensor-memory lane quarter, half the columns each
+constexpr int kColSplitPair = kEpiWarpsPair / 4;
+constexpr int kWarpCols = kPairN / kColSplitPair;
+constexpr int kOutBufs = kEpiWarpsPair == 8 ? 1 : 2; // TMA-store staging buffers per warp (32 KB in all either way)
+constexpr int kThreadsPair = 64 + 32 * kEpiWarpsPair;
+constexpr int kOutBytes = kEpiWarpsPair * kOutBufs * 32 * kRowB;
+constexpr int kEpiBytes = kEpiWarpsPair * 2 * kWarpCols * int(sizeof(float));
 constexpr int kBarBytes = (2 * kMaxStages + 6) * 8 + 16;
 constexpr int kSmemPair = kRingBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
 static_assert(kStages * kStageBytes <= kRingBytes, "streaming ring must fit");
@@ -89,6 +97,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const uint32_t rank = cluster_ctarank();         // 0 = leader
   const uint32_t peer = rank ^ 1u;
 
+  griddep_launch_dependents();  // all CTAs of this grid are resident: the next launch may queue behind them
   if (threadIdx.x == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&full_bar[i], 1);                  // the leader producer's arrive.expect_tx
@@ -97,8 +106,8 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     mbar_init(bres_bar, 1);
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
-    mbar_init(&tmem_empty[0], 2 * 4 * 32);         // epilogue threads of both CTAs
-    mbar_init(&tmem_empty[1], 2 * 4 * 32);
+    mbar_init(&tmem_empty[0], 2 * kEpiWarpsPair * 32);  // epilogue threads of both CTAs
+    mbar_init(&tmem_empty[1], 2 * kEpiWarpsPair * 32);
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -113,6 +122,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   }
   tc_fence_before();
   __syncthreads();
+  griddep_wait();      // from here on global memory is touched: the launch before this one must be complete
   cluster_sync_all();  // both CTAs' barriers exist before anyone signals across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
@@ -129,6 +139,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool alive = true;
+      long long prof_wait = 0, prof_issue = 0, prof_iters = 0, prof_t0 = p.prof ? clock64() : 0;
       const uint32_t full0 = map_to_cta(smem_u32(&full_bar[0]), 0);  // the leader's barriers
       if (b_resident && pair_id < total_tiles) {
         // this CTA's 128 filter rows for every reduction step, once (n_tiles == 1 in this mode)
@@ -168,11 +179,15 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             const uint16_t off_h = static_cast<uint16_t>(r * p.dil_h);
             const int tap = r * p.S + s;
             for (int cb = 0; cb < p.c_blocks; ++cb) {
+              const long long pt0 = p.prof ? clock64() : 0;
               if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
                                      kIncidentProducerWait)) {
                 alive = false;
                 break;
               }
+              const long long pt1 = p.prof ? clock64() : 0;
+              prof_wait += pt1 - pt0;
+              ++prof_iters;
               uint8_t* st = stage_base + stage * stage_stride;
               if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], pair_tx);
               const uint32_t bar = full0 + stage * 8;
@@ -183,6 +198,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, off_w, off_h);
               }
               if (!b_resident) tma_load_3d_pair(st + kABytes, &tmB, bar, c0, tap, b_row0);
+              if (p.prof) prof_issue += clock64() - pt1;
               if (++stage == uint32_t(n_stages)) {
                 stage = 0;
                 phase ^= 1u;
@@ -190,6 +206,9 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
           }
         }
+      }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[0] = prof_wait; p.prof[1] = prof_issue; p.prof[2] = clock64() - prof_t0; p.prof[3] = prof_iters;
       }
       if (!alive || *abort_flag) {
         // After an incident: give copies already issued time to land.
@@ -204,6 +223,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t stage = 0, phase = 0;
       uint32_t tcount = 0;
       bool alive = true;
+      long long prof_wfull = 0, prof_wtmem = 0, prof_t0 = p.prof ? clock64() : 0;
       if (b_resident && pair_id < total_tiles) {
         alive = mbar_wait_bounded(bres_bar, 0u, abort_flag, p.status, kIncidentMmaWaitFull);
       }
@@ -214,18 +234,22 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       for (int tile = pair_id; tile < total_tiles && alive; tile += num_pairs, ++tcount) {
         const uint32_t buf = tcount & 1u;
         const uint32_t bphase = (tcount >> 1) & 1u;
+        const long long mt0 = p.prof ? clock64() : 0;
         if (!mbar_wait_bounded(&tmem_empty[buf], bphase ^ 1u, abort_flag, p.status,
                                kIncidentMmaWaitTmem)) {
           alive = false;
           break;
         }
+        if (p.prof) prof_wtmem += clock64() - mt0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kPairN;
         for (int kit = 0; kit < k_iters; ++kit) {
+          const long long mt1 = p.prof ? clock64() : 0;
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull)) {
             alive = false;
             break;
           }
+          if (p.prof) prof_wfull += clock64() - mt1;
           tc_fence_after();
           const uint32_t st = smem_u32(stage_base + stage * stage_stride);
           const uint32_t bt = b_resident ? smem_u32(b_res + kit * kBBytes) : st + kABytes;
@@ -247,6 +271,9 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           tc_commit_pair(tfull_peer + buf * 8);
         }
       }
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[4] = prof_wfull; p.prof[5] = prof_wtmem; p.prof[6] = clock64() - prof_t0; p.prof[7] = tcount;
+      }
       if (!alive || *abort_flag) {
         volatile uint32_t never = 0;
         tc_commit_pair(smem_u32(drain_bar));
@@ -256,25 +283,27 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   } else {
     // ------------------------------------------------------------ epilogue
     const int ew = warp & 3;
-    float* s_scale = epi_stage + (warp - 2) * 2 * kPairN;
-    float* s_bias = s_scale + kPairN;
+    const int chalf = (warp - 2) >> 2;  // which share of the tile's columns this warp drains
+    float* s_scale = epi_stage + (warp - 2) * 2 * kWarpCols;
+    float* s_bias = s_scale + kWarpCols;
     const T* g_bias = static_cast<const T*>(p.bias);
     const T* g_scale = static_cast<const T*>(p.scale);
     const T* g_res = (RES && !p.lowc) ? static_cast<const T*>(p.residual) : nullptr;
-    uint8_t* my_out = out_stage + (warp - 2) * 2 * 32 * kRowB;
+    uint8_t* my_out = out_stage + (warp - 2) * kOutBufs * 32 * kRowB;
     const uint32_t tempty_leader = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     uint32_t tcount = 0;
     uint32_t store_seq = 0;
     int staged_n_tile = -1;
+    long long prof_ewait = 0, prof_t0 = p.prof ? clock64() : 0;
     for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++tcount) {
       const int m_pair = tile / n_tiles;
       const int n_tile = tile - m_pair * n_tiles;
-      const int n0 = n_tile * kPairN;
+      const int n0 = n_tile * kPairN + chalf * kWarpCols;  // first column this warp owns
       const uint32_t buf = tcount & 1u;
       const uint32_t bphase = (tcount >> 1) & 1u;
       if (n_tile != staged_n_tile) {
         __syncwarp();
-        for (int j = lane; j < kPairN; j += 32) {
+        for (int j = lane; j < kWarpCols; j += 32) {
           const int col = n0 + j;
           s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col % p.k_real]) : 1.0f;
           s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col % p.k_real]) : 0.0f;
@@ -297,8 +326,10 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
         load_residual_row<T>(res_row, n0, p.Kout, res0);
       }
+      const long long et0 = p.prof ? clock64() : 0;
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
       ok = __all_sync(0xffffffffu, ok);
+      if (p.prof) prof_ewait += clock64() - et0;
       if (!ok) break;
       tc_fence_after();
       int st_row, st_img, st_rows;
@@ -311,13 +342,16 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         st_row = m_tile * kRows + ew * 32;
         st_rows = 32;
       }
-      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN;
-      epilogue_store_tile<T, kPairN, RES>(t_row, n0, p.Kout, p.relu, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
+      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN + chalf * kWarpCols;
+      epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.relu, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
                                      st_row, st_img, st_rows, store_seq, res_row, res0);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }
     if (lane == 0) bulk_wait_group0();
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {  // first epilogue warp of the first leader
+      p.prof[8] = prof_ewait; p.prof[9] = clock64() - prof_t0;
+    }
   }
 
   // Neither CTA may retire while its partner can still signal its barriers or
@@ -339,13 +373,15 @@ cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   cfg.blockDim = dim3(kThreadsPair, 1, 1);
   cfg.dynamicSmemBytes = kSmemPair;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // set-up may overlap the previous launch's tail
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = launch_overlap_enabled() ? 2 : 1;
   if (p.residual != nullptr) return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, true>, tmA, tmB, tmY, tmY2, p);
   return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, false>, tmA, tmB, tmY, tmY2, p);
 }
@@ -369,6 +405,7 @@ cudaError_t igemm_pair_prepare_device() {
 
 int igemm_pair_smem_bytes() { return kSmemPair; }
 int igemm_pair_stages() { return kStages; }
+int igemm_pair_threads() { return kThreadsPair; }
 int igemm_pair_max_resident_steps() { return kMaxResidentSteps; }
 
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,

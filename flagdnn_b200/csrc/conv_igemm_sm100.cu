@@ -12,9 +12,14 @@
 //               of two fp32 accumulators in tensor memory; tcgen05.commit frees
 //               the stage and, after the last reduction step, publishes the
 //               accumulator;
-//   warps 2..5  epilogue: tcgen05.ld of the finished accumulator, per-channel
+//   warps 2..9  epilogue: tcgen05.ld of the finished accumulator, per-channel
 //               scale, bias, ReLU, one rounding to the output type, store —
-//               while the issuer already fills the other accumulator.
+//               while the issuer already fills the other accumulator.  Two
+//               warps share each tensor-memory lane quarter and take half of
+//               the tile's columns each: a short-reduction layer (1x1, few
+//               input channels) is bound by how fast tiles drain, and one warp
+//               per quarter leaves its chain of load, convert, stage and store
+//               latencies exposed.
 // fp32 tensors run the same loop on TF32-split operands (high and low halves
 // staged side by side): lo*hi + hi*lo + hi*hi per reduction step.
 //
@@ -37,8 +42,11 @@ namespace {
 
 constexpr int kBM = 128;            // output rows per tile (= tcgen05 M, = TMEM lanes)
 constexpr int kRowBytes = 128;      // one swizzled shared-memory row
-constexpr int kThreads = 192;       // 6 warps: producer, issuer, 4 epilogue
-constexpr int kEpiWarps = 4;
+#ifndef FDNN_EPI_WARPS
+#define FDNN_EPI_WARPS 8
+#endif
+constexpr int kEpiWarps = FDNN_EPI_WARPS;  // 8: two per tensor-memory lane quarter (4: one)
+constexpr int kThreads = 64 + 32 * kEpiWarps;  // producer, issuer, epilogue warps
 
 template <typename T, int BN>
 struct TileCfg {
@@ -48,14 +56,21 @@ struct TileCfg {
   static constexpr int kABytes = kBM * kRowBytes;
   static constexpr int kBBytes = BN * kRowBytes;
   static constexpr int kStageBytes = (kSplit ? 2 : 1) * (kABytes + kBBytes);
-  // operand ring: what is left of the 227 KB after the output staging; 3 x 48 KB for the widest 16-bit tile
-  static constexpr int kStages = (176 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;  // two accumulators; 128, 256 or 512
   // per-warp output staging (32 rows x 128 bytes, swizzled, for the TMA store),
   // per-warp scale and bias staging, then barriers and bookkeeping words
   static constexpr int kOutCols = kRowBytes / int(sizeof(T));  // output channels per TMA store
-  static constexpr int kOutBytes = kEpiWarps * 2 * 32 * kRowBytes;  // two 4 KB buffers per warp
-  static constexpr int kEpiBytes = kEpiWarps * 2 * BN * int(sizeof(float));
+  // a tile's columns are split between the two warps of a lane quarter when each half is two stores
+  // or more (narrower tiles keep one warp per quarter and spend the shared memory on pipeline stages)
+  static constexpr int kColSplit = (kEpiWarps == 8 && BN / kOutCols >= 4) ? 2 : 1;
+  static constexpr int kWarpCols = BN / kColSplit;             // columns one epilogue warp drains
+  static constexpr int kActiveEpiWarps = 4 * kColSplit;
+  static constexpr int kOutBytes = kActiveEpiWarps * 2 * 32 * kRowBytes;  // two 4 KB buffers per warp
+  static constexpr int kEpiBytes = kActiveEpiWarps * 2 * kWarpCols * int(sizeof(float));
+  // operand ring: what is left of the 227 KB; 3 x 48 KB for the widest 16-bit tile
+  static constexpr int kMaxStages = 16;
+  static constexpr int kRingBudget = 227 * 1024 - kOutBytes - kEpiBytes - (2 * kMaxStages + 8) * 8 - 1024;
+  static constexpr int kStages = kRingBudget / kStageBytes < kMaxStages ? kRingBudget / kStageBytes : kMaxStages;
   static constexpr int kBarBytes = (2 * kStages + 4 + 1) * 8 + 16;
   static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
@@ -111,6 +126,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  griddep_launch_dependents();  // all CTAs of this grid are resident: the next launch may queue behind them
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&full_bar[i], 1);
@@ -118,8 +134,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
-    mbar_init(&tmem_empty[0], kEpiWarps * 32);
-    mbar_init(&tmem_empty[1], kEpiWarps * 32);
+    mbar_init(&tmem_empty[0], Cfg::kActiveEpiWarps * 32);
+    mbar_init(&tmem_empty[1], Cfg::kActiveEpiWarps * 32);
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -139,6 +155,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  griddep_wait();  // from here on global memory is touched: the launch before this one must be complete
 
   const int total_tiles = p.m_tiles * p.n_tiles;
   const int k_iters = p.R * p.S * p.c_blocks;
@@ -285,11 +302,13 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         mbar_wait_bounded(drain_bar, 0u, &never, p.status, kIncidentDrainWait, kWaitLimitCycles / 16);
       }
     }
-  } else {
+  } else if (warp - 2 < Cfg::kActiveEpiWarps) {
     // ------------------------------------------------------------ epilogue
-    const int ew = warp & 3;  // tensor-memory lane quarter this warp may read
-    float* s_scale = epi_stage + (warp - 2) * 2 * BN;
-    float* s_bias = s_scale + BN;
+    constexpr int WC = Cfg::kWarpCols;
+    const int ew = warp & 3;           // tensor-memory lane quarter this warp may read
+    const int chalf = (warp - 2) >> 2;  // which share of the tile's columns it drains
+    float* s_scale = epi_stage + (warp - 2) * 2 * WC;
+    float* s_bias = s_scale + WC;
     const T* g_bias = static_cast<const T*>(p.bias);
     const T* g_scale = static_cast<const T*>(p.scale);
     T* y = static_cast<T*>(p.y);
@@ -301,13 +320,13 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
       const int m_tile = tile / p.n_tiles;
       const int n_tile = tile - m_tile * p.n_tiles;
-      const int n0 = n_tile * BN;
+      const int n0 = n_tile * BN + chalf * WC;  // first column this warp owns
       const uint32_t buf = tcount & 1u;
       const uint32_t bphase = (tcount >> 1) & 1u;
 
       if (n_tile != staged_n_tile) {
         __syncwarp();
-        for (int j = lane; j < BN; j += 32) {
+        for (int j = lane; j < WC; j += 32) {
           const int col = n0 + j;
           s_scale[j] = (g_scale != nullptr && col < p.Kout) ? to_f32<T>(g_scale[col % p.k_real]) : 1.0f;
           s_bias[j] = (g_bias != nullptr && col < p.Kout) ? to_f32<T>(g_bias[col % p.k_real]) : 0.0f;
@@ -340,7 +359,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (!ok) break;
       tc_fence_after();
 
-      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * BN;
+      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * BN + chalf * WC;
       // Where this warp's 32 rows go in y seen as (channel, row, image): the whole
       // output is one "image" outside low-channel mode.
       int st_row, st_img, st_rows;
@@ -356,12 +375,12 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (p.tma_store) {
         // a tile's last warp may own fewer than 32 valid rows: tmA2 then holds a second
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
-        epilogue_store_tile<T, BN, RES>(t_row, n0, p.Kout, p.relu, s_scale, s_bias,
+        epilogue_store_tile<T, WC, RES>(t_row, n0, p.Kout, p.relu, s_scale, s_bias,
                                    out_stage + (warp - 2) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
                                    st_img, st_rows, store_seq, res_row, res0);
       } else {
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+      for (int chunk = 0; chunk < WC / 32; ++chunk) {
         const int col0 = n0 + chunk * 32;
         if (col0 >= p.Kout) break;  // uniform across the warp
         uint32_t raw[32];
@@ -393,7 +412,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_arrive(&tmem_empty[buf]);
     }
     if (p.tma_store && lane == 0) bulk_wait_group0();  // stores must be done before the CTA retires
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {  // first epilogue warp
       p.prof[8] = prof_ewait; p.prof[9] = clock64() - prof_t0;
     }
   }
@@ -411,11 +430,19 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CU
                        const CUtensorMap& tmB2, const CUtensorMap& tmY, const IgemmParams& p, int grid,
                        cudaStream_t stream) {
   using Cfg = TileCfg<T, BN>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // set-up may overlap the previous launch's tail
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = launch_overlap_enabled() ? 1 : 0;
   if (p.residual != nullptr)
-    conv_igemm_kernel<T, BN, true><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, tmY, p);
-  else
-    conv_igemm_kernel<T, BN, false><<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tmA, tmA2, tmB, tmB2, tmY, p);
-  return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, true>, tmA, tmA2, tmB, tmB2, tmY, p);
+  return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, false>, tmA, tmA2, tmB, tmB2, tmY, p);
 }
 
 template <typename T, int BN>
@@ -448,6 +475,8 @@ int igemm_smem_bytes(int dtype, int tile_n) {
   if (tile_n == 128) return TileCfg<__half, 128>::kSmemBytes;
   return TileCfg<__half, 256>::kSmemBytes;
 }
+
+int igemm_threads() { return kThreads; }
 
 int igemm_stages(int dtype, int tile_n) {
   if (dtype == FDNN_F32) return tile_n == 64 ? TileCfg<float, 64>::kStages : TileCfg<float, 128>::kStages;

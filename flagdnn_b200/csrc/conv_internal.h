@@ -44,6 +44,11 @@ struct IgemmParams {
   long long* prof;       // optional: 16 cycle counters written by CTA 0 (nullptr = off)
 };
 
+// Whether the tensor-core kernels are launched with programmatic stream serialization (their set-up
+// overlaps the tail of the launch before them on the stream).  On unless the environment variable
+// FLAGDNN_B200_LAUNCH_OVERLAP is "0" when the library makes its first launch.
+bool launch_overlap_enabled();
+
 // Launchers (defined in conv_igemm_sm100.cu).  `dtype` is FDNN_F16/BF16/F32.
 // tmA2 / tmB2 are the low-half operands of the split-TF32 path (ignored for
 // 16-bit types); tmY is the output map used when p.tma_store is set.  Returns a cudaError_t from the launch.
@@ -53,6 +58,7 @@ cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CU
 // Dynamic shared memory and pipeline depth of a tile configuration.
 int igemm_smem_bytes(int dtype, int tile_n);
 int igemm_stages(int dtype, int tile_n);
+int igemm_threads();       // threads per CTA of the single-CTA kernel
 // One-time opt-in to large dynamic shared memory for every instantiation.
 cudaError_t igemm_prepare_device();
 
@@ -64,6 +70,7 @@ cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorM
 cudaError_t igemm_pair_prepare_device();
 int igemm_pair_smem_bytes();
 int igemm_pair_stages();
+int igemm_pair_threads();
 int igemm_pair_max_resident_steps();  // reductions this short (and one channel tile) keep the filter resident
 
 // Direct convolution on CUDA cores (conv_direct.cu): any dtype, groups, strides.

@@ -90,6 +90,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it on the stream is still draining.  It runs
+// its set-up (barriers, tensor memory, descriptor prefetch), then blocks in
+// griddep_wait() until that kernel has completed and its writes are visible;
+// nothing before the wait may touch global memory.  griddep_launch_dependents()
+// in the earlier kernel says that the next one may be scheduled as soon as
+// every CTA of this grid has issued it (or exited); without it the trigger
+// fires when the grid completes, which is ordinary stream order.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // --------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");

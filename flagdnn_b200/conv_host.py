@@ -203,7 +203,8 @@ def _empty_output(input, n, c_out, oh, ow, meta=False):
     )
 
 
-def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activation, residual=None) -> torch.Tensor:
+def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activation, residual=None,
+         out=None) -> torch.Tensor:
     n, _, h, w = input.shape
     c_out, _, kh, kw = weight.shape
     oh = _conv_out_dim(h, padding4[0], padding4[1], dilation[0], kh, stride[0])
@@ -218,7 +219,8 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         scale = scale.contiguous()
     lib = nat.load()
     with torch.cuda.device(input.device):
-        out = _empty_output(input, n, c_out, oh, ow)
+        if out is None:
+            out = _empty_output(input, n, c_out, oh, ow)
         if n == 0:
             return out
         if residual is not None:
@@ -451,3 +453,62 @@ def device_status() -> int:
     if status not in (nat.FDNN_OK, nat.FDNN_DEVICE_TIMEOUT):
         nat.check(status)
     return int(word.value)
+
+
+def mm(
+    input: torch.Tensor,
+    mat2: torch.Tensor,
+    out_dtype: Optional[torch.dtype] = None,
+    *,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Drop-in for ``flag_dnn.ops.mm`` (src/flag_dnn/ops/mm.py:336) on real tensors: ``input @ mat2`` is a
+    1x1 convolution over M one-pixel images with K channels whose filter is ``mat2`` transposed, so it runs
+    on the same kernels (fp64 on the direct one).  Checks and messages follow src/flag_dnn/ops/mm.py:100-140,
+    the ``out`` handling src/flag_dnn/ops/mm.py:153-181.  Complex tensors and an fp32 result from 16-bit
+    operands are not implemented on this path."""
+    if input.dim() != 2:
+        raise RuntimeError("self must be a matrix")
+    if mat2.dim() != 2:
+        raise RuntimeError("mat2 must be a matrix")
+    if input.shape[1] != mat2.shape[0]:
+        raise RuntimeError("mat1 and mat2 shapes cannot be multiplied "
+                           f"({input.shape[0]}x{input.shape[1]} and {mat2.shape[0]}x{mat2.shape[1]})")
+    if input.device != mat2.device:
+        raise RuntimeError(f"mm: input and mat2 must be on the same device, but got {input.device} and {mat2.device}")
+    if input.dtype != mat2.dtype:
+        raise RuntimeError(f"expected mat1 and mat2 to have the same dtype, but got: {input.dtype} != {mat2.dtype}")
+    if input.layout != torch.strided or mat2.layout != torch.strided:
+        raise NotImplementedError("flag_dnn mm supports dense strided tensors only")
+    if input.dtype in (torch.complex64, torch.complex128):
+        raise NotImplementedError("flag_dnn mm: complex tensors are not implemented on the convolution kernels")
+    if input.dtype not in (torch.float16, torch.bfloat16, torch.float32, torch.float64):
+        raise NotImplementedError(f"flag_dnn mm does not support dtype={input.dtype}")
+    if out_dtype is not None and out_dtype != input.dtype:
+        if input.dtype in (torch.float16, torch.bfloat16) and out_dtype == torch.float32:
+            raise NotImplementedError("flag_dnn mm: an fp32 result from fp16/bf16 operands is not implemented "
+                                      "on the convolution kernels")
+        raise RuntimeError("out_dtype must be the same as input dtype or fp32 for fp16/bf16 inputs")
+    if not input.is_cuda:
+        raise NotImplementedError("flag_dnn mm CUDA implementation requires CUDA input")
+    m, k = input.shape
+    n = mat2.shape[1]
+    if out is not None:
+        if out.device != input.device:
+            raise RuntimeError(f"mm out tensor device mismatch: expected {input.device}, got {out.device}")
+        if out.dtype != input.dtype:
+            raise RuntimeError(f"Expected out tensor to have dtype {input.dtype}, but got {out.dtype} instead")
+        if out.dim() != 2 or tuple(out.shape) != (m, n):
+            out.resize_((m, n))
+    y = out if out is not None and out.is_contiguous() else torch.empty((m, n), dtype=input.dtype, device=input.device)
+    if y.numel() > 0:
+        if k == 0:
+            y.zero_()
+        else:
+            x4 = input.unsqueeze(-1).unsqueeze(-1)                 # [M, K, 1, 1]: M images of one pixel
+            w4 = mat2.t().unsqueeze(-1).unsqueeze(-1)              # [N, K, 1, 1]: the filter is mat2 transposed
+            _run(x4, w4, None, None, (1, 1), (0, 0, 0, 0), (1, 1), 1, nat.ACT_NONE, out=y.view(m, n, 1, 1))
+    if out is not None and y is not out:
+        out.copy_(y)
+        return out
+    return y

@@ -53,4 +53,5 @@ add = _capturable("add", _eager_binary(torch.add))
 sub = _capturable("sub", _eager_binary(torch.sub))
 mul = _capturable("mul", _eager_binary(torch.mul))
 conv1d = _conv.conv1d  # eager only: the graph registry has no conv1d node, as in the reference
+mm = _conv.mm          # eager only
 fused_conv2d_bias_relu = _conv.fused_conv2d_bias_relu

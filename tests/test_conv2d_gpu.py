@@ -149,6 +149,60 @@ def test_conv1d_matches_torch_cpu(fd, case, dtype_name):
     _check(out, ref, dtype_name)
 
 
+MM_CASES = [(0, 3, 4), (2, 0, 4), (2, 3, 0), (2, 3, 4), (7, 5, 3), (16, 17, 15), (32, 64, 16),   # the reference's
+            (300, 256, 520), (4096, 1024, 256), (129, 72, 8)]
+
+
+@pytest.mark.parametrize("use_out", [False, True])
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16", "float16", "float64"])
+@pytest.mark.parametrize("case", MM_CASES, ids=["x".join(map(str, c)) for c in MM_CASES])
+def test_mm_matches_torch_cpu(fd, case, dtype_name, use_out):
+    """mm as a 1x1 convolution over one-pixel images, the reference's cases (tests/test_mm.py:9-17) and larger."""
+    m, k, n = case
+    dtype = getattr(torch, dtype_name)
+    a = torch.empty(m, k).uniform_(-1, 1, generator=torch.Generator().manual_seed(5)).to(dtype).cuda()
+    b = torch.empty(k, n).uniform_(-1, 1, generator=torch.Generator().manual_seed(6)).to(dtype).cuda()
+    a0, b0 = a.clone(), b.clone()
+    cdt = torch.float64 if dtype_name == "float64" else torch.float32
+    ref = torch.mm(a.cpu().to(cdt), b.cpu().to(cdt))
+    if use_out:
+        buf = torch.empty(m, n, dtype=dtype, device="cuda")
+        got = fd.mm(a, b, out=buf)
+        assert got.data_ptr() == buf.data_ptr()
+    else:
+        got = fd.mm(a, b)
+    assert got.shape == (m, n) and got.dtype == dtype
+    # the reference's own test allows atol = 1e-4 * K (tests/test_mm.py:27-30 with reduce_dim=k); here the
+    # absolute part grows with sqrt(K) only, the relative part is the dtype's usual one
+    tol = dict(TOL[dtype_name])
+    tol["atol"] = tol["atol"] * max(1.0, k ** 0.5)
+    torch.testing.assert_close(got.cpu().to(cdt), ref, **tol)
+    assert torch.equal(a, a0) and torch.equal(b, b0)
+
+
+def test_mm_strided_operands_and_checks(fd):
+    a = torch.randn(64, 96, device="cuda")[:, ::2]            # non-contiguous left operand
+    b = torch.randn(40, 48, device="cuda").t()                # transposed right operand: [48, 40]
+    torch.testing.assert_close(fd.mm(a, b).cpu(), torch.mm(a.cpu(), b.cpu()), rtol=1e-4, atol=1e-4)
+    out = torch.empty(40, 64, device="cuda").t()              # non-contiguous out: result is copied back
+    got = fd.mm(a, b, out=out)
+    assert got is out
+    torch.testing.assert_close(out.cpu(), torch.mm(a.cpu(), b.cpu()), rtol=1e-4, atol=1e-4)
+    with pytest.raises(RuntimeError, match="self must be a matrix"):
+        fd.mm(torch.randn(2, 3, 4, device="cuda"), b)
+    with pytest.raises(RuntimeError, match="cannot be multiplied"):
+        fd.mm(torch.randn(2, 3, device="cuda"), torch.randn(4, 5, device="cuda"))
+    with pytest.raises(RuntimeError, match="same dtype"):
+        fd.mm(torch.randn(2, 3, device="cuda"), torch.randn(3, 5, device="cuda", dtype=torch.float16))
+    with pytest.raises(NotImplementedError):
+        fd.mm(torch.randn(2, 3, device="cuda", dtype=torch.complex64), torch.randn(3, 5, device="cuda", dtype=torch.complex64))
+    with pytest.raises(NotImplementedError):
+        fd.mm(torch.randn(2, 3, device="cuda", dtype=torch.float16), torch.randn(3, 5, device="cuda", dtype=torch.float16),
+              out_dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="out_dtype must be"):
+        fd.mm(torch.randn(2, 3, device="cuda"), torch.randn(3, 5, device="cuda"), out_dtype=torch.float16)
+
+
 def test_aten_override_routes_functional_conv2d(fd):
     g = torch.Generator().manual_seed(3)
     x = torch.randn(2, 16, 12, 12, generator=g).cuda()

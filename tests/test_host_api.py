@@ -47,6 +47,15 @@ def test_conv1d_argument_checks():
         flag_dnn.conv1d(x, w, stride=(1, 1))
 
 
+def test_mm_argument_checks():
+    with pytest.raises(RuntimeError, match="mat2 must be a matrix"):
+        flag_dnn.mm(torch.randn(2, 3), torch.randn(3))
+    with pytest.raises(RuntimeError, match=r"cannot be multiplied \(2x3 and 4x5\)"):
+        flag_dnn.mm(torch.randn(2, 3), torch.randn(4, 5))
+    with pytest.raises(NotImplementedError, match="requires CUDA input"):
+        flag_dnn.mm(torch.randn(2, 3), torch.randn(3, 5))
+
+
 def test_graph_capture_fuses_bias_relu_and_eliminates_dead_node():
     @flag_dnn.graph
     def fn(x, bias):

@@ -32,7 +32,7 @@ from .graph import (  # noqa: F401
     compile,
     graph,
 )
-from .ops import add, bias_add, conv1d, conv2d, mm, mul, relu, sub  # noqa: F401
+from .ops import add, bias_add, conv1d, conv2d, gelu, mm, mul, relu, sub  # noqa: F401
 
 __version__ = "0.1.0"
 

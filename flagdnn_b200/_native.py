@@ -22,7 +22,7 @@ FDNN_DEVICE_TIMEOUT = 6
 
 F16, BF16, F32, F64 = 0, 1, 2, 3
 ALGO_AUTO, ALGO_DIRECT, ALGO_IGEMM, ALGO_IGEMM_PAIR = 0, 1, 2, 3
-ACT_NONE, ACT_RELU = 0, 1
+ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH = 0, 1, 2, 3
 
 EXPORTED_SYMBOLS = (
     "fdnn_abi_version",

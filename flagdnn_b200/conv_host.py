@@ -190,6 +190,9 @@ def conv2d_plan(input, weight, stride=1, padding=0, dilation=1, groups=1, algo=N
     return plan.as_dict()
 
 
+_ACTIVATIONS = {"none": nat.ACT_NONE, "relu": nat.ACT_RELU, "gelu": nat.ACT_GELU, "gelu_tanh": nat.ACT_GELU_TANH}
+
+
 def _empty_output(input, n, c_out, oh, ow, meta=False):
     # channels_last output iff the input has unit channel stride
     # (src/flag_dnn/ops/conv2d.py:3729-3738, fused_conv.py:120-130); fp64 always
@@ -257,6 +260,8 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
             out.add_(residual)
             if activation == nat.ACT_RELU:
                 out.relu_()
+            elif activation in (nat.ACT_GELU, nat.ACT_GELU_TANH):
+                out.copy_(torch.nn.functional.gelu(out, approximate="tanh" if activation == nat.ACT_GELU_TANH else "none"))
         # `ws` goes back to torch's caching allocator when this frame ends; the
         # allocator orders reuse on the stream the kernels were queued on.
     return out
@@ -298,8 +303,8 @@ def fused_conv2d_bias_relu(
 
     ``config`` (the reference's Triton tile override) is accepted and ignored.
     Two additions the reference's callers never pass: ``scale`` (BN-folded
-    per-channel multiplier applied before the bias) and ``activation`` ("relu"
-    or "none").
+    per-channel multiplier applied before the bias) and ``activation`` ("relu",
+    "none", "gelu" or "gelu_tanh").
     """
     del config
     if not (isinstance(input, torch.Tensor) and input.is_cuda):
@@ -316,7 +321,7 @@ def fused_conv2d_bias_relu(
         raise RuntimeError("input, weight, and bias must be on the same device")
     if scale is not None and (scale.dtype != input.dtype or scale.device != input.device or scale.dim() != 1):
         raise RuntimeError("scale must be a 1D tensor with the dtype and device of input")
-    if activation not in ("relu", "none"):
+    if activation not in _ACTIVATIONS:
         raise NotImplementedError(f"unsupported activation {activation!r}")
     stride = _pair(stride)
     dilation = _pair(dilation)
@@ -329,8 +334,7 @@ def fused_conv2d_bias_relu(
         raise RuntimeError(f"bias shape mismatch, expected ({c_out},)")
     if scale is not None and scale.numel() != c_out:
         raise RuntimeError(f"scale shape mismatch, expected ({c_out},)")
-    act = nat.ACT_RELU if activation == "relu" else nat.ACT_NONE
-    return _run(input, weight, bias, scale, stride, padding4, dilation, 1, act)
+    return _run(input, weight, bias, scale, stride, padding4, dilation, 1, _ACTIVATIONS[activation])
 
 
 def conv2d_bias_act(
@@ -345,6 +349,7 @@ def conv2d_bias_act(
     scale: Optional[torch.Tensor] = None,
     relu: bool = False,
     residual: Optional[torch.Tensor] = None,
+    activation: Optional[str] = None,
 ) -> torch.Tensor:
     """conv2d with the full epilogue (scale, bias, residual add, ReLU) and conv2d's
     argument range (any groups, fp64): ``act(conv(x, w) * scale + bias + residual)``
@@ -361,8 +366,11 @@ def conv2d_bias_act(
     if scale is not None and (scale.dtype != input.dtype or scale.device != input.device
                               or scale.dim() != 1 or scale.numel() != weight.shape[0]):
         raise RuntimeError("scale must be a 1D tensor of length C_out with the dtype and device of input")
-    return _run(input, weight, bias, scale, stride, padding4, dilation, groups,
-                nat.ACT_RELU if relu else nat.ACT_NONE, residual)
+    if activation is None:
+        activation = "relu" if relu else "none"
+    if activation not in _ACTIVATIONS:
+        raise NotImplementedError(f"unsupported activation {activation!r}")
+    return _run(input, weight, bias, scale, stride, padding4, dilation, groups, _ACTIVATIONS[activation], residual)
 
 
 def conv1d(

@@ -571,7 +571,7 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
   p.M = p.m_tiles * 128;
   p.n_tiles = (n_gemm + plan.tile_n - 1) / plan.tile_n;
   p.bias = bias; p.scale = scale; p.y = y;
-  p.relu = activation == FDNN_ACT_RELU;
+  p.act = activation;
   p.vec_store = 0;
   p.tma_store = 1;
   p.lowc = 1;
@@ -691,7 +691,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   int st = make_plan(desc, x, w_packed != nullptr ? reinterpret_cast<const void*>(uintptr_t(1)) : w, y, &plan,
                      allow_group);
   if (st != FDNN_OK) return st;
-  if (activation != FDNN_ACT_NONE && activation != FDNN_ACT_RELU)
+  if (activation < FDNN_ACT_NONE || activation > FDNN_ACT_GELU_TANH)
     return fail(FDNN_BAD_PARAM, "unknown activation");
   const fdnn_conv_desc& d = *desc;
   if (d.n == 0 || plan.oh == 0 || plan.ow == 0) return FDNN_OK;  // empty output: nothing to launch
@@ -712,7 +712,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
       p.y_s[i] = d.y_strides[i];
     }
     p.x = x; p.w = w; p.bias = bias; p.scale = scale; p.residual = residual; p.y = y;
-    p.relu = activation == FDNN_ACT_RELU;
+    p.act = activation;
     cudaError_t e = launch_direct(d.dtype, p, stream);
     if (e != cudaSuccess) return fail_cuda("direct conv launch", e);
     return FDNN_OK;
@@ -825,7 +825,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   p.y_sn = d.y_strides[0]; p.y_sk = d.y_strides[1]; p.y_sh = d.y_strides[2]; p.y_sw = d.y_strides[3];
   p.bias = bias; p.scale = scale; p.y = y;
   p.residual = residual;
-  p.relu = activation == FDNN_ACT_RELU;
+  p.act = activation;
   const int gran = 16 / es;
   p.vec_store = (d.y_strides[1] == 1 && d.y_strides[0] % gran == 0 && d.y_strides[2] % gran == 0 &&
                  d.y_strides[3] % gran == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0)

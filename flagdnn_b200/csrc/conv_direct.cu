@@ -75,7 +75,14 @@ conv_direct_kernel(const DirectParams p, const bool k_fastest) {
     if (bias != nullptr) acc += ld<T, A>(bias + k);
     const long long y_idx = n * p.y_s[0] + k * p.y_s[1] + oh * p.y_s[2] + ow * p.y_s[3];
     if (p.residual != nullptr) acc += ld<T, A>(static_cast<const T*>(p.residual) + y_idx);
-    if (p.relu) acc = (acc < A(0)) ? A(0) : acc;
+    if (p.act == FDNN_ACT_RELU) {
+      acc = (acc < A(0)) ? A(0) : acc;  // keeps NaN, like torch.relu
+    } else if (p.act == FDNN_ACT_GELU) {
+      acc = A(0.5) * acc * (A(1) + erf(acc * A(0.70710678118654752440)));
+    } else if (p.act == FDNN_ACT_GELU_TANH) {
+      const A u = A(0.79788456080286535588) * (acc + A(0.044715) * acc * acc * acc);
+      acc = A(0.5) * acc * (A(1) + tanh(u));
+    }
     y[y_idx] = cvt<T, A>(acc);
   }
 }

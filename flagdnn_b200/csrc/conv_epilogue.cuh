@@ -1,6 +1,6 @@
 // Epilogue shared by the implicit-GEMM kernels when y is dense NHWC: one warp
 // drains its 32 accumulator rows from tensor memory, applies per-channel scale,
-// bias and ReLU in fp32, rounds once, stages 32 rows x 128 bytes in shared
+// bias and the activation in fp32, rounds once, stages 32 rows x 128 bytes in shared
 // memory and hands each box to a TMA store.  The arithmetic is that of the
 // reference's fused kernel (src/flag_dnn/graph/kernels/fused_conv.py:297-310),
 // plus an optional residual tensor added in fp32 before the activation.
@@ -19,6 +19,18 @@ __device__ __forceinline__ float relu_keep_nan(float a) {
   float r;
   asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(0.0f));
   return r;
+}
+
+// Epilogue activation by its FDNN_ACT_* code: none, ReLU, GELU (erf form, torch's default) or GELU's tanh
+// approximation (torch's approximate="tanh").  All keep NaN.
+__device__ __forceinline__ float apply_activation(float v, int act) {
+  if (act == 1) return relu_keep_nan(v);
+  if (act == 2) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+  if (act == 3) {
+    const float u = 0.79788456080286536f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(u));
+  }
+  return v;
 }
 
 template <typename T>
@@ -85,7 +97,7 @@ __device__ __forceinline__ void load_residual_row(const T* src, int col0, int ko
 // res                the residual row of the first column group, loaded by the caller before it
 //                    waited for the accumulator so that the load hides behind the main loop
 template <typename T, int BN, bool RES = false, int NBUF = 2>
-__device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int relu,
+__device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int act,
                                                     const float* s_scale, const float* s_bias,
                                                     uint8_t* my_out, int lane, const CUtensorMap* tm_full,
                                                     const CUtensorMap* tm_tail, int st_row, int st_img,
@@ -135,11 +147,11 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
             v3 += r3;
           }
         }
-        if (relu) {
-          v0 = relu_keep_nan(v0);
-          v1 = relu_keep_nan(v1);
-          v2 = relu_keep_nan(v2);
-          v3 = relu_keep_nan(v3);
+        if (act) {  // uniform across the launch
+          v0 = apply_activation(v0, act);
+          v1 = apply_activation(v1, act);
+          v2 = apply_activation(v2, act);
+          v3 = apply_activation(v3, act);
         }
         if constexpr (std::is_same<T, float>::value) {
           row[4 * j4 + 0] = __float_as_uint(v0);

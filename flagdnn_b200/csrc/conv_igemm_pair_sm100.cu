@@ -343,7 +343,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         st_rows = 32;
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN + chalf * kWarpCols;
-      epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.relu, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
+      epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.act, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
                                      st_row, st_img, st_rows, store_seq, res_row, res0);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);

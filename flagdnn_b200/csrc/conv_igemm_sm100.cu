@@ -375,7 +375,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       if (p.tma_store) {
         // a tile's last warp may own fewer than 32 valid rows: tmA2 then holds a second
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
-        epilogue_store_tile<T, WC, RES>(t_row, n0, p.Kout, p.relu, s_scale, s_bias,
+        epilogue_store_tile<T, WC, RES>(t_row, n0, p.Kout, p.act, s_scale, s_bias,
                                    out_stage + (warp - 2) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
                                    st_img, st_rows, store_seq, res_row, res0);
       } else {
@@ -393,7 +393,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           a = fmaf(a, s_scale[chunk * 32 + j], s_bias[chunk * 32 + j]);
           if (RES && g_res != nullptr && row_ok && col0 + j < p.Kout)
             a += to_f32<T>(g_res[y_off + (long long)(col0 + j) * p.y_sk]);
-          if (p.relu) a = (a < 0.0f) ? 0.0f : a;  // keeps NaN, like torch.relu
+          if (p.act) a = apply_activation(a, p.act);
           v[j] = a;
         }
         if (row_ok) {

@@ -27,7 +27,7 @@ struct IgemmParams {
   const void* scale;     // [Kout] in the tensor dtype, or nullptr
   void* y;
   const void* residual;  // tensor with y's dtype and strides added before the activation, or nullptr
-  int relu;
+  int act;               // FDNN_ACT_* applied after scale, bias and residual
   int vec_store;         // 1: y is channel-contiguous and 16-byte aligned per pixel
   int tma_store;         // 1: y is dense NHWC; the epilogue writes it through the tmY tensor map
   // Low-channel mode (C <= 4): one GEMM row is a quad of 4 output pixels of one
@@ -84,7 +84,7 @@ struct DirectParams {
   const void* scale;
   const void* residual;  // same dtype and strides as y, or nullptr
   void* y;
-  int relu;
+  int act;  // FDNN_ACT_*
 };
 cudaError_t launch_direct(int dtype, const DirectParams& p, cudaStream_t stream);
 

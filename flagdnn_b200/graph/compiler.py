@@ -186,6 +186,10 @@ def _candidates_for(node, graph: Graph) -> list:
             {"name": "fused_conv2d_bias_relu.sm100_direct", "backend": "sm100", "op_type": node.op_type,
              "implementation": "sm100_direct", "priority": 50, "configs": []},
         ]
+    if node.op_type == "fused_conv2d_bias_gelu":
+        return [{"name": "fused_conv2d_bias_gelu.sm100_igemm", "backend": "sm100", "op_type": node.op_type,
+                 "implementation": "sm100_fused", "priority": 0,
+                 "configs": [{"tile_m": 128, "tile_k_bytes": 128, "accumulators": 2}]}]
     if node.op_type == "fused_conv2d_bias_add_relu":
         return [{"name": "fused_conv2d_bias_add_relu.sm100_igemm", "backend": "sm100", "op_type": node.op_type,
                  "implementation": "sm100_fused_residual", "priority": 0,

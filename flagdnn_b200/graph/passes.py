@@ -92,8 +92,11 @@ def _match_conv_chain(graph: Graph, bias_node: OpNode):
 
 
 def _fuse_conv_bias_relu(graph: Graph) -> bool:
+    """conv2d -> [mul(scale) ->] bias_add -> relu | gelu.  The ReLU form is the reference's rule
+    (src/flag_dnn/graph/passes/fusion.py:40-83); the GELU form has no counterpart there (the reference
+    leaves conv2d(+bias) and gelu as two nodes) and becomes a fused_conv2d_bias_gelu node."""
     for act in list(graph.nodes):
-        if act.op_type != "relu" or len(act.inputs) != 1 or len(act.outputs) != 1:
+        if act.op_type not in ("relu", "gelu") or len(act.inputs) != 1 or len(act.outputs) != 1:
             continue
         bias_node = _single_use_producer(graph, act.inputs[0], "bias_add")
         if bias_node is None:
@@ -103,14 +106,16 @@ def _fuse_conv_bias_relu(graph: Graph) -> bool:
             continue
         conv_node, mul_node, scale_id = match
         attrs = dict(conv_node.attrs)
-        attrs["activation"] = "relu"
+        attrs.update(act.attrs)
+        attrs["activation"] = act.op_type
         inputs = [conv_node.inputs[0], conv_node.inputs[1], bias_node.inputs[1]]
         doomed = [conv_node.id, bias_node.id, act.id]
         if mul_node is not None:
             inputs.append(scale_id)
             doomed.append(mul_node.id)
-        fused = OpNode(id=graph.new_node_id(), op_type="fused_conv2d_bias_relu", inputs=inputs,
-                       outputs=list(act.outputs), attrs=attrs, name="fused_conv2d_bias_relu")
+        kind = "fused_conv2d_bias_relu" if act.op_type == "relu" else "fused_conv2d_bias_gelu"
+        fused = OpNode(id=graph.new_node_id(), op_type=kind, inputs=inputs,
+                       outputs=list(act.outputs), attrs=attrs, name=kind)
         graph.replace_nodes_with(doomed, fused)
         return True
     return False
@@ -158,17 +163,19 @@ def _fold_conv_bias(graph: Graph) -> bool:
 
 
 def _fuse_bias_relu(graph: Graph) -> bool:
+    """bias_add -> relu | gelu (src/flag_dnn/graph/passes/fusion.py:129-160)."""
     for act in list(graph.nodes):
-        if act.op_type != "relu" or len(act.inputs) != 1 or len(act.outputs) != 1:
+        if act.op_type not in ("relu", "gelu") or len(act.inputs) != 1 or len(act.outputs) != 1:
             continue
         bias_node = _single_use_producer(graph, act.inputs[0], "bias_add")
         if bias_node is None:
             continue
         attrs = dict(bias_node.attrs)
         attrs.update(act.attrs)
-        attrs["activation"] = "relu"
-        fused = OpNode(id=graph.new_node_id(), op_type="fused_bias_relu", inputs=list(bias_node.inputs),
-                       outputs=list(act.outputs), attrs=attrs, name="fused_bias_relu")
+        attrs["activation"] = act.op_type
+        kind = "fused_bias_relu" if act.op_type == "relu" else "fused_bias_gelu"
+        fused = OpNode(id=graph.new_node_id(), op_type=kind, inputs=list(bias_node.inputs),
+                       outputs=list(act.outputs), attrs=attrs, name=kind)
         graph.replace_nodes_with([bias_node.id, act.id], fused)
         return True
     return False

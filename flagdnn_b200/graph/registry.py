@@ -152,6 +152,22 @@ def _run_fused_conv2d_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
                                       scale=scale, relu=True, **kw)
 
 
+def _gelu_code(attrs: dict) -> str:
+    return "gelu_tanh" if attrs.get("approximate", "none") == "tanh" else "gelu"
+
+
+def _run_fused_conv2d_bias_gelu(inputs: list, attrs: dict) -> torch.Tensor:
+    """inputs: x, w, bias[, scale]; gelu(conv * scale + bias) in the convolution's epilogue."""
+    from .. import conv_host as native
+
+    _require_device(inputs, "fused_conv2d_bias_gelu")
+    a = _public(attrs)
+    scale = inputs[3].reshape(-1) if len(inputs) > 3 else None
+    return native.conv2d_bias_act(inputs[0], inputs[1], inputs[2], stride=a.get("stride", 1),
+                                  padding=a.get("padding", 0), dilation=a.get("dilation", 1),
+                                  groups=a.get("groups", 1), scale=scale, activation=_gelu_code(attrs))
+
+
 def _run_fused_conv2d_bias_add_relu(inputs: list, attrs: dict) -> torch.Tensor:
     """inputs: x, w, residual[, bias[, scale]]; relu(conv * scale + bias + residual) in one kernel."""
     from .. import conv_host as native
@@ -231,6 +247,14 @@ def _run_fused_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
     return torch.relu(_run_bias_add(inputs, attrs))
 
 
+def _run_gelu(inputs: list, attrs: dict) -> torch.Tensor:
+    return torch.nn.functional.gelu(inputs[0], approximate=attrs.get("approximate", "none"))
+
+
+def _run_fused_bias_gelu(inputs: list, attrs: dict) -> torch.Tensor:
+    return torch.nn.functional.gelu(_run_bias_add(inputs, attrs), approximate=attrs.get("approximate", "none"))
+
+
 def _binary_runner(fn):
     def run(inputs: list, attrs: dict) -> torch.Tensor:
         other = inputs[1] if len(inputs) > 1 else attrs["other"]
@@ -248,6 +272,9 @@ def _register_defaults() -> None:
     register_op(OpSchema("bias_add", _normalize_binary("bias_add"), _infer_same, _run_bias_add))
     register_op(OpSchema("relu", _normalize_unary("relu"), _infer_same, _run_relu))
     register_op(OpSchema("fused_bias_relu", _normalize_binary("fused_bias_relu"), _infer_same, _run_fused_bias_relu))
+    register_op(OpSchema("gelu", _normalize_unary("gelu"), _infer_same, _run_gelu))
+    register_op(OpSchema("fused_bias_gelu", _normalize_binary("fused_bias_gelu"), _infer_same, _run_fused_bias_gelu))
+    register_op(OpSchema("fused_conv2d_bias_gelu", _normalize_conv2d, _infer_conv2d, _run_fused_conv2d_bias_gelu))
     register_op(OpSchema("add", _normalize_binary("add"), _infer_broadcast, _binary_runner(torch.add)))
     register_op(OpSchema("sub", _normalize_binary("sub"), _infer_broadcast, _binary_runner(torch.sub)))
     register_op(OpSchema("mul", _normalize_binary("mul"), _infer_broadcast, _binary_runner(torch.mul)))

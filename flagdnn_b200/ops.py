@@ -40,6 +40,10 @@ def _eager_relu(x: torch.Tensor, inplace: bool = False, **_: Any) -> torch.Tenso
     return torch.relu_(x) if inplace else torch.relu(x)
 
 
+def _eager_gelu(x: torch.Tensor, approximate: str = "none", **_: Any) -> torch.Tensor:
+    return torch.nn.functional.gelu(x, approximate=approximate)
+
+
 def _eager_binary(fn):
     def run(x, y, **_: Any):
         return fn(x, y)
@@ -49,6 +53,7 @@ def _eager_binary(fn):
 conv2d = _capturable("conv2d", _conv.conv2d)
 bias_add = _capturable("bias_add", _eager_bias_add)
 relu = _capturable("relu", _eager_relu)
+gelu = _capturable("gelu", _eager_gelu)
 add = _capturable("add", _eager_binary(torch.add))
 sub = _capturable("sub", _eager_binary(torch.sub))
 mul = _capturable("mul", _eager_binary(torch.mul))

@@ -55,6 +55,8 @@ typedef enum fdnn_status {
 /* epilogue activation */
 #define FDNN_ACT_NONE 0
 #define FDNN_ACT_RELU 1
+#define FDNN_ACT_GELU 2      /* 0.5 x (1 + erf(x / sqrt 2)), torch's default */
+#define FDNN_ACT_GELU_TANH 3 /* torch's approximate="tanh" form */
 
 /* Problem descriptor.  Replaces the argument list the reference passes to its
  * Triton launches (src/flag_dnn/graph/kernels/fused_conv.py:151-191,

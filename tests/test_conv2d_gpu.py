@@ -460,6 +460,38 @@ def test_residual_contract(fd):
         assert torch.isnan(out[1, 5, 2, 3]) and int(torch.isnan(out).sum()) == 1
 
 
+@pytest.mark.parametrize("approximate", ["none", "tanh"])
+@pytest.mark.parametrize("dtype_name,channels_last,groups", [("bfloat16", True, 1), ("float16", False, 1),
+                                                             ("float32", True, 1), ("float64", False, 1),
+                                                             ("float16", True, 4)])
+def test_gelu_epilogue(fd, dtype_name, channels_last, groups, approximate):
+    """gelu(conv * scale + bias) in the epilogue of every kernel family, both GELU forms, through the graph."""
+    dtype = getattr(torch, dtype_name)
+    n, c, hw, k = 3, 32, 13, 72
+    x = _to_dev(_rand((n, c, hw, hw), 120), dtype, channels_last)
+    w = _to_dev(_rand((k, c // groups, 3, 3), 121, std=(c // groups * 9) ** -0.5), dtype, channels_last)
+    b = _rand((k,), 122, std=0.5).to(dtype).cuda()
+    cdt = torch.float64 if dtype_name == "float64" else torch.float32
+    ref = torch.nn.functional.gelu(oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, groups, compute_dtype=cdt),
+                                   approximate=approximate)
+
+    @fd.graph
+    def layer(x, w, b):
+        return fd.gelu(fd.bias_add(fd.conv2d(x, w, padding=1, groups=groups), b), approximate=approximate)
+
+    compiled = fd.compile(layer, inputs=[x, w, b], options={"cache": None})
+    assert [nd.op_type for nd in compiled.graph.nodes] == ["fused_conv2d_bias_gelu"]
+    _check(compiled.run(x, w, b), ref, dtype_name)
+    got = fd.conv2d_bias_act(x, w, b, padding=1, groups=groups,
+                             activation="gelu_tanh" if approximate == "tanh" else "gelu")
+    _check(got, ref, dtype_name)
+    if dtype_name == "bfloat16":
+        x_nan = x.clone()
+        x_nan[0, 0, 0, 0] = float("nan")
+        out = fd.conv2d_bias_act(x_nan, w, b, padding=1, activation="gelu")
+        assert torch.isnan(out[0, :, 0, 0]).all() and not torch.isnan(out[1:]).any()
+
+
 def test_scaled_graph_folds_into_one_node(fd):
     x = _rand((2, 16, 8, 8), 20).to(torch.float16).cuda().contiguous(memory_format=torch.channels_last)
     w = _rand((24, 16, 3, 3), 21, std=0.08).to(torch.float16).cuda()

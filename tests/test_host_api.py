@@ -221,6 +221,31 @@ def test_graph_residual_tail_becomes_one_node():
     assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "add", "relu"]
 
 
+def test_graph_gelu_patterns():
+    specs = [flag_dnn.TensorSpec("x", (1, 8, 8, 8), "float16"), flag_dnn.TensorSpec("w", (16, 8, 3, 3), "float16"),
+             flag_dnn.TensorSpec("b", (16,), "float16")]
+
+    @flag_dnn.graph
+    def conv_gelu(x, w, b):
+        return flag_dnn.gelu(flag_dnn.bias_add(flag_dnn.conv2d(x, w, padding=1), b), approximate="tanh")
+
+    compiled = flag_dnn.compile(conv_gelu, inputs=specs, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["fused_conv2d_bias_gelu"]
+    assert compiled.graph.nodes[0].attrs["approximate"] == "tanh" and compiled.graph.nodes[0].attrs["activation"] == "gelu"
+
+    @flag_dnn.graph
+    def bias_gelu(x, w, b):                       # no convolution upstream: the reference's fused_bias_gelu
+        return flag_dnn.gelu(flag_dnn.bias_add(x, w))
+
+    compiled = flag_dnn.compile(bias_gelu, inputs=[specs[0], flag_dnn.TensorSpec("b8", (8,), "float16"), specs[2]],
+                                options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["fused_bias_gelu"]
+    x = torch.randn(1, 8, 8, 8, dtype=torch.float32)
+    b8 = torch.randn(8, dtype=torch.float32)
+    compiled32 = flag_dnn.compile(bias_gelu, inputs=[x, b8, b8], options={"cache": None})
+    torch.testing.assert_close(compiled32.run(x, b8, b8), torch.nn.functional.gelu(x + b8.view(1, 8, 1, 1)))
+
+
 def test_graph_memory_plan_cache_hit():
     cache = flag_dnn.PlanCache(enable_disk=False)
 

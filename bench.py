@@ -653,20 +653,179 @@ def run_stack_reference(args):
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 
 
+# ------------------------------------------------------------------ rows next to the path: block tail, mm
+EXTRA = {
+    # a ResNet block's last layer: 1x1 conv 64->256 at 56x56, folded scale + bias, shortcut add, ReLU, one kernel
+    "res": dict(desc="1x1 conv 64->256 56x56 N=256 bf16 NHWC + scale + bias + shortcut add + ReLU (one kernel)",
+                bound="hbm"),
+    # mm on the same kernels: a 1x1 convolution over one-pixel images
+    "mm": dict(desc="mm bf16 [8192 x 4096] @ [4096 x 4096] as a 1x1 convolution over one-pixel images",
+               bound="tensor"),
+}
+
+
+def run_extra(args):
+    """One JSON line for a row next to the hot path, same timing rules (cold L2, CUDA graph, events, clocks)."""
+    import torch
+
+    import flagdnn_b200 as fd
+
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise RuntimeError("the 'res' and 'mm' workloads are single-GPU measurements")
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    wl = EXTRA[args.workload]
+    peaks, peak_src = load_peaks()
+    bf = torch.bfloat16
+    g = torch.Generator(device=device).manual_seed(0)
+
+    def rnd(*shape, std=1.0):
+        return (torch.randn(*shape, generator=g, device=device) * std).to(bf)
+
+    if args.workload == "res":
+        n, c, hw, k = 256, 64, 56, 256
+        w = rnd(k, 1, 1, c, std=c ** -0.5).permute(0, 3, 1, 2)
+        scale, bias = (torch.rand(k, generator=g, device=device) + 0.5).to(bf), rnd(k, std=0.1)
+        per_set = 2 * n * hw * hw * (c + 2 * k)
+        n_sets = max(2, -(-3 * 126 * 2 ** 20 // per_set))
+        sets = [(rnd(n, hw, hw, c).permute(0, 3, 1, 2), rnd(n, hw, hw, k).permute(0, 3, 1, 2)) for _ in range(n_sets)]
+        flops = 2.0 * n * hw * hw * k * c
+        nbytes = per_set + 2 * (k * c + 2 * k)
+
+        def step(i):
+            x, shortcut = sets[i]
+            return fd.conv2d_bias_act(x, w, bias, scale=scale, relu=True, residual=shortcut)
+
+        def cpu_once(m):
+            import oracle
+
+            x, shortcut = sets[0][0][:m].cpu(), sets[0][1][:m].cpu()
+            wc, sc, bc = w.cpu(), scale.cpu(), bias.cpu()
+
+            def run():
+                y = oracle.conv2d_torch_cpu(x, wc, bc, 1, 0, 1, 1, scale=sc, compute_dtype=bf)
+                return torch.relu(y + shortcut)
+            return run, 2.0 * m * hw * hw * k * c, f"{m} of {n} images, conv2d*scale+bias, add, relu in bf16 on CPU"
+        h2d, d2h = 2 * n * hw * hw * (c + k), 2 * n * hw * hw * k
+        host_in = [t.contiguous(memory_format=torch.channels_last).cpu().pin_memory() for t in sets[0]]
+    else:
+        m_, k_, n_ = 8192, 4096, 4096
+        b_mat = rnd(k_, n_, std=k_ ** -0.5)
+        per_set = 2 * (m_ * k_ + m_ * n_)
+        n_sets = max(2, -(-3 * 126 * 2 ** 20 // per_set))
+        sets = [(rnd(m_, k_),) for _ in range(n_sets)]
+        flops = 2.0 * m_ * k_ * n_
+        nbytes = per_set + 2 * k_ * n_
+
+        def step(i):
+            return fd.mm(sets[i][0], b_mat)
+
+        def cpu_once(m):
+            a, bc = sets[0][0][:m].cpu(), b_mat.cpu()
+            return (lambda: torch.mm(a, bc)), 2.0 * m * k_ * n_, f"{m} of {m_} rows, torch.mm in bf16 on CPU"
+        h2d, d2h = 2 * m_ * k_, 2 * m_ * n_
+        host_in = [sets[0][0].cpu().pin_memory()]
+
+    for i in range(n_sets):
+        out = step(i)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        step(0)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(n_sets):
+                out = step(i)
+        replays = max(1, -(-min(args.steps, 400) // n_sets))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(max(1, -(-max(args.warmup, 3) // n_sets))):
+            graph.replay()
+        stream.synchronize()
+        with ClockSampler(0) as clocks:
+            e0.record(stream)
+            for _ in range(replays):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+    steps = replays * n_sets
+    ms_per_step = e0.elapsed_time(e1) / steps
+
+    # end to end: operands from pinned host memory, the result back, every step
+    dev_in = [torch.empty_like(t, device=device) for t in host_in]
+    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    if args.workload == "res":
+        host_out = torch.empty(out.shape, dtype=out.dtype).contiguous(memory_format=torch.channels_last).pin_memory()
+
+    def e2e_step():
+        for d, h in zip(dev_in, host_in):
+            d.copy_(h, non_blocking=True)
+        if args.workload == "res":
+            y = fd.conv2d_bias_act(dev_in[0], w, bias, scale=scale, relu=True, residual=dev_in[1])
+        else:
+            y = fd.mm(dev_in[0], b_mat)
+        host_out.copy_(y, non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(5):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / 5
+
+    use_all_host_threads(torch)
+    run, cpu_flops, sample = cpu_once(8 if args.workload == "res" else 256)
+    run()
+    times, t_all = [], time.perf_counter()
+    while len(times) < 3 or time.perf_counter() - t_all < 10.0:
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+    cpu_med = statistics.median(times)
+
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    if wl["bound"] == "tensor":
+        achieved, peak, unit = value, peaks["bf16_tflops"], "TFLOP/s"
+    else:
+        achieved, peak, unit = nbytes / (ms_per_step * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+    print(json.dumps({
+        "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bfloat16", "data": "synthetic",
+        "config": {"workload": args.workload, "description": wl["desc"], "launch": "cuda_graph_replay",
+                   "l2": f"{n_sets} rotating operand sets = {n_sets * per_set / 2**20:.0f} MiB > 126 MiB L2"},
+        "roofline": {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                     "traffic": None, "peak_source": f"of {peak_src}", "algorithmic_flops_per_launch": flops,
+                     "algorithmic_bytes_per_launch": nbytes},
+        "cpu_baseline": {"value": cpu_flops / cpu_med / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": f"{sample}, {len(times)} repeats, median"},
+        "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": 5, "ms_per_step": e2e_ms},
+        "gpu_launches": steps, "clocks": clocks.summary(),
+        "device_status_word": fd.device_status(),
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c5"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS) + ["c5"] + sorted(EXTRA))
     ap.add_argument("--batch", type=int, default=1024, help="total batch of the c5 workload (split over the ranks)")
     ap.add_argument("--eager", action="store_true",
                     help="launch every step through the API instead of replaying a CUDA graph (for profilers)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (short runs under a profiler)")
     args = ap.parse_args()
-    if args.workload == "c5":
+    if args.workload in EXTRA:
+        if args.impl == "reference":
+            raise SystemExit("the 'res' and 'mm' workloads report their CPU leg in the same line (cpu_baseline)")
+        run_extra(args)
+    elif args.workload == "c5":
         if args.impl == "reference":
             run_stack_reference(args)
         else:

@@ -466,6 +466,26 @@ int encode_output_map(CUtensorMap* tm, int dtype, void* base, int K, long long M
   return FDNN_OK;
 }
 
+// The residual tensor (laid out like a dense NHWC y) with one box per output tile: 128 rows x box_cols
+// channels, no swizzle.  The producers use it for L2 prefetches only; nothing is copied to shared memory.
+int encode_residual_map(CUtensorMap* tm, int dtype, const void* base, int K, long long M, long long row_stride,
+                        int box_cols) {
+  const int es = elem_size(dtype);
+  cuuint64_t dims[3] = {cuuint64_t(K), cuuint64_t(M), 1};
+  cuuint64_t strides[2] = {cuuint64_t(row_stride) * es, cuuint64_t(row_stride) * es * cuuint64_t(M)};
+  cuuint32_t box[3] = {cuuint32_t(box_cols), 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[160];
+    std::snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled (residual) failed with CUresult %d", int(r));
+    return fail(FDNN_CUDA_ERROR, buf);
+  }
+  return FDNN_OK;
+}
+
 __device__ uint32_t g_status_word;
 
 std::once_flag g_prepare_once[64];
@@ -584,10 +604,10 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
   if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
     p.b_resident = (n_gemm <= 256 && d.r <= igemm_pair_max_resident_steps()) ? 1 : 0;
-    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY2, p, plan.grid, stream);
+    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY2, tmY, p, plan.grid, stream);
   } else {
     // the single-CTA kernel has no fifth 16-bit map slot: the tail map travels in the unused tmA2 slot
-    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmY2, tmB, tmB, tmY, p, plan.grid, stream);
+    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmY2, tmB, tmB, tmY, tmY, p, plan.grid, stream);
   }
   if (e != cudaSuccess) return fail_cuda("low-channel igemm launch", e);
   return FDNN_OK;
@@ -840,9 +860,16 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
       st = encode_output_map(&tmY, d.dtype, y, d.k, p.M, row);
       if (st != FDNN_OK) return st;
       p.tma_store = 1;
+      p.y_row = row;
     } else {
       tmY = tmA;
     }
+  }
+  alignas(64) CUtensorMap tmR = tmY;
+  if (residual != nullptr && p.tma_store) {
+    const int box_cols = plan.algo == FDNN_ALGO_IGEMM_PAIR ? 256 : plan.tile_n;
+    st = encode_residual_map(&tmR, d.dtype, residual, d.k, p.M, p.y_row, box_cols);
+    if (st != FDNN_OK) return st;
   }
   p.prof = g_prof_buffer;
   p.status = g_status_ptr[dev];
@@ -850,9 +877,9 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
     if (!p.tma_store) return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs a dense channels-last output");
     p.b_resident = (d.k <= 256 && d.r * d.s * p.c_blocks <= igemm_pair_max_resident_steps()) ? 1 : 0;
-    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY, p, plan.grid, stream);
+    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY, tmR, p, plan.grid, stream);
   } else {
-    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, p, plan.grid, stream);
+    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, tmR, p, plan.grid, stream);
   }
   if (e != cudaSuccess) return fail_cuda("igemm launch", e);
   return FDNN_OK;

@@ -66,20 +66,23 @@ __device__ __forceinline__ void unpack2<float>(uint32_t w, float& a, float& b) {
   b = 0.0f;
 }
 
-// The 128 bytes of one row of the residual tensor that line up with one staged output row:
-// `src` points at column `col0` of this lane's row (nullptr: row outside the tensor, reads zeros).
-// Columns at or beyond `kout` read zeros; kout is a multiple of the 16-byte piece.
+// One 32-row x 128-byte box of the residual tensor, fetched so that every load instruction of the warp
+// covers four whole 128-byte rows: lane L takes the 16-byte piece L % 8 of rows 4 i + L / 8, i = 0..7.
+// `box` points at the box's first row and column (element units), `row_stride` is the distance between
+// rows, `rows` how many of the 32 exist, `col0` the box's first column; columns at or beyond `kout` and
+// missing rows read zeros (kout is a multiple of the 16-byte piece).
 template <typename T>
-__device__ __forceinline__ void load_residual_row(const T* src, int col0, int kout, uint32_t (&res)[32]) {
+__device__ __forceinline__ void load_residual_box(const T* box, long long row_stride, int rows, int col0, int kout,
+                                                  int lane, uint4 (&res)[8]) {
   constexpr int kPiece = 16 / int(sizeof(T));
+  const int piece = lane & 7;
+  const bool col_ok = col0 + piece * kPiece < kout;
 #pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (src != nullptr && col0 + q * kPiece < kout) v = __ldg(reinterpret_cast<const uint4*>(src + q * kPiece));
-    res[4 * q + 0] = v.x;
-    res[4 * q + 1] = v.y;
-    res[4 * q + 2] = v.z;
-    res[4 * q + 3] = v.w;
+  for (int i = 0; i < 8; ++i) {
+    const int row = 4 * i + (lane >> 3);
+    res[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (box != nullptr && col_ok && row < rows)
+      res[i] = __ldg(reinterpret_cast<const uint4*>(box + row * row_stride + piece * kPiece));
   }
 }
 
@@ -93,16 +96,18 @@ __device__ __forceinline__ void load_residual_row(const T* src, int col0, int ko
 // st_row, st_img     y coordinates (row, image) of the warp's first row; st_rows: valid rows (<= 0: none)
 // store_seq          running count of this warp's staged boxes (selects the staging buffer)
 // RES                a residual tensor (same layout as y) is added before the activation
-// res_row            this lane's residual row at column n0 (nullptr for a row outside the tensor)
-// res                the residual row of the first column group, loaded by the caller before it
-//                    waited for the accumulator so that the load hides behind the main loop
+// res_box            the residual at this warp's first row and column n0 (nullptr: no valid row);
+//                    res_stride: elements between its rows; res_rows: how many of the 32 rows exist
+// res                the residual box of the first column group (load_residual_box), fetched by the caller
+//                    before it waited for the accumulator so that the load hides behind the main loop
 template <typename T, int BN, bool RES = false, int NBUF = 2>
 __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int act,
                                                     const float* s_scale, const float* s_bias,
                                                     uint8_t* my_out, int lane, const CUtensorMap* tm_full,
                                                     const CUtensorMap* tm_tail, int st_row, int st_img,
                                                     int st_rows, uint32_t& store_seq,
-                                                    const T* res_row = nullptr, uint32_t* res = nullptr) {
+                                                    const T* res_box = nullptr, long long res_stride = 0,
+                                                    int res_rows = 0, uint4* res = nullptr) {
   constexpr int kPerStore = 128 / int(sizeof(T));  // channels per staged row: 64 (16-bit) or 32 (fp32)
   constexpr int kLoads = kPerStore / 32;
   int groups = (kout - n0 + kPerStore - 1) / kPerStore;
@@ -113,10 +118,21 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
   for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + l * 32, raw[l]);
 #pragma unroll 1
   for (int g = 0; g < groups; ++g) {
-    uint32_t res_next[32];
-    if (RES && g + 1 < groups) {
-      load_residual_row<T>(res_row != nullptr ? res_row + (g + 1) * kPerStore : nullptr,
-                           n0 + (g + 1) * kPerStore, kout, res_next);
+    uint8_t* buf = my_out + (NBUF == 2 ? (store_seq & 1u) * (32 * 128) : 0u);  // alternates across groups AND tiles
+    ++store_seq;
+    if constexpr (RES) {
+      // the box goes through the staging buffer: stored as fetched (four rows per instruction), read back
+      // row per lane, with the swizzle of the output so that neither side has bank conflicts
+      if (lane == 0) {
+        if constexpr (NBUF == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = 4 * i + (lane >> 3);
+        *reinterpret_cast<uint4*>(buf + row * 128 + (((lane & 7) ^ (row & 7)) << 4)) = res[i];
+      }
+      __syncwarp();  // each lane reads its own row back piece by piece while it computes
     }
     tmem_ld_wait();
     uint32_t row[32];  // the 128 bytes this lane contributes
@@ -133,14 +149,18 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
         float v3 = fmaf(__uint_as_float(raw[l][4 * j4 + 3]), sc.w, bi.w);
         if constexpr (RES) {
           if constexpr (std::is_same<T, float>::value) {
-            v0 += __uint_as_float(res[4 * j4 + 0]);
-            v1 += __uint_as_float(res[4 * j4 + 1]);
-            v2 += __uint_as_float(res[4 * j4 + 2]);
-            v3 += __uint_as_float(res[4 * j4 + 3]);
+            const uint4 mine = *reinterpret_cast<const uint4*>(buf + lane * 128 + ((j4 ^ (lane & 7)) << 4));
+            v0 += __uint_as_float(mine.x);
+            v1 += __uint_as_float(mine.y);
+            v2 += __uint_as_float(mine.z);
+            v3 += __uint_as_float(mine.w);
           } else {
+            // 16-byte piece l*4 + j4/2 of the row holds the eight values of two passes of this loop
+            const uint2 mine = *reinterpret_cast<const uint2*>(
+                buf + lane * 128 + (((l * 4 + (j4 >> 1)) ^ (lane & 7)) << 4) + ((j4 & 1) << 3));
             float r0, r1, r2, r3;
-            unpack2<T>(res[l * 16 + 2 * j4 + 0], r0, r1);
-            unpack2<T>(res[l * 16 + 2 * j4 + 1], r2, r3);
+            unpack2<T>(mine.x, r0, r1);
+            unpack2<T>(mine.y, r2, r3);
             v0 += r0;
             v1 += r1;
             v2 += r2;
@@ -169,15 +189,11 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
 #pragma unroll
       for (int l = 0; l < kLoads; ++l) tmem_ld_32x32b_x32(t_row + (g + 1) * kPerStore + l * 32, raw[l]);
     }
-    if (RES && g + 1 < groups) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) res[j] = res_next[j];
-    }
-    uint8_t* buf = my_out + (NBUF == 2 ? (store_seq & 1u) * (32 * 128) : 0u);  // alternates across groups AND tiles
-    ++store_seq;
-    if (lane == 0) {
-      // the box staged NBUF groups ago has left this buffer
-      if constexpr (NBUF == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
+    if constexpr (!RES) {
+      if (lane == 0) {
+        // the box staged NBUF groups ago has left this buffer
+        if constexpr (NBUF == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
+      }
     }
     __syncwarp();
 #pragma unroll
@@ -185,6 +201,13 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
       // 128-byte swizzle: the 16-byte pieces of neighbouring rows land in different banks
       *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) << 4)) =
           make_uint4(row[4 * q], row[4 * q + 1], row[4 * q + 2], row[4 * q + 3]);
+    }
+    if constexpr (RES) {
+      // the next group's box is requested now (not earlier: its 32 registers would not fit beside the
+      // accumulator columns and the finished row) and travels while this one leaves
+      if (g + 1 < groups)
+        load_residual_box<T>(res_box != nullptr ? res_box + (g + 1) * kPerStore : nullptr, res_stride, res_rows,
+                             n0 + (g + 1) * kPerStore, kout, lane, *reinterpret_cast<uint4(*)[8]>(res));
     }
     fence_proxy_async_smem();
     __syncwarp();

@@ -64,7 +64,7 @@ template <typename T, bool RES>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmY2,
-                       const IgemmParams p) {
+                       const __grid_constant__ CUtensorMap tmR, const IgemmParams p) {
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : 1u;
   constexpr uint32_t kIdesc = make_idesc(kFmt, 2 * kRows, kPairN);
 
@@ -169,6 +169,11 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           const int ow0 = rem - oh0 * p.OW;
           w_base = ow0 * p.stride_w - p.pad_left;
           h_base = oh0 * p.stride_h - p.pad_top;
+        }
+        if constexpr (RES) {
+          // this CTA's 128 x 256 residual values of the tile, asked into L2 a whole main loop before the
+          // epilogue reads them
+          if (p.residual != nullptr && !p.lowc) tma_prefetch_l2_3d(&tmR, n_tile * kPairN, m_tile * kRows, 0);
         }
         const uint32_t a_tx = p.lowc ? uint32_t(p.a_tx_bytes) : uint32_t(kABytes);
         const uint32_t pair_tx = 2 * (a_tx + (b_resident ? 0u : uint32_t(kBBytes)));
@@ -312,20 +317,13 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         staged_n_tile = n_tile;
       }
       const int m_tile = 2 * m_pair + int(rank);
-      // the residual row of the first column group is requested before the accumulator wait
-      const T* res_row = nullptr;
-      uint32_t res0[32];
-      if (RES && g_res != nullptr) {
-        const int m = m_tile * kRows + ew * 32 + lane;
-        if (m < p.M) {
-          const int ohw = p.OH * p.OW;
-          const int img = m / ohw;
-          const int rem = m - img * ohw;
-          const int oh = rem / p.OW;
-          res_row = g_res + img * p.y_sn + oh * p.y_sh + (rem - oh * p.OW) * p.y_sw + n0;
-        }
-        load_residual_row<T>(res_row, n0, p.Kout, res0);
-      }
+      // the residual box of the first column group is requested before the accumulator wait; y is dense
+      // NHWC here, so output pixel m starts at element m * y_row
+      const long long m_first = (long long)m_tile * kRows + ew * 32;
+      const int res_rows = p.M - m_first < 32 ? int(p.M - m_first) : 32;
+      const T* res_box = (g_res != nullptr && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
+      uint4 res0[8];
+      if constexpr (RES) load_residual_box<T>(res_box, p.y_row, res_rows, n0, p.Kout, lane, res0);
       const long long et0 = p.prof ? clock64() : 0;
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
       ok = __all_sync(0xffffffffu, ok);
@@ -344,7 +342,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN + chalf * kWarpCols;
       epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.act, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
-                                     st_row, st_img, st_rows, store_seq, res_row, res0);
+                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows, res0);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }
@@ -367,7 +365,8 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
 template <typename T>
 cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
-                          const CUtensorMap& tmY2, const IgemmParams& p, int grid, cudaStream_t stream) {
+                          const CUtensorMap& tmY2, const CUtensorMap& tmR, const IgemmParams& p, int grid,
+                          cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3(kThreadsPair, 1, 1);
@@ -382,8 +381,8 @@ cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = launch_overlap_enabled() ? 2 : 1;
-  if (p.residual != nullptr) return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, true>, tmA, tmB, tmY, tmY2, p);
-  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, false>, tmA, tmB, tmY, tmY2, p);
+  if (p.residual != nullptr) return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, true>, tmA, tmB, tmY, tmY2, tmR, p);
+  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, false>, tmA, tmB, tmY, tmY2, tmR, p);
 }
 
 }  // namespace
@@ -409,10 +408,10 @@ int igemm_pair_threads() { return kThreadsPair; }
 int igemm_pair_max_resident_steps() { return kMaxResidentSteps; }
 
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                              const CUtensorMap& tmY, const CUtensorMap& tmY2, const IgemmParams& p,
-                              int grid, cudaStream_t stream) {
-  if (dtype == FDNN_F16) return launch_pair_t<__half>(tmA, tmB, tmY, tmY2, p, grid, stream);
-  if (dtype == FDNN_BF16) return launch_pair_t<__nv_bfloat16>(tmA, tmB, tmY, tmY2, p, grid, stream);
+                              const CUtensorMap& tmY, const CUtensorMap& tmY2, const CUtensorMap& tmR,
+                              const IgemmParams& p, int grid, cudaStream_t stream) {
+  if (dtype == FDNN_F16) return launch_pair_t<__half>(tmA, tmB, tmY, tmY2, tmR, p, grid, stream);
+  if (dtype == FDNN_BF16) return launch_pair_t<__nv_bfloat16>(tmA, tmB, tmY, tmY2, tmR, p, grid, stream);
   return cudaErrorInvalidValue;
 }
 

@@ -6,8 +6,10 @@
 // output tiles.  Three roles, one pipeline:
 //   warp 0      TMA producer: per (r, s, channel block) one im2col-mode copy of
 //               128 pixels x 128 bytes of activations (padding arrives as the
-//               copy's zero fill) and one tiled copy of the filter slice, into
-//               a ring of shared-memory stages guarded by full/empty mbarriers;
+//               copy's zero fill) into a ring of shared-memory stages guarded
+//               by full/empty mbarriers;
+//               and one tiled copy of the filter slice (optionally issued by a
+//               second producer warp, FDNN_PRODUCERS=2);
 //   warp 1      MMA issuer: tcgen05.mma from shared-memory descriptors into one
 //               of two fp32 accumulators in tensor memory; tcgen05.commit frees
 //               the stage and, after the last reduction step, publishes the
@@ -46,7 +48,16 @@ constexpr int kRowBytes = 128;      // one swizzled shared-memory row
 #define FDNN_EPI_WARPS 8
 #endif
 constexpr int kEpiWarps = FDNN_EPI_WARPS;  // 8: two per tensor-memory lane quarter (4: one)
-constexpr int kThreads = 64 + 32 * kEpiWarps;  // producer, issuer, epilogue warps
+#ifndef FDNN_PRODUCERS
+#define FDNN_PRODUCERS 1
+#endif
+// 2: activation and filter copies come from different warps.  Measured on B200: no faster on any layer
+// shape (a reduction step is bound by shared-memory bandwidth, operand reads of the MMAs plus the copies'
+// fills, not by the issuing thread), so one producer is the default.
+constexpr int kProducers = FDNN_PRODUCERS;
+constexpr int kFilterProducerWarp = 2 + kEpiWarps;  // after the epilogue warps (their index decides their lane quarter)
+// producer, issuer, epilogue warps, then the filter producer and an idle warp (whole groups of four)
+constexpr int kThreads = 64 + 32 * kEpiWarps + (kProducers == 2 ? 64 : 0);
 
 template <typename T, int BN>
 struct TileCfg {
@@ -103,7 +114,8 @@ template <typename T, int BN, bool RES>
 __global__ void __launch_bounds__(kThreads, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                   const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
-                  const __grid_constant__ CUtensorMap tmY, const IgemmParams p) {
+                  const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmR,
+                  const IgemmParams p) {
   using Cfg = TileCfg<T, BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : (std::is_same<T, __nv_bfloat16>::value ? 1u : 2u);
@@ -129,7 +141,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   griddep_launch_dependents();  // all CTAs of this grid are resident: the next launch may queue behind them
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
-      mbar_init(&full_bar[i], 1);
+      mbar_init(&full_bar[i], kProducers);
       mbar_init(&empty_bar[i], 1);
     }
     mbar_init(&tmem_full[0], 1);
@@ -161,50 +173,58 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int k_iters = p.R * p.S * p.c_blocks;
   const int ohw = p.OH * p.OW;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool alive = true;
-      long long prof_wait = 0, prof_issue = 0, prof_t0 = p.prof ? clock64() : 0;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-        const int m_tile = tile / p.n_tiles;
-        const int n_tile = tile - m_tile * p.n_tiles;
-        int img, w_base, h_base;
-        if (p.lowc) {
-          img = m_tile / p.tiles_per_image;
-          const int ti = m_tile - img * p.tiles_per_image;
-          w_base = 0;
-          h_base = ti * p.ohs * p.stride_h - p.pad_top;
-        } else {
-          const int m0 = m_tile * kBM;
-          img = m0 / ohw;
-          const int rem = m0 - img * ohw;
-          const int oh0 = rem / p.OW;
-          const int ow0 = rem - oh0 * p.OW;
-          w_base = ow0 * p.stride_w - p.pad_left;
-          h_base = oh0 * p.stride_h - p.pad_top;
-        }
-        const uint32_t stage_tx = p.lowc ? uint32_t(p.a_tx_bytes + Cfg::kBBytes) : uint32_t(Cfg::kStageBytes);
-        for (int r = 0; r < p.R && alive; ++r) {
-          for (int s = 0; s < p.S && alive; ++s) {
-            const uint16_t off_w = static_cast<uint16_t>(s * p.dil_w);
-            const uint16_t off_h = static_cast<uint16_t>(r * p.dil_h);
-            const int tap = r * p.S + s;
-            for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
-              const uint32_t stage = it % kStages;
-              const uint32_t phase = (it / kStages) & 1u;
-              const long long pt0 = p.prof ? clock64() : 0;
-              if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
-                                     kIncidentProducerWait)) {
-                alive = false;
-                break;
-              }
-              const long long pt1 = p.prof ? clock64() : 0;
-              prof_wait += pt1 - pt0;
-              uint8_t* st = stage_base + stage * Cfg::kStageBytes;
-              mbar_arrive_expect_tx(&full_bar[stage], stage_tx);
-              const int c0 = cb * Cfg::kKB;
+  // One elected thread issues copies; with two producers the activation and the filter copies of a
+  // stage come from different warps and each credits its own bytes to the stage's "full" barrier.
+  auto produce = [&](const bool do_a, const bool do_b, const bool record) {
+    uint32_t it = 0;
+    bool alive = true;
+    long long prof_wait = 0, prof_issue = 0, prof_t0 = p.prof ? clock64() : 0;
+    for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_tile = tile / p.n_tiles;
+      const int n_tile = tile - m_tile * p.n_tiles;
+      int img, w_base, h_base;
+      if (p.lowc) {
+        img = m_tile / p.tiles_per_image;
+        const int ti = m_tile - img * p.tiles_per_image;
+        w_base = 0;
+        h_base = ti * p.ohs * p.stride_h - p.pad_top;
+      } else {
+        const int m0 = m_tile * kBM;
+        img = m0 / ohw;
+        const int rem = m0 - img * ohw;
+        const int oh0 = rem / p.OW;
+        const int ow0 = rem - oh0 * p.OW;
+        w_base = ow0 * p.stride_w - p.pad_left;
+        h_base = oh0 * p.stride_h - p.pad_top;
+      }
+      if constexpr (RES) {
+        // the epilogue of this tile will read its 128 x BN residual values a whole main loop from now:
+        // ask for them to be brought into L2 so that its loads are short and HBM reads are requested early
+        if (do_a && p.residual != nullptr && p.tma_store && !p.lowc) tma_prefetch_l2_3d(&tmR, n_tile * BN, m_tile * kBM, 0);
+      }
+      const uint32_t a_tx = (Cfg::kSplit ? 2u : 1u) * (p.lowc ? uint32_t(p.a_tx_bytes) : uint32_t(Cfg::kABytes));
+      const uint32_t b_tx = (Cfg::kSplit ? 2u : 1u) * uint32_t(Cfg::kBBytes);
+      const uint32_t my_tx = (do_a ? a_tx : 0u) + (do_b ? b_tx : 0u);
+      for (int r = 0; r < p.R && alive; ++r) {
+        for (int s = 0; s < p.S && alive; ++s) {
+          const uint16_t off_w = static_cast<uint16_t>(s * p.dil_w);
+          const uint16_t off_h = static_cast<uint16_t>(r * p.dil_h);
+          const int tap = r * p.S + s;
+          for (int cb = 0; cb < p.c_blocks; ++cb, ++it) {
+            const uint32_t stage = it % kStages;
+            const uint32_t phase = (it / kStages) & 1u;
+            const long long pt0 = p.prof ? clock64() : 0;
+            if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
+                                   kIncidentProducerWait)) {
+              alive = false;
+              break;
+            }
+            const long long pt1 = p.prof ? clock64() : 0;
+            prof_wait += pt1 - pt0;
+            uint8_t* st = stage_base + stage * Cfg::kStageBytes;
+            mbar_arrive_expect_tx(&full_bar[stage], my_tx);
+            const int c0 = cb * Cfg::kKB;
+            if (do_a) {
               if (p.lowc) {
                 // window copy: (64 elements, all quads of a row, `ohs` rows at the conv stride, image)
                 tma_load_4d(st, &tmA, &full_bar[stage], 0, 0, h_base + r * p.dil_h, img);
@@ -214,31 +234,43 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               if constexpr (Cfg::kSplit) {
                 tma_load_im2col_4d(st + Cfg::kABytes, &tmA2, &full_bar[stage], c0, w_base, h_base,
                                    img, off_w, off_h);
+              }
+            }
+            if (do_b) {
+              if constexpr (Cfg::kSplit) {
                 tma_load_3d(st + 2 * Cfg::kABytes, &tmB, &full_bar[stage], c0, tap, n_tile * BN);
                 tma_load_3d(st + 2 * Cfg::kABytes + Cfg::kBBytes, &tmB2, &full_bar[stage], c0, tap,
                             n_tile * BN);
               } else {
                 tma_load_3d(st + Cfg::kABytes, &tmB, &full_bar[stage], c0, tap, n_tile * BN);
               }
-              if (p.prof) prof_issue += clock64() - pt1;
             }
+            if (p.prof) prof_issue += clock64() - pt1;
           }
         }
       }
-      if (p.prof && blockIdx.x == 0) {
-        p.prof[0] = prof_wait; p.prof[1] = prof_issue; p.prof[2] = clock64() - prof_t0; p.prof[3] = it;
-      }
-      if (!alive || *abort_flag) {
-        // Teardown after an incident: let the copies already issued land before
-        // the CTA gives its shared memory back.
-        const uint32_t first = it > uint32_t(kStages) ? it - kStages : 0u;
-        for (uint32_t j = first; j < it; ++j) {
-          volatile uint32_t never = 0;
-          mbar_wait_bounded(&full_bar[j % kStages], (j / kStages) & 1u, &never, p.status,
-                            kIncidentDrainWait, kWaitLimitCycles / 16);
-        }
+    }
+    if (record && p.prof && blockIdx.x == 0) {
+      p.prof[0] = prof_wait; p.prof[1] = prof_issue; p.prof[2] = clock64() - prof_t0; p.prof[3] = it;
+    }
+    if (!alive || *abort_flag) {
+      // Teardown after an incident: let the copies already issued land before
+      // the CTA gives its shared memory back.
+      const uint32_t first = it > uint32_t(kStages) ? it - kStages : 0u;
+      for (uint32_t j = first; j < it; ++j) {
+        volatile uint32_t never = 0;
+        mbar_wait_bounded(&full_bar[j % kStages], (j / kStages) & 1u, &never, p.status,
+                          kIncidentDrainWait, kWaitLimitCycles / 16);
       }
     }
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) produce(true, kProducers == 1, true);
+  } else if (kProducers == 2 && warp == kFilterProducerWarp) {
+    // ---------------------------------------------- producer of the filter copies
+    if (lane == 0) produce(false, true, false);
   } else if (warp == 1) {
     // -------------------------------------------------------------- issuer
     if (lane == 0) {
@@ -345,11 +377,14 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int ow = rem - oh * p.OW;
         y_off = img * p.y_sn + oh * p.y_sh + ow * p.y_sw;
       }
-      // the residual row of the first column group is requested before the accumulator wait
-      const T* res_row = (g_res != nullptr && row_ok) ? g_res + y_off + n0 : nullptr;
-      uint32_t res0[32];
+      // the residual box of the first column group is requested before the accumulator wait; with a
+      // dense NHWC y, output pixel m starts at element m * y_row
+      const int m_first = m_tile * kBM + ew * 32;
+      const int res_rows = p.M - m_first < 32 ? p.M - m_first : 32;
+      const T* res_box = (g_res != nullptr && p.tma_store && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
+      uint4 res0[8];
       if constexpr (RES) {
-        if (p.tma_store) load_residual_row<T>(res_row, n0, p.Kout, res0);
+        if (p.tma_store) load_residual_box<T>(res_box, p.y_row, res_rows, n0, p.Kout, lane, res0);
       }
 
       const long long et0 = p.prof ? clock64() : 0;
@@ -377,7 +412,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
         epilogue_store_tile<T, WC, RES>(t_row, n0, p.Kout, p.act, s_scale, s_bias,
                                    out_stage + (warp - 2) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
-                                   st_img, st_rows, store_seq, res_row, res0);
+                                   st_img, st_rows, store_seq, res_box, p.y_row, res_rows, res0);
       } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < WC / 32; ++chunk) {
@@ -427,8 +462,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <typename T, int BN>
 cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
-                       const CUtensorMap& tmB2, const CUtensorMap& tmY, const IgemmParams& p, int grid,
-                       cudaStream_t stream) {
+                       const CUtensorMap& tmB2, const CUtensorMap& tmY, const CUtensorMap& tmR, const IgemmParams& p,
+                       int grid, cudaStream_t stream) {
   using Cfg = TileCfg<T, BN>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -441,8 +476,8 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CU
   cfg.attrs = attr;
   cfg.numAttrs = launch_overlap_enabled() ? 1 : 0;
   if (p.residual != nullptr)
-    return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, true>, tmA, tmA2, tmB, tmB2, tmY, p);
-  return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, false>, tmA, tmA2, tmB, tmB2, tmY, p);
+    return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, true>, tmA, tmA2, tmB, tmB2, tmY, tmR, p);
+  return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, false>, tmA, tmA2, tmB, tmB2, tmY, tmR, p);
 }
 
 template <typename T, int BN>
@@ -487,8 +522,8 @@ int igemm_stages(int dtype, int tile_n) {
 
 cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
                          const CUtensorMap& tmB, const CUtensorMap& tmB2, const CUtensorMap& tmY,
-                         const IgemmParams& p, int grid, cudaStream_t stream) {
-#define FDNN_GO(T, BN) return launch_one<T, BN>(tmA, tmA2, tmB, tmB2, tmY, p, grid, stream);
+                         const CUtensorMap& tmR, const IgemmParams& p, int grid, cudaStream_t stream) {
+#define FDNN_GO(T, BN) return launch_one<T, BN>(tmA, tmA2, tmB, tmB2, tmY, tmR, p, grid, stream);
   if (dtype == FDNN_F16) {
     if (tile_n == 64) FDNN_GO(__half, 64)
     if (tile_n == 128) FDNN_GO(__half, 128)

@@ -23,6 +23,7 @@ struct IgemmParams {
   int c_blocks;          // ceil(Cpad / channels per 128-byte row)
   int m_tiles, n_tiles;
   long long y_sn, y_sk, y_sh, y_sw;  // element strides of y
+  long long y_row;       // dense NHWC y (tma_store): elements between consecutive output pixels
   const void* bias;      // [Kout] in the tensor dtype, or nullptr
   const void* scale;     // [Kout] in the tensor dtype, or nullptr
   void* y;
@@ -51,10 +52,11 @@ bool launch_overlap_enabled();
 
 // Launchers (defined in conv_igemm_sm100.cu).  `dtype` is FDNN_F16/BF16/F32.
 // tmA2 / tmB2 are the low-half operands of the split-TF32 path (ignored for
-// 16-bit types); tmY is the output map used when p.tma_store is set.  Returns a cudaError_t from the launch.
+// 16-bit types); tmY is the output map used when p.tma_store is set; tmR covers the residual tensor
+// with one tile-sized box (L2 prefetch; read only when p.residual is set and y is dense NHWC).  Returns a cudaError_t from the launch.
 cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
                          const CUtensorMap& tmB, const CUtensorMap& tmB2, const CUtensorMap& tmY,
-                         const IgemmParams& p, int grid, cudaStream_t stream);
+                         const CUtensorMap& tmR, const IgemmParams& p, int grid, cudaStream_t stream);
 // Dynamic shared memory and pipeline depth of a tile configuration.
 int igemm_smem_bytes(int dtype, int tile_n);
 int igemm_stages(int dtype, int tile_n);
@@ -65,8 +67,8 @@ cudaError_t igemm_prepare_device();
 // CTA-pair variant (conv_igemm_pair_sm100.cu): 16-bit types, 256 x 256 pair
 // tiles, TMA-store epilogue only (p.tma_store must be set).  `grid` must be even.
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
-                              const CUtensorMap& tmY, const CUtensorMap& tmY2, const IgemmParams& p,
-                              int grid, cudaStream_t stream);
+                              const CUtensorMap& tmY, const CUtensorMap& tmY2, const CUtensorMap& tmR,
+                              const IgemmParams& p, int grid, cudaStream_t stream);
 cudaError_t igemm_pair_prepare_device();
 int igemm_pair_smem_bytes();
 int igemm_pair_stages();

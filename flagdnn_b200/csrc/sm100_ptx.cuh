@@ -109,6 +109,14 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
 }
 
+// Asks for a 3-D box of a tensor to be brought into L2; nothing lands in shared memory and nothing waits.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* tm, int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+
 // Tiled 3-D tensor copy global -> shared of this CTA, completion on `bar`.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar,
                                             int32_t c0, int32_t c1, int32_t c2) {

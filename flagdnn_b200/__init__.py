@@ -32,7 +32,9 @@ from .graph import (  # noqa: F401
     compile,
     graph,
 )
-from .ops import add, bias_add, conv1d, conv2d, gelu, mm, mul, relu, sub  # noqa: F401
+from .ops import (  # noqa: F401
+    adaptive_avg_pool2d, add, bias_add, conv1d, conv2d, gelu, max_pool2d, mm, mul, relu, sub,
+)
 
 __version__ = "0.1.0"
 

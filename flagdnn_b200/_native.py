@@ -32,6 +32,8 @@ EXPORTED_SYMBOLS = (
     "fdnn_conv2d_pack_weight",
     "fdnn_conv2d_fwd",
     "fdnn_conv2d_fwd_residual",
+    "fdnn_max_pool2d_fwd",
+    "fdnn_adaptive_avg_pool2d_fwd",
     "fdnn_conv2d_fwd_host",
     "fdnn_conv2d_host_arena_bytes",
     "fdnn_device_status",
@@ -83,6 +85,13 @@ class ConvPlan(ctypes.Structure):
         return {name: getattr(self, name) for name, _ in self._fields_}
 
 
+class PoolDesc(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_int32) for name in
+                ("dtype", "n", "c", "h", "w", "oh", "ow", "kernel_h", "kernel_w", "stride_h", "stride_w",
+                 "pad_h", "pad_w", "dil_h", "dil_w")] + \
+               [("x_strides", ctypes.c_int64 * 4), ("y_strides", ctypes.c_int64 * 4)]
+
+
 class NativeError(RuntimeError):
     """A non-OK status that maps to RuntimeError in the reference's convention."""
 
@@ -112,6 +121,10 @@ def load() -> ctypes.CDLL:
     lib.fdnn_conv2d_pack_weight.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, i64, vp]
     lib.fdnn_conv2d_fwd.restype = i32
     lib.fdnn_conv2d_fwd.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, i32, vp, vp, i64, vp]
+    lib.fdnn_max_pool2d_fwd.restype = i32
+    lib.fdnn_max_pool2d_fwd.argtypes = [ctypes.POINTER(PoolDesc), vp, vp, vp, vp]
+    lib.fdnn_adaptive_avg_pool2d_fwd.restype = i32
+    lib.fdnn_adaptive_avg_pool2d_fwd.argtypes = [ctypes.POINTER(PoolDesc), vp, vp, vp]
     lib.fdnn_conv2d_fwd_residual.restype = i32
     lib.fdnn_conv2d_fwd_residual.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.fdnn_conv2d_fwd_host.restype = i32

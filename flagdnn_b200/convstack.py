@@ -7,8 +7,9 @@ shortcut of each stage's first block.  Every convolution carries a BN-folded
 per-channel scale and bias; all but each block's third 1x1 and the projection
 are followed by ReLU (those two feed the residual add).
 
-Only the convolutions run through this library; the pooling after the stem and
-the residual add + ReLU are plain torch glue.
+The convolutions and the pooling after the stem run through this library; the
+residual add + ReLU is fused into each block's last convolution on request,
+otherwise plain torch glue.
 """
 from __future__ import annotations
 
@@ -17,7 +18,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from . import conv_host
+from . import conv_host, pool_host
 
 
 @dataclass(frozen=True)
@@ -116,7 +117,7 @@ class ResNet50ConvStack:
             return out
 
         y = step(0, x)
-        y = torch.nn.functional.max_pool2d(y, 3, 2, 1)
+        y = pool_host.max_pool2d(y, 3, 2, 1) if y.is_cuda else torch.nn.functional.max_pool2d(y, 3, 2, 1)
         index = 1
         for blocks in (3, 4, 6, 3):
             for block in range(blocks):

@@ -890,6 +890,52 @@ int fdnn_debug_set_profile_buffer(void* device_buffer_16_int64) {
   return FDNN_OK;
 }
 
+static int pool_params(const fdnn_pool_desc* d, const void* x, void* y, PoolParams* p, bool max_pool) {
+  if (d == nullptr) return fail(FDNN_BAD_PARAM, "descriptor is NULL");
+  if (d->dtype < FDNN_F16 || d->dtype > FDNN_F64) return fail(FDNN_BAD_PARAM, "unknown dtype");
+  if (d->n < 0 || d->c < 0 || d->h < 0 || d->w < 0 || d->oh < 0 || d->ow < 0)
+    return fail(FDNN_BAD_PARAM, "negative extent");
+  if (max_pool) {
+    if (d->kernel_h <= 0 || d->kernel_w <= 0 || d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 ||
+        d->dil_w <= 0 || d->pad_h < 0 || d->pad_w < 0)
+      return fail(FDNN_BAD_PARAM, "kernel, stride and dilation must be positive, padding non-negative");
+    if (2 * d->pad_h > d->kernel_h || 2 * d->pad_w > d->kernel_w)
+      return fail(FDNN_BAD_PARAM, "pad should be at most half of effective kernel size");
+  }
+  const long long total = (long long)d->n * d->c * d->oh * d->ow;
+  if (total > 0 && (x == nullptr || y == nullptr)) return fail(FDNN_BAD_PARAM, "x and y must not be NULL");
+  p->N = d->n; p->C = d->c; p->H = d->h; p->W = d->w; p->OH = d->oh; p->OW = d->ow;
+  p->kh = d->kernel_h; p->kw = d->kernel_w; p->sh = d->stride_h; p->sw = d->stride_w;
+  p->ph = d->pad_h; p->pw = d->pad_w; p->dh = d->dil_h; p->dw = d->dil_w;
+  for (int i = 0; i < 4; ++i) {
+    p->x_s[i] = d->x_strides[i];
+    p->y_s[i] = d->y_strides[i];
+  }
+  p->x = x; p->y = y; p->idx = nullptr;
+  return FDNN_OK;
+}
+
+int fdnn_max_pool2d_fwd(const fdnn_pool_desc* desc, const void* x, void* y, int64_t* indices, void* stream) {
+  PoolParams p;
+  int st = pool_params(desc, x, y, &p, true);
+  if (st != FDNN_OK) return st;
+  p.idx = reinterpret_cast<long long*>(indices);
+  cudaError_t e = launch_max_pool2d(desc->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda("max_pool2d launch", e);
+  return FDNN_OK;
+}
+
+int fdnn_adaptive_avg_pool2d_fwd(const fdnn_pool_desc* desc, const void* x, void* y, void* stream) {
+  PoolParams p;
+  int st = pool_params(desc, x, y, &p, false);
+  if (st != FDNN_OK) return st;
+  if ((long long)desc->n * desc->c * desc->oh * desc->ow > 0 && (desc->h == 0 || desc->w == 0))
+    return fail(FDNN_BAD_PARAM, "adaptive pooling needs a non-empty input plane");
+  cudaError_t e = launch_adaptive_avg_pool2d(desc->dtype, p, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda("adaptive_avg_pool2d launch", e);
+  return FDNN_OK;
+}
+
 int fdnn_device_status(uint32_t* word) {
   uint32_t v = 0;
   cudaError_t e = cudaDeviceSynchronize();

@@ -98,8 +98,9 @@ __device__ __forceinline__ void load_residual_box(const T* box, long long row_st
 // RES                a residual tensor (same layout as y) is added before the activation
 // res_box            the residual at this warp's first row and column n0 (nullptr: no valid row);
 //                    res_stride: elements between its rows; res_rows: how many of the 32 rows exist
-// res                the residual box of the first column group (load_residual_box), fetched by the caller
-//                    before it waited for the accumulator so that the load hides behind the main loop
+//                    (the producer asked for the tile's residual values to be brought into L2 a main loop
+//                    earlier, so these loads are L2 hits; holding a prefetched box in registers across
+//                    column groups does not fit beside the accumulator columns and spills)
 template <typename T, int BN, bool RES = false, int NBUF = 2>
 __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int act,
                                                     const float* s_scale, const float* s_bias,
@@ -107,7 +108,7 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
                                                     const CUtensorMap* tm_tail, int st_row, int st_img,
                                                     int st_rows, uint32_t& store_seq,
                                                     const T* res_box = nullptr, long long res_stride = 0,
-                                                    int res_rows = 0, uint4* res = nullptr) {
+                                                    int res_rows = 0) {
   constexpr int kPerStore = 128 / int(sizeof(T));  // channels per staged row: 64 (16-bit) or 32 (fp32)
   constexpr int kLoads = kPerStore / 32;
   int groups = (kout - n0 + kPerStore - 1) / kPerStore;
@@ -123,6 +124,9 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
     if constexpr (RES) {
       // the box goes through the staging buffer: stored as fetched (four rows per instruction), read back
       // row per lane, with the swizzle of the output so that neither side has bank conflicts
+      uint4 res[8];
+      load_residual_box<T>(res_box != nullptr ? res_box + g * kPerStore : nullptr, res_stride, res_rows,
+                           n0 + g * kPerStore, kout, lane, res);
       if (lane == 0) {
         if constexpr (NBUF == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
       }
@@ -201,13 +205,6 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
       // 128-byte swizzle: the 16-byte pieces of neighbouring rows land in different banks
       *reinterpret_cast<uint4*>(buf + lane * 128 + ((q ^ (lane & 7)) << 4)) =
           make_uint4(row[4 * q], row[4 * q + 1], row[4 * q + 2], row[4 * q + 3]);
-    }
-    if constexpr (RES) {
-      // the next group's box is requested now (not earlier: its 32 registers would not fit beside the
-      // accumulator columns and the finished row) and travels while this one leaves
-      if (g + 1 < groups)
-        load_residual_box<T>(res_box != nullptr ? res_box + (g + 1) * kPerStore : nullptr, res_stride, res_rows,
-                             n0 + (g + 1) * kPerStore, kout, lane, *reinterpret_cast<uint4(*)[8]>(res));
     }
     fence_proxy_async_smem();
     __syncwarp();

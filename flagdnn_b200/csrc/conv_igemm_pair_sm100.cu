@@ -16,7 +16,7 @@
 //   warp 1 (leader)    issuer: waits "stage full", issues the pair MMAs, commits
 //                      to both CTAs' "stage empty" barriers, and after the last
 //                      step to both CTAs' "accumulator full" barriers
-//   warps 2..9 (each)  epilogue on the CTA's own 128 rows (two warps per tensor-
+//   warps 4..11 (each) epilogue on the CTA's own 128 rows (two warps per tensor-
 //                      memory lane quarter, half of the columns each), then an
 //                      arrive on the leader's "accumulator empty" barrier
 #include <cuda_bf16.h>
@@ -51,7 +51,12 @@ constexpr int kEpiWarpsPair = FDNN_PAIR_EPI_WARPS;   // 8: two per tensor-memory
 constexpr int kColSplitPair = kEpiWarpsPair / 4;
 constexpr int kWarpCols = kPairN / kColSplitPair;
 constexpr int kOutBufs = kEpiWarpsPair == 8 ? 1 : 2; // TMA-store staging buffers per warp (32 KB in all either way)
-constexpr int kThreadsPair = 64 + 32 * kEpiWarpsPair;
+constexpr int kFirstEpiWarpPair = 4;                 // warp group 0: producer, issuer, two idle warps
+constexpr int kThreadsPair = 32 * (kFirstEpiWarpPair + kEpiWarpsPair);
+// warp group 0 hands registers to the epilogue warp groups (see conv_igemm_sm100.cu)
+constexpr int kRegsLeanPair = 104;
+constexpr int kRegsEpiloguePair = kEpiWarpsPair == 8 ? 200 : 232;
+static_assert(128 * kRegsLeanPair + 32 * kEpiWarpsPair * kRegsEpiloguePair <= 65536, "register file budget");
 constexpr int kOutBytes = kEpiWarpsPair * kOutBufs * 32 * kRowB;
 constexpr int kEpiBytes = kEpiWarpsPair * 2 * kWarpCols * int(sizeof(float));
 constexpr int kBarBytes = (2 * kMaxStages + 6) * 8 + 16;
@@ -134,6 +139,8 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int num_pairs = gridDim.x >> 1;
   const int ohw = p.OH * p.OW;
 
+  if (warp < kFirstEpiWarpPair) {
+  warpgroup_reg_dec<kRegsLeanPair>();
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -285,16 +292,19 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         mbar_wait_bounded(drain_bar, 0u, &never, p.status, kIncidentDrainWait, kWaitLimitCycles / 16);
       }
     }
+  }
   } else {
+  warpgroup_reg_inc<kRegsEpiloguePair>();
+  {
     // ------------------------------------------------------------ epilogue
     const int ew = warp & 3;
-    const int chalf = (warp - 2) >> 2;  // which share of the tile's columns this warp drains
-    float* s_scale = epi_stage + (warp - 2) * 2 * kWarpCols;
+    const int chalf = (warp - kFirstEpiWarpPair) >> 2;  // which share of the tile's columns this warp drains
+    float* s_scale = epi_stage + (warp - kFirstEpiWarpPair) * 2 * kWarpCols;
     float* s_bias = s_scale + kWarpCols;
     const T* g_bias = static_cast<const T*>(p.bias);
     const T* g_scale = static_cast<const T*>(p.scale);
     const T* g_res = (RES && !p.lowc) ? static_cast<const T*>(p.residual) : nullptr;
-    uint8_t* my_out = out_stage + (warp - 2) * kOutBufs * 32 * kRowB;
+    uint8_t* my_out = out_stage + (warp - kFirstEpiWarpPair) * kOutBufs * 32 * kRowB;
     const uint32_t tempty_leader = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     uint32_t tcount = 0;
     uint32_t store_seq = 0;
@@ -317,13 +327,10 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         staged_n_tile = n_tile;
       }
       const int m_tile = 2 * m_pair + int(rank);
-      // the residual box of the first column group is requested before the accumulator wait; y is dense
-      // NHWC here, so output pixel m starts at element m * y_row
+      // where this warp's residual rows start: y is dense NHWC here, output pixel m is at element m * y_row
       const long long m_first = (long long)m_tile * kRows + ew * 32;
       const int res_rows = p.M - m_first < 32 ? int(p.M - m_first) : 32;
       const T* res_box = (g_res != nullptr && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
-      uint4 res0[8];
-      if constexpr (RES) load_residual_box<T>(res_box, p.y_row, res_rows, n0, p.Kout, lane, res0);
       const long long et0 = p.prof ? clock64() : 0;
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
       ok = __all_sync(0xffffffffu, ok);
@@ -342,14 +349,15 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN + chalf * kWarpCols;
       epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.act, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
-                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows, res0);
+                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }
     if (lane == 0) bulk_wait_group0();
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {  // first epilogue warp of the first leader
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 32 * kFirstEpiWarpPair) {  // first epilogue warp of the first leader
       p.prof[8] = prof_ewait; p.prof[9] = clock64() - prof_t0;
     }
+  }
   }
 
   // Neither CTA may retire while its partner can still signal its barriers or

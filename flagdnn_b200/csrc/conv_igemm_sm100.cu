@@ -14,7 +14,7 @@
 //               of two fp32 accumulators in tensor memory; tcgen05.commit frees
 //               the stage and, after the last reduction step, publishes the
 //               accumulator;
-//   warps 2..9  epilogue: tcgen05.ld of the finished accumulator, per-channel
+//   warps 4..11 epilogue: tcgen05.ld of the finished accumulator, per-channel
 //               scale, bias, ReLU, one rounding to the output type, store —
 //               while the issuer already fills the other accumulator.  Two
 //               warps share each tensor-memory lane quarter and take half of
@@ -55,9 +55,17 @@ constexpr int kEpiWarps = FDNN_EPI_WARPS;  // 8: two per tensor-memory lane quar
 // shape (a reduction step is bound by shared-memory bandwidth, operand reads of the MMAs plus the copies'
 // fills, not by the issuing thread), so one producer is the default.
 constexpr int kProducers = FDNN_PRODUCERS;
-constexpr int kFilterProducerWarp = 2 + kEpiWarps;  // after the epilogue warps (their index decides their lane quarter)
-// producer, issuer, epilogue warps, then the filter producer and an idle warp (whole groups of four)
-constexpr int kThreads = 64 + 32 * kEpiWarps + (kProducers == 2 ? 64 : 0);
+constexpr int kFilterProducerWarp = 2;  // in the first warp group, beside the producer and the issuer
+// Warp group 0 holds the producer, the issuer (and the optional filter producer); the epilogue warps are
+// whole warp groups after it, so that group 0 can hand most of its registers to them: the kernel starts
+// with 168 registers per thread (64 K / 384), group 0 keeps kRegsLean and each epilogue thread gets
+// kRegsEpilogue — the epilogue holds two 32-column accumulator slices, a finished row and, with a
+// residual, a 32 x 128-byte box in flight, which does not fit in 168 without spilling.
+constexpr int kFirstEpiWarp = 4;
+constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
+constexpr int kRegsLean = 104;
+constexpr int kRegsEpilogue = kEpiWarps == 8 ? 200 : 232;  // 128 * 104 + 256 * 200 = 384 * 168
+static_assert(128 * kRegsLean + 32 * kEpiWarps * kRegsEpilogue <= 65536, "register file budget");
 
 template <typename T, int BN>
 struct TileCfg {
@@ -265,6 +273,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   };
 
+  if (warp < kFirstEpiWarp) {
+  warpgroup_reg_dec<kRegsLean>();
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) produce(true, kProducers == 1, true);
@@ -334,12 +344,15 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         mbar_wait_bounded(drain_bar, 0u, &never, p.status, kIncidentDrainWait, kWaitLimitCycles / 16);
       }
     }
-  } else if (warp - 2 < Cfg::kActiveEpiWarps) {
+  }
+  } else {
+  warpgroup_reg_inc<kRegsEpilogue>();
+  if (warp - kFirstEpiWarp < Cfg::kActiveEpiWarps) {
     // ------------------------------------------------------------ epilogue
     constexpr int WC = Cfg::kWarpCols;
     const int ew = warp & 3;           // tensor-memory lane quarter this warp may read
-    const int chalf = (warp - 2) >> 2;  // which share of the tile's columns it drains
-    float* s_scale = epi_stage + (warp - 2) * 2 * WC;
+    const int chalf = (warp - kFirstEpiWarp) >> 2;  // which share of the tile's columns it drains
+    float* s_scale = epi_stage + (warp - kFirstEpiWarp) * 2 * WC;
     float* s_bias = s_scale + WC;
     const T* g_bias = static_cast<const T*>(p.bias);
     const T* g_scale = static_cast<const T*>(p.scale);
@@ -377,16 +390,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int ow = rem - oh * p.OW;
         y_off = img * p.y_sn + oh * p.y_sh + ow * p.y_sw;
       }
-      // the residual box of the first column group is requested before the accumulator wait; with a
-      // dense NHWC y, output pixel m starts at element m * y_row
+      // where this warp's residual rows start: with a dense NHWC y, output pixel m is at element m * y_row
       const int m_first = m_tile * kBM + ew * 32;
       const int res_rows = p.M - m_first < 32 ? p.M - m_first : 32;
       const T* res_box = (g_res != nullptr && p.tma_store && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
-      uint4 res0[8];
-      if constexpr (RES) {
-        if (p.tma_store) load_residual_box<T>(res_box, p.y_row, res_rows, n0, p.Kout, lane, res0);
-      }
-
       const long long et0 = p.prof ? clock64() : 0;
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
       ok = __all_sync(0xffffffffu, ok);
@@ -411,8 +418,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // a tile's last warp may own fewer than 32 valid rows: tmA2 then holds a second
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
         epilogue_store_tile<T, WC, RES>(t_row, n0, p.Kout, p.act, s_scale, s_bias,
-                                   out_stage + (warp - 2) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
-                                   st_img, st_rows, store_seq, res_box, p.y_row, res_rows, res0);
+                                   out_stage + (warp - kFirstEpiWarp) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
+                                   st_img, st_rows, store_seq, res_box, p.y_row, res_rows);
       } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < WC / 32; ++chunk) {
@@ -447,9 +454,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_arrive(&tmem_empty[buf]);
     }
     if (p.tma_store && lane == 0) bulk_wait_group0();  // stores must be done before the CTA retires
-    if (p.prof && blockIdx.x == 0 && threadIdx.x == 64) {  // first epilogue warp
+    if (p.prof && blockIdx.x == 0 && threadIdx.x == 32 * kFirstEpiWarp) {  // first epilogue warp
       p.prof[8] = prof_ewait; p.prof[9] = clock64() - prof_t0;
     }
+  }
   }
 
   tc_fence_before();

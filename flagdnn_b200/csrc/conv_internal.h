@@ -90,6 +90,18 @@ struct DirectParams {
 };
 cudaError_t launch_direct(int dtype, const DirectParams& p, cudaStream_t stream);
 
+// Pooling (pool.cu): element strides of x and y in (n, c, h, w) order; idx (max pooling only) may be null.
+struct PoolParams {
+  int N, C, H, W, OH, OW;
+  int kh, kw, sh, sw, ph, pw, dh, dw;
+  long long x_s[4], y_s[4];
+  const void* x;
+  void* y;
+  long long* idx;
+};
+cudaError_t launch_max_pool2d(int dtype, const PoolParams& p, cudaStream_t stream);
+cudaError_t launch_adaptive_avg_pool2d(int dtype, const PoolParams& p, cudaStream_t stream);
+
 // Relayout kernels (conv_repack.cu).
 // x[N,C,H,W] (any strides) -> dense NHWC with C padded to c_pad (zeros).  For
 // f32 two planes are written: TF32-rounded high halves at dst, the rounded

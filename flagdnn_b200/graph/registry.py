@@ -189,6 +189,85 @@ def _infer_conv2d_residual(specs: list, attrs: dict) -> TensorSpec:
     return _infer_conv2d([specs[0], specs[1]], attrs)
 
 
+# ---------------------------------------------------------------- pooling
+_MAXPOOL_ARG_NAMES = ["input", "kernel_size", "stride", "padding", "dilation", "ceil_mode", "return_indices"]
+
+
+def _normalize_max_pool2d(ctx: Any, args: tuple, kwargs: dict) -> tuple:
+    params = {"stride": None, "padding": 0, "dilation": 1, "ceil_mode": False, "return_indices": False}
+    params.update(kwargs)
+    for name, arg in zip(_MAXPOOL_ARG_NAMES, args):
+        params[name] = arg
+    if params.get("return_indices"):
+        raise NotImplementedError("graph max_pool2d returns values only (return_indices=False)")
+    if "input" not in params or "kernel_size" not in params:
+        raise TypeError("max_pool2d expects an input and a kernel_size")
+    return [ctx.as_value(params.pop("input"), "input")], params
+
+
+def _infer_max_pool2d(specs: list, attrs: dict) -> TensorSpec:
+    import math
+
+    x = specs[0]
+    if len(x.shape) != 4:
+        raise RuntimeError("graph max_pool2d expects a 4D input")
+    kernel = _pair(attrs["kernel_size"])
+    stride = _pair(attrs["stride"]) if attrs.get("stride") is not None else kernel
+    pad, dil = _pair(attrs.get("padding", 0)), _pair(attrs.get("dilation", 1))
+    ceil_mode = bool(attrs.get("ceil_mode", False))
+
+    def out(length, p, d, k, s):
+        o = (length + 2 * p - d * (k - 1) - 1) / s + 1
+        o = math.ceil(o) if ceil_mode else math.floor(o)
+        if ceil_mode and (o - 1) * s >= length + p:
+            o -= 1
+        return max(int(o), 0)
+
+    n, c, h, w = x.shape
+    return TensorSpec("", (n, c, out(h, pad[0], dil[0], kernel[0], stride[0]), out(w, pad[1], dil[1], kernel[1], stride[1])),
+                      x.dtype, layout=x.layout, device=x.device)
+
+
+def _run_max_pool2d(inputs: list, attrs: dict) -> torch.Tensor:
+    from .. import pool_host
+
+    a = _public(attrs)
+    if not _on_device(inputs):   # glue on CPU specs (shape checks, tests); device tensors use the library
+        return torch.nn.functional.max_pool2d(inputs[0], a["kernel_size"], a.get("stride"), a.get("padding", 0),
+                                              a.get("dilation", 1), bool(a.get("ceil_mode", False)))
+    return pool_host.max_pool2d(inputs[0], a["kernel_size"], a.get("stride"), a.get("padding", 0),
+                                a.get("dilation", 1), bool(a.get("ceil_mode", False)))
+
+
+def _normalize_adaptive_avg_pool2d(ctx: Any, args: tuple, kwargs: dict) -> tuple:
+    params = dict(kwargs)
+    for name, arg in zip(["input", "output_size"], args):
+        params[name] = arg
+    if "input" not in params or "output_size" not in params:
+        raise TypeError("adaptive_avg_pool2d expects an input and an output_size")
+    return [ctx.as_value(params.pop("input"), "input")], params
+
+
+def _infer_adaptive_avg_pool2d(specs: list, attrs: dict) -> TensorSpec:
+    x = specs[0]
+    if len(x.shape) != 4:
+        raise RuntimeError("graph adaptive_avg_pool2d expects a 4D input")
+    size = attrs["output_size"]
+    oh, ow = (size, size) if isinstance(size, int) else size
+    oh = x.shape[2] if oh is None else int(oh)
+    ow = x.shape[3] if ow is None else int(ow)
+    return TensorSpec("", (x.shape[0], x.shape[1], oh, ow), x.dtype, layout=x.layout, device=x.device)
+
+
+def _run_adaptive_avg_pool2d(inputs: list, attrs: dict) -> torch.Tensor:
+    from .. import pool_host
+
+    a = _public(attrs)
+    if not _on_device(inputs):
+        return torch.nn.functional.adaptive_avg_pool2d(inputs[0], a["output_size"])
+    return pool_host.adaptive_avg_pool2d(inputs[0], a["output_size"])
+
+
 # -------------------------------------------------------------- glue ops
 def _normalize_unary(name: str):
     def normalize(ctx: Any, args: tuple, kwargs: dict) -> tuple:
@@ -269,6 +348,9 @@ def _register_defaults() -> None:
     register_op(OpSchema("fused_conv2d_bias_relu", _normalize_conv2d, _infer_conv2d, _run_fused_conv2d_bias_relu))
     register_op(OpSchema("fused_conv2d_bias_add_relu", _normalize_conv2d_residual, _infer_conv2d_residual,
                          _run_fused_conv2d_bias_add_relu))
+    register_op(OpSchema("max_pool2d", _normalize_max_pool2d, _infer_max_pool2d, _run_max_pool2d))
+    register_op(OpSchema("adaptive_avg_pool2d", _normalize_adaptive_avg_pool2d, _infer_adaptive_avg_pool2d,
+                         _run_adaptive_avg_pool2d))
     register_op(OpSchema("bias_add", _normalize_binary("bias_add"), _infer_same, _run_bias_add))
     register_op(OpSchema("relu", _normalize_unary("relu"), _infer_same, _run_relu))
     register_op(OpSchema("fused_bias_relu", _normalize_binary("fused_bias_relu"), _infer_same, _run_fused_bias_relu))

@@ -12,6 +12,7 @@ from typing import Any
 import torch
 
 from . import conv_host as _conv
+from . import pool_host as _pool
 from .graph.compiler import current_capture
 
 
@@ -54,6 +55,8 @@ conv2d = _capturable("conv2d", _conv.conv2d)
 bias_add = _capturable("bias_add", _eager_bias_add)
 relu = _capturable("relu", _eager_relu)
 gelu = _capturable("gelu", _eager_gelu)
+max_pool2d = _capturable("max_pool2d", _pool.max_pool2d)
+adaptive_avg_pool2d = _capturable("adaptive_avg_pool2d", _pool.adaptive_avg_pool2d)
 add = _capturable("add", _eager_binary(torch.add))
 sub = _capturable("sub", _eager_binary(torch.sub))
 mul = _capturable("mul", _eager_binary(torch.mul))

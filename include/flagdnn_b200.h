@@ -162,6 +162,30 @@ int fdnn_conv2d_fwd_host(const fdnn_conv_desc* desc, const void* x_host,
 /* Device bytes fdnn_conv2d_fwd_host needs for `desc`. */
 int fdnn_conv2d_host_arena_bytes(const fdnn_conv_desc* desc, int64_t* bytes);
 
+/* Pooling next to the path (the layers either side of a ResNet's convolutions).
+ * Strides are element strides in (n, c, h, w) order; NCHW and channels-last
+ * both work, dense channels-last f16/bf16 with c % 8 == 0 moves 16 bytes per
+ * thread.  `oh` / `ow` are the output sizes the caller computed (for max
+ * pooling with the ceil_mode rule of src/flag_dnn/ops/max_pool2d.py:201-230). */
+typedef struct fdnn_pool_desc {
+  int32_t dtype; /* FDNN_F16 / BF16 / F32 / F64 */
+  int32_t n, c, h, w, oh, ow;
+  int32_t kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w; /* max pooling only */
+  int64_t x_strides[4];
+  int64_t y_strides[4];
+} fdnn_pool_desc;
+
+/* Replaces the Triton launches of max_pool2d (src/flag_dnn/ops/max_pool2d.py:174-330).
+ * -inf padding, NaN wins; `indices` (int64, y's strides, ih * W + iw) may be NULL. */
+int fdnn_max_pool2d_fwd(const fdnn_pool_desc* desc, const void* x, void* y,
+                        int64_t* indices, void* stream);
+
+/* Replaces the Triton launches of adaptive_avg_pool2d
+ * (src/flag_dnn/ops/adaptive_avg_pool2d.py:456-640): window
+ * [floor(o*L/O), ceil((o+1)*L/O)), fp32 (fp64) accumulate. */
+int fdnn_adaptive_avg_pool2d_fwd(const fdnn_pool_desc* desc, const void* x,
+                                 void* y, void* stream);
+
 /* Every wait inside the kernels is bounded; a wait that runs out records a
  * code in a per-device status word and the kernel returns early.  This call
  * synchronises the current device, returns the word in *word (0 = no

@@ -64,7 +64,7 @@ def test_query_plans_headline_configs(native_lib):
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
     assert (plan.algo, plan.tile_m, plan.tile_n, plan.stages) == (nat.ALGO_IGEMM, 128, 256, 3)
     assert plan.workspace_bytes == 0 and plan.packed_weight_bytes == 0
-    assert plan.oh == 14 and plan.ow == 14 and plan.block == 320 and plan.grid == 148
+    assert plan.oh == 14 and plan.ow == 14 and plan.block == 384 and plan.grid == 148
     assert plan.flops == pytest.approx(59.190e9, rel=1e-3)
     assert plan.bytes == pytest.approx(52.56e6, rel=1e-2)
     # 1x1 bottleneck reduce: narrow tile so the activations are read once

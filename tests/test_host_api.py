@@ -246,6 +246,23 @@ def test_graph_gelu_patterns():
     torch.testing.assert_close(compiled32.run(x, b8, b8), torch.nn.functional.gelu(x + b8.view(1, 8, 1, 1)))
 
 
+def test_pooling_ops_capture_and_refuse_cpu_eagerly():
+    @flag_dnn.graph
+    def tail(x):
+        return flag_dnn.adaptive_avg_pool2d(flag_dnn.max_pool2d(x, 3, stride=2, padding=1, ceil_mode=True), (1, None))
+
+    compiled = flag_dnn.compile(tail, inputs=[flag_dnn.TensorSpec("x", (2, 8, 15, 15), "float32")], options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["max_pool2d", "adaptive_avg_pool2d"]
+    x = torch.randn(2, 8, 15, 15)
+    ref = torch.nn.functional.adaptive_avg_pool2d(torch.nn.functional.max_pool2d(x, 3, 2, 1, ceil_mode=True), (1, None))
+    out = compiled.run(x)                        # CPU tensors: shape-checking glue, as for the other glue ops
+    assert out.shape == (2, 8, 1, 8) and torch.allclose(out, ref)
+    with pytest.raises(NotImplementedError, match="requires CUDA input"):
+        flag_dnn.max_pool2d(x, 2)
+    with pytest.raises(NotImplementedError, match="requires CUDA input"):
+        flag_dnn.adaptive_avg_pool2d(x, 1)
+
+
 def test_graph_memory_plan_cache_hit():
     cache = flag_dnn.PlanCache(enable_disk=False)
 

@@ -658,8 +658,8 @@ EXTRA = {
     # a ResNet block's last layer: 1x1 conv 64->256 at 56x56, folded scale + bias, shortcut add, ReLU, one kernel
     "res": dict(desc="1x1 conv 64->256 56x56 N=256 bf16 NHWC + scale + bias + shortcut add + ReLU (one kernel)",
                 bound="hbm"),
-    # mm on the same kernels: a 1x1 convolution over one-pixel images
-    "mm": dict(desc="mm bf16 [8192 x 4096] @ [4096 x 4096] as a 1x1 convolution over one-pixel images",
+    # mm on the same kernels: a 1x1 convolution over a row of M pixels
+    "mm": dict(desc="mm bf16 [8192 x 4096] @ [4096 x 4096] as a 1x1 convolution over a row of M pixels",
                bound="tensor"),
 }
 

@@ -471,7 +471,7 @@ def mm(
     out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Drop-in for ``flag_dnn.ops.mm`` (src/flag_dnn/ops/mm.py:336) on real tensors: ``input @ mat2`` is a
-    1x1 convolution over M one-pixel images with K channels whose filter is ``mat2`` transposed, so it runs
+    1x1 convolution over a row of M pixels with K channels whose filter is ``mat2`` transposed, so it runs
     on the same kernels (fp64 on the direct one).  Checks and messages follow src/flag_dnn/ops/mm.py:100-140,
     the ``out`` handling src/flag_dnn/ops/mm.py:153-181.  Complex tensors and an fp32 result from 16-bit
     operands are not implemented on this path."""
@@ -513,9 +513,12 @@ def mm(
         if k == 0:
             y.zero_()
         else:
-            x4 = input.unsqueeze(-1).unsqueeze(-1)                 # [M, K, 1, 1]: M images of one pixel
+            # one image of one row of M pixels with K channels (row m of `input` is pixel m), so that a tile's
+            # 128 GEMM rows are 128 neighbouring pixels of a row; the result [1, N, 1, M] is y transposed
+            x4 = input.t().unsqueeze(0).unsqueeze(2)               # [1, K, 1, M]
             w4 = mat2.t().unsqueeze(-1).unsqueeze(-1)              # [N, K, 1, 1]: the filter is mat2 transposed
-            _run(x4, w4, None, None, (1, 1), (0, 0, 0, 0), (1, 1), 1, nat.ACT_NONE, out=y.view(m, n, 1, 1))
+            _run(x4, w4, None, None, (1, 1), (0, 0, 0, 0), (1, 1), 1, nat.ACT_NONE,
+                 out=y.t().unsqueeze(0).unsqueeze(2))              # [1, N, 1, M] over y's memory
     if out is not None and y is not out:
         out.copy_(y)
         return out

@@ -127,7 +127,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   }
   tc_fence_before();
   __syncthreads();
-  griddep_wait();      // from here on global memory is touched: the launch before this one must be complete
+  griddep_wait();      // from here on global memory is consumed: the launch before this one must be complete
   cluster_sync_all();  // both CTAs' barriers exist before anyone signals across
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;

@@ -175,7 +175,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  griddep_wait();  // from here on global memory is touched: the launch before this one must be complete
+  griddep_wait();  // from here on global memory is consumed: the launch before this one must be complete
 
   const int total_tiles = p.m_tiles * p.n_tiles;
   const int k_iters = p.R * p.S * p.c_blocks;

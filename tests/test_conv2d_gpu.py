@@ -157,7 +157,7 @@ MM_CASES = [(0, 3, 4), (2, 0, 4), (2, 3, 0), (2, 3, 4), (7, 5, 3), (16, 17, 15),
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16", "float16", "float64"])
 @pytest.mark.parametrize("case", MM_CASES, ids=["x".join(map(str, c)) for c in MM_CASES])
 def test_mm_matches_torch_cpu(fd, case, dtype_name, use_out):
-    """mm as a 1x1 convolution over one-pixel images, the reference's cases (tests/test_mm.py:9-17) and larger."""
+    """mm as a 1x1 convolution over a row of M pixels, the reference's cases (tests/test_mm.py:9-17) and larger."""
     m, k, n = case
     dtype = getattr(torch, dtype_name)
     a = torch.empty(m, k).uniform_(-1, 1, generator=torch.Generator().manual_seed(5)).to(dtype).cuda()

@@ -140,7 +140,9 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int ohw = p.OH * p.OW;
 
   if (warp < kFirstEpiWarpPair) {
+#ifndef FDNN_NO_REG_REALLOC
   warpgroup_reg_dec<kRegsLeanPair>();
+#endif
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -294,7 +296,9 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
   }
   } else {
+#ifndef FDNN_NO_REG_REALLOC
   warpgroup_reg_inc<kRegsEpiloguePair>();
+#endif
   {
     // ------------------------------------------------------------ epilogue
     const int ew = warp & 3;

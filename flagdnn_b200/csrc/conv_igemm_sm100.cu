@@ -274,7 +274,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   };
 
   if (warp < kFirstEpiWarp) {
+#ifndef FDNN_NO_REG_REALLOC
   warpgroup_reg_dec<kRegsLean>();
+#endif
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) produce(true, kProducers == 1, true);
@@ -346,7 +348,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   }
   } else {
+#ifndef FDNN_NO_REG_REALLOC
   warpgroup_reg_inc<kRegsEpilogue>();
+#endif
   if (warp - kFirstEpiWarp < Cfg::kActiveEpiWarps) {
     // ------------------------------------------------------------ epilogue
     constexpr int WC = Cfg::kWarpCols;

@@ -22,6 +22,16 @@ def native_lib():
 
 
 @pytest.fixture(scope="session")
+def golden_next():
+    """Outputs of the unmodified reference (CPU graphs) for the rows next to the path: block tails, GELU, mm."""
+    import numpy as np
+
+    path = os.path.join(ROOT, "tests", "golden", "reference_cpu_outputs_next.npz")
+    with np.load(path) as data:
+        return {k: data[k] for k in data.files}
+
+
+@pytest.fixture(scope="session")
 def golden():
     import numpy as np
 

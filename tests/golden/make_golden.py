@@ -173,6 +173,76 @@ def main() -> None:
 
     np.savez_compressed(OUT_DIR / "reference_cpu_outputs.npz", **records)
     print("wrote", OUT_DIR / "reference_cpu_outputs.npz", len(records), "arrays")
+    _write_next_rows(flag_dnn)
+
+
+# Graphs next to the conv -> bias -> ReLU path, as the unmodified reference runs them on CPU: a residual
+# block's tail (conv, per-channel scale, bias, shortcut add, ReLU), conv -> bias -> GELU in both forms, mm.
+TAIL_CASES = [((2, 16, 12, 12), (24, 16, 1, 1), 1, 0), ((2, 8, 10, 10), (8, 8, 3, 3), 1, 1),
+              ((1, 32, 9, 9), (40, 32, 3, 3), 2, 1)]
+GELU_CASES = [((2, 8, 10, 10), (12, 8, 3, 3), 1, 1, "none"), ((1, 16, 7, 7), (16, 16, 1, 1), 1, 0, "tanh")]
+MM_CASES = [(2, 3, 4), (7, 5, 3), (16, 17, 15), (32, 64, 16), (64, 128, 96)]
+
+
+def _write_next_rows(flag_dnn) -> None:
+    records = {}
+    for idx, (ishape, wshape, stride, padding) in enumerate(TAIL_CASES):
+        seed = 3000 + idx
+        fan_in = wshape[1] * wshape[2] * wshape[3]
+        x = _seeded(ishape, seed)
+        w = _seeded(wshape, seed + 100, std=fan_in ** -0.5)
+        s = torch.rand(wshape[0], 1, 1, generator=torch.Generator().manual_seed(seed + 150)) + 0.5
+        b = _seeded((wshape[0],), seed + 200, std=0.1)
+        oh = (ishape[2] + 2 * padding - wshape[2]) // stride + 1
+        shortcut = _seeded((ishape[0], wshape[0], oh, oh), seed + 300)
+
+        @flag_dnn.graph
+        def tail(x, weight, scale, bias, shortcut, _s=stride, _p=padding):
+            y = flag_dnn.conv2d(x, weight, stride=_s, padding=_p)
+            y = flag_dnn.bias_add(flag_dnn.mul(y, scale), bias)
+            return flag_dnn.relu(flag_dnn.add(y, shortcut))
+
+        compiled = flag_dnn.compile(tail, inputs=[x, w, s, b, shortcut], options={"cache": None})
+        y = compiled.run(x.clone(), w.clone(), s.clone(), b.clone(), shortcut.clone())
+        key = f"tail_{idx:02d}"
+        for name, t in (("x", x), ("w", w), ("s", s), ("b", b), ("r", shortcut), ("y", y)):
+            records[f"{key}_{name}"] = t.numpy()
+        records[key + "_meta"] = np.array([stride, padding], dtype=np.int64)
+
+    for idx, (ishape, wshape, stride, padding, approximate) in enumerate(GELU_CASES):
+        seed = 4000 + idx
+        fan_in = wshape[1] * wshape[2] * wshape[3]
+        x = _seeded(ishape, seed)
+        w = _seeded(wshape, seed + 100, std=fan_in ** -0.5)
+        b = _seeded((wshape[0],), seed + 200, std=0.5)
+
+        @flag_dnn.graph
+        def act(x, weight, bias, _s=stride, _p=padding, _a=approximate):
+            return flag_dnn.gelu(flag_dnn.bias_add(flag_dnn.conv2d(x, weight, stride=_s, padding=_p), bias),
+                                 approximate=_a)
+
+        compiled = flag_dnn.compile(act, inputs=[x, w, b], options={"cache": None})
+        y = compiled.run(x.clone(), w.clone(), b.clone())
+        key = f"gelu_{idx:02d}"
+        for name, t in (("x", x), ("w", w), ("b", b), ("y", y)):
+            records[f"{key}_{name}"] = t.numpy()
+        records[key + "_meta"] = np.array([stride, padding, int(approximate == "tanh")], dtype=np.int64)
+
+    for idx, (m, k, n) in enumerate(MM_CASES):
+        a = _seeded((m, k), 5000 + idx, dist="uniform")
+        bm = _seeded((k, n), 5100 + idx, dist="uniform")
+
+        @flag_dnn.graph
+        def matmul(a, b):
+            return flag_dnn.mm(a, b)
+
+        compiled = flag_dnn.compile(matmul, inputs=[a, bm], options={"cache": None})
+        y = compiled.run(a.clone(), bm.clone())
+        key = f"mm_{idx:02d}"
+        records[key + "_a"], records[key + "_b"], records[key + "_y"] = a.numpy(), bm.numpy(), y.numpy()
+
+    np.savez_compressed(OUT_DIR / "reference_cpu_outputs_next.npz", **records)
+    print("wrote", OUT_DIR / "reference_cpu_outputs_next.npz", len(records), "arrays")
 
 
 def _pair(v):

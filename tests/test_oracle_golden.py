@@ -33,6 +33,43 @@ def test_eager_cases_match_reference_outputs(golden, idx):
     torch.testing.assert_close(got_loops, ref, rtol=2e-5, atol=2e-5)
 
 
+N_TAIL, N_GELU, N_MM = 3, 2, 5   # cases in tests/golden/make_golden.py::_write_next_rows
+
+
+@pytest.mark.parametrize("idx", range(N_TAIL))
+def test_block_tail_cases_match_reference_outputs(golden_next, idx):
+    """relu(conv * scale + bias + shortcut): the oracle's sequence is the reference graph's (conv2d, mul, bias_add, add, relu)."""
+    key = f"tail_{idx:02d}"
+    x, w, s, b, r, ref = (torch.from_numpy(golden_next[f"{key}_{n}"]) for n in ("x", "w", "s", "b", "r", "y"))
+    stride, padding = (int(v) for v in golden_next[key + "_meta"])
+    got = torch.relu(oracle.conv2d_torch_cpu(x, w, b, stride, padding, 1, 1, scale=s.reshape(-1)) + r)
+    torch.testing.assert_close(got, ref, rtol=0, atol=0)
+    loops = torch.relu(oracle.conv2d_loops(x, w, b, stride, padding, 1, 1, scale=s.reshape(-1)) + r)
+    torch.testing.assert_close(loops, ref, rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("idx", range(N_GELU))
+def test_gelu_cases_match_reference_outputs(golden_next, idx):
+    key = f"gelu_{idx:02d}"
+    x, w, b, ref = (torch.from_numpy(golden_next[f"{key}_{n}"]) for n in ("x", "w", "b", "y"))
+    stride, padding, tanh = (int(v) for v in golden_next[key + "_meta"])
+    got = torch.nn.functional.gelu(oracle.conv2d_torch_cpu(x, w, b, stride, padding, 1, 1),
+                                   approximate="tanh" if tanh else "none")
+    torch.testing.assert_close(got, ref, rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("idx", range(N_MM))
+def test_mm_cases_match_reference_outputs(golden_next, idx):
+    """mm as the oracle sees it: a 1x1 convolution over a row of M pixels equals the reference's torch.mm."""
+    key = f"mm_{idx:02d}"
+    a, b, ref = (torch.from_numpy(golden_next[f"{key}_{n}"]) for n in ("a", "b", "y"))
+    torch.testing.assert_close(torch.mm(a, b), ref, rtol=0, atol=0)
+    x4 = a.t().unsqueeze(0).unsqueeze(2)                      # [1, K, 1, M]
+    w4 = b.t().unsqueeze(-1).unsqueeze(-1)                    # [N, K, 1, 1]
+    as_conv = oracle.conv2d_loops(x4.contiguous(), w4.contiguous(), None, 1, 0, 1, 1)[0, :, 0, :].t()
+    torch.testing.assert_close(as_conv, ref, rtol=2e-5, atol=2e-5)
+
+
 def test_loops_double_matches_torch_double():
     g = torch.Generator().manual_seed(7)
     x = torch.randn(2, 6, 11, 9, generator=g, dtype=torch.float64)

@@ -49,17 +49,39 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Tests whether the phase with the given parity has completed.  While it is still open the hardware may
+// park the thread for up to kParkNs nanoseconds (it is woken when the phase completes) instead of
+// returning at once: ten warps of a CTA re-polling their barriers every few dozen clocks cost enough
+// power to lower the clock of a tensor-bound kernel by 5-9 % on B200 (measured: 50.0 -> 45.8 us on the
+// 3x3 256-channel layer with 2 us; no gain with 20 us, where late wake-ups eat it up).
+#ifndef FDNN_PARKED_WAIT_NS
+#define FDNN_PARKED_WAIT_NS 2000
+#endif
+constexpr uint32_t kParkNs = FDNN_PARKED_WAIT_NS;
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred P;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
+  if constexpr (kParkNs > 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kParkNs)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred P;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  }
   return ok != 0;
 }
 

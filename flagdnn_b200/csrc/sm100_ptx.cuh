@@ -53,7 +53,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // park the thread for up to kParkNs nanoseconds (it is woken when the phase completes) instead of
 // returning at once: ten warps of a CTA re-polling their barriers every few dozen clocks cost enough
 // power to lower the clock of a tensor-bound kernel by 5-9 % on B200 (measured: 50.0 -> 45.8 us on the
-// 3x3 256-channel layer with 2 us; no gain with 20 us, where late wake-ups eat it up).
+// 3x3 256-channel layer; hints from 0.25 to 8 us measure the same).
 #ifndef FDNN_PARKED_WAIT_NS
 #define FDNN_PARKED_WAIT_NS 2000
 #endif

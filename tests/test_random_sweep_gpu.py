@@ -1,0 +1,82 @@
+"""Seeded random sweep over the operator surface: shapes, strides, paddings, dilations, groups, dtypes,
+layouts, epilogues.  Every case is checked against the CPU oracle on the same bits; the planner decides
+which kernel family runs (direct, single-CTA, CTA pairs, low-channel, pixel-grouped), so the sweep also
+walks the boundaries between them."""
+import random
+
+import pytest
+import torch
+
+import oracle
+from cases import TOL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def fd(native_lib):
+    import flagdnn_b200
+
+    assert torch.cuda.is_available()
+    yield flagdnn_b200
+    assert flagdnn_b200.device_status() == 0, "a kernel recorded a bounded-wait incident"
+
+
+def _case(rng: random.Random):
+    groups = rng.choice([1, 1, 1, 1, 2, 4])
+    c = groups * rng.choice([1, 2, 3, 4, 8, 16, 24, 40, 64, 96])
+    k = groups * rng.choice([1, 2, 4, 8, 16, 20, 32, 64, 72, 128])
+    r, s = rng.choice([(1, 1), (3, 3), (3, 3), (1, 3), (5, 5), (7, 7), (2, 2), (3, 1)])
+    stride = (rng.choice([1, 1, 2, 3]), rng.choice([1, 1, 2]))
+    dil = (rng.choice([1, 1, 1, 2]), rng.choice([1, 1, 2]))
+    pad = (rng.randint(0, r // 2 + 1), rng.randint(0, s // 2 + 1))
+    h = rng.randint(max(1, dil[0] * (r - 1) + 1 - 2 * pad[0]), 40)
+    w = rng.randint(max(1, dil[1] * (s - 1) + 1 - 2 * pad[1]), 40)
+    n = rng.choice([1, 2, 3, 5, 8, 33])
+    # a few large problems so that the tensor-core paths (and pixel grouping / CTA pairs) are reached
+    if rng.random() < 0.3:
+        n, h, w = rng.choice([16, 32, 48]), rng.choice([28, 32, 56]), rng.choice([28, 32, 56])
+    return n, c, h, w, k, r, s, stride, pad, dil, groups
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_random_case_matches_oracle(fd, seed):
+    rng = random.Random(1234 + seed)
+    n, c, h, w, k, r, s, stride, pad, dil, groups = _case(rng)
+    dtype_name = rng.choice(["bfloat16", "bfloat16", "float16", "float32", "float64"])
+    if dtype_name == "float64" and n * k * h * w * c * r * s // groups > 2e9:
+        dtype_name = "float32"
+    channels_last = rng.random() < 0.6
+    epilogue = rng.choice(["none", "bias", "bias_relu", "scale_bias_relu", "residual_relu", "gelu"])
+    dtype = getattr(torch, dtype_name)
+    g = torch.Generator().manual_seed(seed)
+
+    def make(shape, std=1.0):
+        t = (torch.randn(shape, generator=g) * std).to(dtype).cuda()
+        return t.contiguous(memory_format=torch.channels_last) if channels_last and t.dim() == 4 else t
+
+    x = make((n, c, h, w))
+    wt = make((k, c // groups, r, s), std=(c // groups * r * s) ** -0.5)
+    bias = None if epilogue == "none" else make((k,), std=0.2)
+    scale = (torch.rand(k, generator=g) + 0.5).to(dtype).cuda() if epilogue == "scale_bias_relu" else None
+    oh = (h + 2 * pad[0] - dil[0] * (r - 1) - 1) // stride[0] + 1
+    ow = (w + 2 * pad[1] - dil[1] * (s - 1) - 1) // stride[1] + 1
+    assert oh >= 1 and ow >= 1
+    residual = make((n, k, oh, ow)) if epilogue == "residual_relu" else None
+    activation = {"none": "none", "bias": "none", "bias_relu": "relu", "scale_bias_relu": "relu",
+                  "residual_relu": "relu", "gelu": "gelu"}[epilogue]
+
+    got = fd.conv2d_bias_act(x, wt, bias, stride=stride, padding=pad, dilation=dil, groups=groups, scale=scale,
+                             residual=residual, activation=activation)
+    cdt = torch.float64 if dtype_name == "float64" else torch.float32
+    ref = oracle.conv2d_torch_cpu(x, wt, bias, stride, pad, dil, groups, scale=scale, compute_dtype=cdt)
+    if residual is not None:
+        ref = ref + residual.cpu().to(cdt)
+    if activation == "relu":
+        ref = torch.relu(ref)
+    elif activation == "gelu":
+        ref = torch.nn.functional.gelu(ref)
+    assert got.shape == ref.shape and got.dtype == dtype
+    tol = TOL[dtype_name]
+    what = f"n{n} c{c} h{h} w{w} k{k} r{r}x{s} stride{stride} pad{pad} dil{dil} g{groups} {dtype_name} cl={channels_last} {epilogue}"
+    torch.testing.assert_close(got.cpu().to(cdt), ref, rtol=tol["rtol"], atol=tol["atol"], msg=lambda m: f"{what}: {m}")

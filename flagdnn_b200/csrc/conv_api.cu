@@ -270,11 +270,10 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     plan->grid = int(tiles_lc < sms_lc ? tiles_lc : sms_lc);
     plan->block = igemm_threads();
     plan->launches = 2;
-    // The CTA-pair kernel (resident filter halves) is kept for callers that ask for it; with eight epilogue
-    // warps the single-CTA kernel drains the stem's tiles as fast and measures 3-4 % quicker (230 vs 238 us).
+    // CTA pairs keep their half of the quad filter resident: 216 vs 225 us on the 7x7 stride-2 stem
     const long long pair_tiles_lc = (long long)((m_tiles_lc + 1) / 2) * ((n_gemm + 255) / 256);
-    (void)pair_tiles_lc;
-    if (algo == FDNN_ALGO_IGEMM_PAIR) {
+    if (algo == FDNN_ALGO_IGEMM_PAIR ||
+        (want_auto && sms_lc % 2 == 0 && n_gemm >= 256 && pair_tiles_lc >= sms_lc / 2)) {
       plan->algo = FDNN_ALGO_IGEMM_PAIR;
       plan->tile_m = 256;
       plan->tile_n = 256;

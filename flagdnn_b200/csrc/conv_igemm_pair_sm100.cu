@@ -353,7 +353,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN + chalf * kWarpCols;
       epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.act, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
-                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows);
+                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows, g_scale != nullptr);
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }

@@ -423,7 +423,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
         epilogue_store_tile<T, WC, RES>(t_row, n0, p.Kout, p.act, s_scale, s_bias,
                                    out_stage + (warp - kFirstEpiWarp) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
-                                   st_img, st_rows, store_seq, res_box, p.y_row, res_rows);
+                                   st_img, st_rows, store_seq, res_box, p.y_row, res_rows, g_scale != nullptr);
       } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < WC / 32; ++chunk) {

@@ -48,7 +48,7 @@ WORKLOADS = {
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the implicit-GEMM
 # kernel, from the ncu captures summarised under profiles/ (None = not captured).
-NCU_TRAFFIC_BYTES = {"c3": 26.96e6, "c2": 495.7e6, "c4": 459.6e6, "c1": None}
+NCU_TRAFFIC_BYTES = {"c3": 26.96e6, "c2": 495.5e6, "c4": 459.0e6, "c1": None}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 

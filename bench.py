@@ -50,6 +50,9 @@ WORKLOADS = {
 # kernel, from the ncu captures summarised under profiles/ (None = not captured).
 NCU_TRAFFIC_BYTES = {"c3": 26.96e6, "c2": 495.5e6, "c4": 459.0e6, "c1": None}
 
+# the arithmetic type as the JSON line names it (fp32 tensors run as 3xTF32 with fp32 accumulation)
+SHORT_DTYPE = {"bfloat16": "bf16", "float16": "f16", "float32": "f32"}
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -213,7 +216,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": SHORT_DTYPE[wl["dtype"]], "data": "synthetic",
         "config": {"workload": args.workload, "description": wl["desc"], "sample_images": sample_n},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
@@ -457,7 +460,7 @@ def _report(args, torch, rank, world, wl, nums, peaks, peak_src, ms_per_step, va
         line = {
             "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": warm_replays * n_sets, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
+            "vs_baseline": None, "dtype": SHORT_DTYPE[wl["dtype"]], "data": "synthetic",
             "config": {"workload": args.workload, "description": wl["desc"], "graph_nodes": node_types,
                        "launch": "eager_api_calls" if args.eager else "cuda_graph_replay", "l2": f"{n_sets} rotating (x, y) sets = "
                        f"{n_sets * per_set / 2**20:.0f} MiB > 126 MiB L2; filter and bias shared",
@@ -640,7 +643,7 @@ def run_stack(args):
         line = {
             "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bfloat16", "data": "synthetic",
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "c5", "description": "ResNet-50 forward conv stack, 53 convs with folded scale+bias(+ReLU), "
                        f"bf16 NHWC 224x224, batch {total_batch} sharded along N", "per_gpu_batch": batch,
                        "inputs": "each layer reads independently generated N(0,1) activations of its shape; "
@@ -681,7 +684,7 @@ def run_stack_reference(args):
     print(json.dumps({
         "impl": "reference", "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": max(1, min(args.steps, 3)), "warmup": 1, "ms_per_step": seconds * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bfloat16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "c5", "sample_images": 2},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
@@ -827,7 +830,7 @@ def run_extra(args):
     print(json.dumps({
         "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bfloat16", "data": "synthetic",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "description": wl["desc"], "launch": "cuda_graph_replay",
                    "l2": f"{n_sets} rotating operand sets = {n_sets * per_set / 2**20:.0f} MiB > 126 MiB L2"},
         "roofline": {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,

@@ -224,6 +224,8 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
     with torch.cuda.device(input.device):
         if out is None:
             out = _empty_output(input, n, c_out, oh, ow)
+        elif tuple(out.shape) != (n, c_out, oh, ow) or out.dtype != input.dtype or out.device != input.device:
+            raise RuntimeError(f"out must be a {input.dtype} tensor of shape {(n, c_out, oh, ow)} on {input.device}")
         if n == 0:
             return out
         if residual is not None:
@@ -275,15 +277,18 @@ def conv2d(
     padding: Union[str, int, Tuple[int, int]] = 0,
     dilation: Union[int, Tuple[int, int]] = 1,
     groups: int = 1,
+    *,
+    out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """Drop-in for ``flag_dnn.ops.conv2d`` (src/flag_dnn/ops/conv2d.py:3575)."""
+    """Drop-in for ``flag_dnn.ops.conv2d`` (src/flag_dnn/ops/conv2d.py:3575).  ``out`` (not in the
+    reference) receives the result: any strides, the output's shape and the input's dtype."""
     stride = _pair(stride)
     dilation = _pair(dilation)
     padding4 = _normalize_padding(weight, stride, padding, dilation)
     _check_conv2d_inputs(input, weight, bias, stride, padding4, dilation, groups)
     if not input.is_cuda:
         raise NotImplementedError("flag_dnn conv2d CUDA implementation requires CUDA input")
-    return _run(input, weight, bias, None, stride, padding4, dilation, groups, nat.ACT_NONE)
+    return _run(input, weight, bias, None, stride, padding4, dilation, groups, nat.ACT_NONE, out=out)
 
 
 def fused_conv2d_bias_relu(
@@ -298,6 +303,7 @@ def fused_conv2d_bias_relu(
     config: Optional[dict[str, Any]] = None,
     scale: Optional[torch.Tensor] = None,
     activation: str = "relu",
+    out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Drop-in for the reference's fused op (src/flag_dnn/graph/kernels/fused_conv.py:62-72).
 
@@ -334,7 +340,7 @@ def fused_conv2d_bias_relu(
         raise RuntimeError(f"bias shape mismatch, expected ({c_out},)")
     if scale is not None and scale.numel() != c_out:
         raise RuntimeError(f"scale shape mismatch, expected ({c_out},)")
-    return _run(input, weight, bias, scale, stride, padding4, dilation, 1, _ACTIVATIONS[activation])
+    return _run(input, weight, bias, scale, stride, padding4, dilation, 1, _ACTIVATIONS[activation], out=out)
 
 
 def conv2d_bias_act(
@@ -350,6 +356,7 @@ def conv2d_bias_act(
     relu: bool = False,
     residual: Optional[torch.Tensor] = None,
     activation: Optional[str] = None,
+    out: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """conv2d with the full epilogue (scale, bias, residual add, ReLU) and conv2d's
     argument range (any groups, fp64): ``act(conv(x, w) * scale + bias + residual)``
@@ -370,7 +377,8 @@ def conv2d_bias_act(
         activation = "relu" if relu else "none"
     if activation not in _ACTIVATIONS:
         raise NotImplementedError(f"unsupported activation {activation!r}")
-    return _run(input, weight, bias, scale, stride, padding4, dilation, groups, _ACTIVATIONS[activation], residual)
+    return _run(input, weight, bias, scale, stride, padding4, dilation, groups, _ACTIVATIONS[activation], residual,
+                out=out)
 
 
 def conv1d(

@@ -21,6 +21,7 @@ import torch
 
 from .ir import Graph
 from .passes import apply_fusion_pass, eliminate_dead_nodes
+from .memory import MemoryPlan, allocate_memory
 from .registry import get_op_schema
 from .spec import GraphTensor, TensorSpec, torch_dtype
 
@@ -151,15 +152,6 @@ class ExecutionStep:
 
 
 @dataclass
-class MemoryPlan:
-    workspace_size: int = 0
-    buffers: dict = field(default_factory=dict)
-
-    def to_dict(self) -> dict:
-        return {"workspace_size": self.workspace_size, "buffers": dict(self.buffers)}
-
-
-@dataclass
 class ExecutionPlan:
     graph_hash: str
     plan_id: str
@@ -215,15 +207,9 @@ def _build_plan(graph_obj: Graph, specs: list, output_structure: Any, options: d
         steps.append(ExecutionStep(node.op_type, list(node.inputs), list(node.outputs), attrs,
                                    backend=best["backend"], kernel_name=best["name"]))
         chosen.append(best)
-    # Intermediate values: their sizes are reported, storage comes from torch's
-    # caching allocator at run time (the reference computes a workspace it never
-    # consumes, src/flag_dnn/graph/registry.py:1431-1434).
-    buffers = {}
-    for node in graph_obj.nodes:
-        for vid in node.outputs:
-            if vid not in graph_obj.outputs:
-                buffers[str(vid)] = graph_obj.values[vid].spec.nbytes()
-    memory_plan = MemoryPlan(workspace_size=sum(buffers.values()), buffers=buffers)
+    # Intermediate values get a place in one workspace (first-fit reuse of dead blocks); with
+    # options={"workspace": True} the executor hands those places to the nodes as their outputs.
+    memory_plan = allocate_memory(graph_obj)
     ghash = graph_obj.graph_hash()
     autotune = bool(options.get("autotune", False)) or str(os.getenv("FLAGDNN_AUTOTUNE", "0")).lower() in ("1", "true", "yes")
     debug = {
@@ -280,7 +266,9 @@ def _cache_key(graph_obj: Graph, specs: list, backend: str) -> str:
 
 
 class CompiledGraph:
-    """A planned graph.  With ``options={"cuda_graph": True}`` the whole plan is captured into one
+    """A planned graph.  With ``options={"workspace": True}`` the intermediates live in one buffer laid out by
+    the memory plan (graph/memory.py) instead of coming from the allocator at every step.
+    With ``options={"cuda_graph": True}`` the whole plan is captured into one
     CUDA graph on its first run with CUDA tensors and replayed afterwards: inputs are copied into
     static buffers (skipped for tensors that already are those buffers, see ``static_inputs``) and
     the returned tensors are static too — consume them before the next ``run``.  Multi-step plans
@@ -288,17 +276,34 @@ class CompiledGraph:
     node; the reference executes such plans node by node from Python
     (src/flag_dnn/graph/executor.py:68-106)."""
 
-    def __init__(self, plan: ExecutionPlan, cuda_graph: bool = False):
+    def __init__(self, plan: ExecutionPlan, cuda_graph: bool = False, workspace: bool = False):
         self.plan = plan
         self.graph = plan.graph
         self._use_cuda_graph = bool(cuda_graph)
+        self._use_workspace = bool(workspace)
+        self._workspaces: dict = {}
         self._captured = None
         self.static_inputs: Optional[list] = None
         self._static_outputs: Any = None
 
+    def _workspace_for(self, inputs: tuple) -> Optional[torch.Tensor]:
+        """One buffer of plan.workspace_size bytes per device, allocated at the first run and reused: the
+        intermediates of consecutive runs then live at fixed addresses and nothing is allocated per step."""
+        if not self._use_workspace or self.plan.workspace_size <= 0:
+            return None
+        device = next((t.device for t in inputs if isinstance(t, torch.Tensor)), None)
+        if device is None or device.type != "cuda":
+            return None
+        if device not in self._workspaces:
+            self._workspaces[device] = torch.empty(self.plan.workspace_size, dtype=torch.uint8, device=device)
+        return self._workspaces[device]
+
+    def _execute(self, inputs: tuple) -> Any:
+        return execute_plan(self.plan, inputs, self._workspace_for(inputs))
+
     def run(self, *inputs: Any) -> Any:
         if not self._use_cuda_graph or not any(isinstance(t, torch.Tensor) and t.is_cuda for t in inputs):
-            return self.plan.run(*inputs)
+            return self._execute(inputs)
         if len(inputs) != len(self.plan.input_specs):
             raise RuntimeError(f"graph expects {len(self.plan.input_specs)} inputs, got {len(inputs)}")
         for index, (spec, tensor) in enumerate(zip(self.plan.input_specs, inputs)):
@@ -306,11 +311,11 @@ class CompiledGraph:
         if self._captured is None:
             self.static_inputs = [torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=t.device).copy_(t)
                                   for t in inputs]
-            self.plan.run(*self.static_inputs)        # warm-up: packs filters, sets kernel attributes
+            self._execute(tuple(self.static_inputs))  # warm-up: packs filters, sets kernel attributes
             torch.cuda.synchronize()
             captured = torch.cuda.CUDAGraph()
             with torch.cuda.graph(captured):
-                self._static_outputs = self.plan.run(*self.static_inputs)
+                self._static_outputs = self._execute(tuple(self.static_inputs))
             self._captured = captured
         for static, given in zip(self.static_inputs, inputs):
             if static.data_ptr() != given.data_ptr():
@@ -387,7 +392,8 @@ def compile(fn: Callable, inputs: Optional[list] = None, input_specs: Optional[l
         plan.debug_info["cache_hit"] = True
         plan.debug_info["cache_layer"] = "memory"
         plan.debug_info["output_structure"] = structure
-    return CompiledGraph(plan, cuda_graph=bool(opts.get("cuda_graph", False)))
+    return CompiledGraph(plan, cuda_graph=bool(opts.get("cuda_graph", False)),
+                         workspace=bool(opts.get("workspace", False)))
 
 
 # ----------------------------------------------------------------- execution
@@ -406,7 +412,29 @@ def _validate_input(spec: TensorSpec, tensor: Any, index: int) -> None:
         raise RuntimeError(f"graph input {index} ({spec.name}) device {tensor.device} != compiled {spec.device}")
 
 
-def execute_plan(plan: ExecutionPlan, inputs: tuple) -> Any:
+def _workspace_view(workspace: torch.Tensor, alloc, spec: TensorSpec, like: Any) -> Optional[torch.Tensor]:
+    """The planned slice of the workspace as a tensor of the value's shape and dtype; channels-last strides
+    when the node's first operand is channels-last (the rule the kernels use for their own outputs)."""
+    dtype = torch_dtype(spec.dtype)
+    shape = tuple(int(v) for v in spec.shape)
+    numel = 1
+    for v in shape:
+        numel *= v
+    nbytes = numel * torch.empty((), dtype=dtype).element_size()
+    if numel == 0 or alloc.offset + nbytes > workspace.numel():
+        return None
+    flat = workspace[alloc.offset: alloc.offset + nbytes].view(dtype)
+    channels_last = (len(shape) == 4 and shape[1] > 1 and isinstance(like, torch.Tensor) and like.dim() == 4
+                     and like.stride(1) == 1 and dtype != torch.float64)
+    if channels_last:
+        n, c, h, w = shape
+        return flat.as_strided(shape, (h * w * c, 1, w * c, c))
+    return flat.view(shape)
+
+
+def execute_plan(plan: ExecutionPlan, inputs: tuple, workspace: Optional[torch.Tensor] = None) -> Any:
+    """Runs the plan's steps.  With ``workspace`` (a uint8 tensor of at least plan.workspace_size bytes on the
+    inputs' device) every intermediate value the memory plan placed is written straight into its slice."""
     graph_obj = plan.graph
     if len(inputs) != len(graph_obj.inputs):
         raise RuntimeError(f"graph expects {len(graph_obj.inputs)} inputs, got {len(inputs)}")
@@ -422,8 +450,16 @@ def execute_plan(plan: ExecutionPlan, inputs: tuple) -> Any:
     for value in graph_obj.values.values():
         if value.is_constant:
             env[value.id] = value.const_value
+    allocations = plan.memory_plan.allocations if (workspace is not None and plan.memory_plan is not None) else {}
     for step in plan.steps:
-        result = get_op_schema(step.op_type).run([env[v] for v in step.inputs], step.attrs)
-        env[step.outputs[0]] = result
+        args = [env[v] for v in step.inputs]
+        attrs = step.attrs
+        alloc = allocations.get(step.outputs[0])
+        if alloc is not None:
+            view = _workspace_view(workspace, alloc, graph_obj.values[step.outputs[0]].spec, args[0] if args else None)
+            if view is not None:
+                attrs = dict(attrs)
+                attrs["_out"] = view
+        env[step.outputs[0]] = get_op_schema(step.op_type).run(args, attrs)
     flat = [env[v] for v in graph_obj.outputs]
     return _rebuild_outputs(plan.debug_info.get("output_structure") or ("leaf",), flat)

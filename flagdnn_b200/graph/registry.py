@@ -127,12 +127,13 @@ def _run_conv2d(inputs: list, attrs: dict) -> torch.Tensor:
     a = _public(attrs)
     bias = inputs[2] if len(inputs) > 2 else None
     scale = inputs[3].reshape(-1) if len(inputs) > 3 else None
+    out = attrs.get("_out")   # the executor's workspace slice for this node's output, if it planned one
     if scale is None:
         return native.conv2d(inputs[0], inputs[1], bias, a.get("stride", 1), a.get("padding", 0),
-                             a.get("dilation", 1), a.get("groups", 1))
+                             a.get("dilation", 1), a.get("groups", 1), out=out)
     return native.fused_conv2d_bias_relu(inputs[0], inputs[1], bias, stride=a.get("stride", 1),
                                          padding=a.get("padding", 0), dilation=a.get("dilation", 1),
-                                         groups=a.get("groups", 1), scale=scale, activation="none")
+                                         groups=a.get("groups", 1), scale=scale, activation="none", out=out)
 
 
 def _run_fused_conv2d_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
@@ -144,12 +145,13 @@ def _run_fused_conv2d_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
     kw = dict(stride=a.get("stride", 1), padding=a.get("padding", 0), dilation=a.get("dilation", 1))
     try:
         return native.fused_conv2d_bias_relu(inputs[0], inputs[1], inputs[2], groups=a.get("groups", 1),
-                                             config=attrs.get("_kernel_config"), scale=scale, **kw)
+                                             config=attrs.get("_kernel_config"), scale=scale, out=attrs.get("_out"),
+                                             **kw)
     except NotImplementedError:
         # Outside the fused entry's contract (grouped convolution, fp64): the
         # same native library still fuses bias and ReLU through its direct kernel.
         return native.conv2d_bias_act(inputs[0], inputs[1], inputs[2], groups=a.get("groups", 1),
-                                      scale=scale, relu=True, **kw)
+                                      scale=scale, relu=True, out=attrs.get("_out"), **kw)
 
 
 def _gelu_code(attrs: dict) -> str:
@@ -165,7 +167,8 @@ def _run_fused_conv2d_bias_gelu(inputs: list, attrs: dict) -> torch.Tensor:
     scale = inputs[3].reshape(-1) if len(inputs) > 3 else None
     return native.conv2d_bias_act(inputs[0], inputs[1], inputs[2], stride=a.get("stride", 1),
                                   padding=a.get("padding", 0), dilation=a.get("dilation", 1),
-                                  groups=a.get("groups", 1), scale=scale, activation=_gelu_code(attrs))
+                                  groups=a.get("groups", 1), scale=scale, activation=_gelu_code(attrs),
+                                  out=attrs.get("_out"))
 
 
 def _run_fused_conv2d_bias_add_relu(inputs: list, attrs: dict) -> torch.Tensor:
@@ -178,7 +181,8 @@ def _run_fused_conv2d_bias_add_relu(inputs: list, attrs: dict) -> torch.Tensor:
     scale = inputs[4].reshape(-1) if len(inputs) > 4 else None
     return native.conv2d_bias_act(inputs[0], inputs[1], bias, stride=a.get("stride", 1), padding=a.get("padding", 0),
                                   dilation=a.get("dilation", 1), groups=a.get("groups", 1), scale=scale,
-                                  relu=a.get("activation", "relu") == "relu", residual=inputs[2])
+                                  relu=a.get("activation", "relu") == "relu", residual=inputs[2],
+                                  out=attrs.get("_out"))
 
 
 def _normalize_conv2d_residual(ctx: Any, args: tuple, kwargs: dict) -> tuple:
@@ -313,17 +317,32 @@ def _format_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     return bias
 
 
+def _usable_out(attrs: dict, *operands) -> Optional[torch.Tensor]:
+    """The planned output slice, if every tensor operand has its dtype (no type promotion in play)."""
+    out = attrs.get("_out")
+    if out is None or any(isinstance(t, torch.Tensor) and t.dtype != out.dtype for t in operands):
+        return None
+    return out
+
+
 def _run_bias_add(inputs: list, attrs: dict) -> torch.Tensor:
     x, bias = inputs
+    out = _usable_out(attrs, x, bias)
+    if out is not None and tuple(out.shape) == tuple(x.shape):
+        return torch.add(x, _format_bias(x, bias), out=out)
     return x + _format_bias(x, bias)
 
 
 def _run_relu(inputs: list, attrs: dict) -> torch.Tensor:
+    out = _usable_out(attrs, inputs[0])
+    if out is not None and tuple(out.shape) == tuple(inputs[0].shape):
+        return torch.clamp_min(inputs[0], 0, out=out)   # NaN stays NaN, like torch.relu
     return torch.relu(inputs[0])
 
 
 def _run_fused_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
-    return torch.relu(_run_bias_add(inputs, attrs))
+    return torch.relu_(_run_bias_add(inputs, attrs)) if attrs.get("_out") is not None else \
+        torch.relu(_run_bias_add(inputs, attrs))
 
 
 def _run_gelu(inputs: list, attrs: dict) -> torch.Tensor:
@@ -339,6 +358,10 @@ def _binary_runner(fn):
         other = inputs[1] if len(inputs) > 1 else attrs["other"]
         if attrs.get("reverse") and len(inputs) == 1:
             return fn(torch.as_tensor(other, dtype=inputs[0].dtype, device=inputs[0].device), inputs[0])
+        out = _usable_out(attrs, inputs[0], other)
+        if out is not None and isinstance(other, torch.Tensor) and \
+                tuple(out.shape) == tuple(torch.broadcast_shapes(inputs[0].shape, other.shape)):
+            return fn(inputs[0], other, out=out)
         return fn(inputs[0], other)
     return run
 

@@ -91,6 +91,15 @@ def test_bottleneck_block_graph_replays_as_one_cuda_graph(native_lib):
     for _ in range(3):
         got = graphed.run(*args)
     assert torch.equal(got, expect)
+    # the same plan with its intermediates in the planned workspace, alone and inside the CUDA graph
+    for opts in ({"workspace": True}, {"workspace": True, "cuda_graph": True}):
+        planned = fd.compile(block, inputs=args, options={"cache": None, **opts})
+        assert planned.plan.workspace_size > 0 and len(planned.plan.memory_plan.blocks) == 2
+        for _ in range(2):
+            out = planned.run(*args)
+        assert torch.equal(out, expect)
+        ws = planned._workspaces[x.device]
+        assert ws.numel() == planned.plan.workspace_size
     x2 = (x * 0.5).contiguous(memory_format=torch.channels_last)
     assert torch.equal(graphed.run(x2, *args[1:]), plain.run(x2, *args[1:]))
 

@@ -263,6 +263,35 @@ def test_pooling_ops_capture_and_refuse_cpu_eagerly():
         flag_dnn.adaptive_avg_pool2d(x, 1)
 
 
+def test_memory_plan_places_intermediates_and_reuses_dead_blocks():
+    """Lifetimes and first-fit reuse as the reference plans them (src/flag_dnn/graph/memory.py:125-199)."""
+    specs = [flag_dnn.TensorSpec("x", (2, 8, 16, 16), "float32"), flag_dnn.TensorSpec("w", (8, 8, 3, 3), "float32"),
+             flag_dnn.TensorSpec("b", (8,), "float32")]
+
+    @flag_dnn.graph
+    def chain(x, w, b):
+        a = flag_dnn.conv2d(x, w, padding=1)          # value A: dies after the second convolution
+        c = flag_dnn.conv2d(a, w, padding=1)          # value C
+        d = flag_dnn.conv2d(c, w, padding=1)          # value D: can take A's block
+        return flag_dnn.relu(flag_dnn.bias_add(flag_dnn.conv2d(d, w, padding=1), b))
+
+    compiled = flag_dnn.compile(chain, inputs=specs, options={"cache": None})
+    plan = compiled.plan.memory_plan
+    nbytes = 2 * 8 * 16 * 16 * 4
+    assert len(plan.lifetimes) == 3 and all(t.size_bytes == nbytes for t in plan.lifetimes)
+    births = sorted((t.birth, t.last_use) for t in plan.lifetimes)
+    assert births == [(0, 1), (1, 2), (2, 3)]
+    assert len(plan.blocks) == 2 and plan.workspace_size == 2 * nbytes        # two live at a time, the third reuses
+    offsets = [plan.allocations[t.value_id].offset for t in sorted(plan.lifetimes, key=lambda t: t.birth)]
+    assert offsets[0] == offsets[2] != offsets[1] and all(o % 256 == 0 for o in offsets)
+    d = compiled.plan.debug_info["memory"]
+    assert set(d) >= {"workspace_size", "lifetimes", "reusable_value_ids", "blocks", "allocations"}
+    assert compiled.plan.workspace_size == plan.workspace_size
+    # graph outputs and inputs are never placed
+    planned = set(plan.allocations)
+    assert not planned & set(compiled.graph.inputs) and not planned & set(compiled.graph.outputs)
+
+
 def test_graph_memory_plan_cache_hit():
     cache = flag_dnn.PlanCache(enable_disk=False)
 

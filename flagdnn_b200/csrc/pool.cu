@@ -42,21 +42,24 @@ __device__ __forceinline__ T down(typename Acc<T>::type v) {
   else return static_cast<T>(v);
 }
 
-// linear index -> (n, c, oh, ow) in y's memory order
-__device__ __forceinline__ void unravel(long long i, const PoolParams& p, bool c_fastest, int& n, int& c, int& oh,
+// linear index -> (n, c, oh, ow) in y's memory order.  I is unsigned 32-bit whenever the output has fewer
+// than 2^31 elements: four 64-bit divisions per element are what such a kernel would otherwise spend
+// its time on.
+template <typename I>
+__device__ __forceinline__ void unravel(I i, const PoolParams& p, bool c_fastest, int& n, int& c, int& oh,
                                         int& ow) {
   if (c_fastest) {
-    c = int(i % p.C); i /= p.C;
-    ow = int(i % p.OW); i /= p.OW;
-    oh = int(i % p.OH); n = int(i / p.OH);
+    c = int(i % I(p.C)); i /= I(p.C);
+    ow = int(i % I(p.OW)); i /= I(p.OW);
+    oh = int(i % I(p.OH)); n = int(i / I(p.OH));
   } else {
-    ow = int(i % p.OW); i /= p.OW;
-    oh = int(i % p.OH); i /= p.OH;
-    c = int(i % p.C); n = int(i / p.C);
+    ow = int(i % I(p.OW)); i /= I(p.OW);
+    oh = int(i % I(p.OH)); i /= I(p.OH);
+    c = int(i % I(p.C)); n = int(i / I(p.C));
   }
 }
 
-template <typename T>
+template <typename T, typename I>
 __global__ void max_pool2d_kernel(const PoolParams p) {
   using A = typename Acc<T>::type;
   const T* x = static_cast<const T*>(p.x);
@@ -66,7 +69,7 @@ __global__ void max_pool2d_kernel(const PoolParams p) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     int n, c, oh, ow;
-    unravel(i, p, c_fastest, n, c, oh, ow);
+    unravel<I>(I(i), p, c_fastest, n, c, oh, ow);
     const T* xc = x + n * p.x_s[0] + c * p.x_s[1];
     A best = -INFINITY;
     long long best_at = -1;
@@ -92,17 +95,17 @@ __global__ void max_pool2d_kernel(const PoolParams p) {
 }
 
 // Dense channels-last 16-bit tensors, C % 8 == 0, no indices: 8 channels per thread.
-template <typename T>
+template <typename T, typename I>
 __global__ void max_pool2d_nhwc8_kernel(const PoolParams p) {
   const int c8 = p.C / 8;
   const long long total = (long long)p.N * p.OH * p.OW * c8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    long long t = i;
-    const int cv = int(t % c8); t /= c8;
-    const int ow = int(t % p.OW); t /= p.OW;
-    const int oh = int(t % p.OH);
-    const int n = int(t / p.OH);
+    I t = I(i);
+    const int cv = int(t % I(c8)); t /= I(c8);
+    const int ow = int(t % I(p.OW)); t /= I(p.OW);
+    const int oh = int(t % I(p.OH));
+    const int n = int(t / I(p.OH));
     const T* xc = static_cast<const T*>(p.x) + n * p.x_s[0] + cv * 8;
     float best[8];
 #pragma unroll
@@ -135,7 +138,7 @@ __global__ void max_pool2d_nhwc8_kernel(const PoolParams p) {
 __device__ __forceinline__ int win_start(int o, int in, int out) { return int(((long long)o * in) / out); }
 __device__ __forceinline__ int win_end(int o, int in, int out) { return int(((long long)(o + 1) * in + out - 1) / out); }
 
-template <typename T>
+template <typename T, typename I>
 __global__ void adaptive_avg_pool2d_kernel(const PoolParams p) {
   using A = typename Acc<T>::type;
   const T* x = static_cast<const T*>(p.x);
@@ -145,7 +148,7 @@ __global__ void adaptive_avg_pool2d_kernel(const PoolParams p) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     int n, c, oh, ow;
-    unravel(i, p, c_fastest, n, c, oh, ow);
+    unravel<I>(I(i), p, c_fastest, n, c, oh, ow);
     const int h0 = win_start(oh, p.H, p.OH), h1 = win_end(oh, p.H, p.OH);
     const int w0 = win_start(ow, p.W, p.OW), w1 = win_end(ow, p.W, p.OW);
     const T* xc = x + n * p.x_s[0] + c * p.x_s[1];
@@ -156,17 +159,17 @@ __global__ void adaptive_avg_pool2d_kernel(const PoolParams p) {
   }
 }
 
-template <typename T>
+template <typename T, typename I>
 __global__ void adaptive_avg_pool2d_nhwc8_kernel(const PoolParams p) {
   const int c8 = p.C / 8;
   const long long total = (long long)p.N * p.OH * p.OW * c8;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    long long t = i;
-    const int cv = int(t % c8); t /= c8;
-    const int ow = int(t % p.OW); t /= p.OW;
-    const int oh = int(t % p.OH);
-    const int n = int(t / p.OH);
+    I t = I(i);
+    const int cv = int(t % I(c8)); t /= I(c8);
+    const int ow = int(t % I(p.OW)); t /= I(p.OW);
+    const int oh = int(t % I(p.OH));
+    const int n = int(t / I(p.OH));
     const int h0 = win_start(oh, p.H, p.OH), h1 = win_end(oh, p.H, p.OH);
     const int w0 = win_start(ow, p.W, p.OW), w1 = win_end(ow, p.W, p.OW);
     const T* xc = static_cast<const T*>(p.x) + n * p.x_s[0] + cv * 8;
@@ -200,28 +203,35 @@ bool nhwc8_ok(const PoolParams& p, int es) {
 
 int grid_for(long long work) {
   long long blocks = (work + 255) / 256;
-  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (blocks > 148LL * 256) blocks = 148LL * 256;
   return int(blocks < 1 ? 1 : blocks);
 }
 
 }  // namespace
 
+#define FDNN_POOL_GO(KERNEL, T)                                            \
+  do {                                                                    \
+    if (small) KERNEL<T, uint32_t><<<g, 256, 0, stream>>>(p);             \
+    else KERNEL<T, unsigned long long><<<g, 256, 0, stream>>>(p);         \
+  } while (0)
+
 cudaError_t launch_max_pool2d(int dtype, const PoolParams& p, cudaStream_t stream) {
   const long long total = (long long)p.N * p.C * p.OH * p.OW;
   if (total == 0) return cudaSuccess;
+  const bool small = total < (1ll << 31);
   const int es = dtype == FDNN_F64 ? 8 : (dtype == FDNN_F32 ? 4 : 2);
   if (nhwc8_ok(p, es)) {
     const int g = grid_for(total / 8);
-    if (dtype == FDNN_F16) max_pool2d_nhwc8_kernel<__half><<<g, 256, 0, stream>>>(p);
-    else max_pool2d_nhwc8_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p);
+    if (dtype == FDNN_F16) FDNN_POOL_GO(max_pool2d_nhwc8_kernel, __half);
+    else FDNN_POOL_GO(max_pool2d_nhwc8_kernel, __nv_bfloat16);
     return cudaGetLastError();
   }
   const int g = grid_for(total);
   switch (dtype) {
-    case FDNN_F16: max_pool2d_kernel<__half><<<g, 256, 0, stream>>>(p); break;
-    case FDNN_BF16: max_pool2d_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p); break;
-    case FDNN_F32: max_pool2d_kernel<float><<<g, 256, 0, stream>>>(p); break;
-    case FDNN_F64: max_pool2d_kernel<double><<<g, 256, 0, stream>>>(p); break;
+    case FDNN_F16: FDNN_POOL_GO(max_pool2d_kernel, __half); break;
+    case FDNN_BF16: FDNN_POOL_GO(max_pool2d_kernel, __nv_bfloat16); break;
+    case FDNN_F32: FDNN_POOL_GO(max_pool2d_kernel, float); break;
+    case FDNN_F64: FDNN_POOL_GO(max_pool2d_kernel, double); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
@@ -230,22 +240,24 @@ cudaError_t launch_max_pool2d(int dtype, const PoolParams& p, cudaStream_t strea
 cudaError_t launch_adaptive_avg_pool2d(int dtype, const PoolParams& p, cudaStream_t stream) {
   const long long total = (long long)p.N * p.C * p.OH * p.OW;
   if (total == 0) return cudaSuccess;
+  const bool small = total < (1ll << 31);
   const int es = dtype == FDNN_F64 ? 8 : (dtype == FDNN_F32 ? 4 : 2);
   if (nhwc8_ok(p, es)) {
     const int g = grid_for(total / 8);
-    if (dtype == FDNN_F16) adaptive_avg_pool2d_nhwc8_kernel<__half><<<g, 256, 0, stream>>>(p);
-    else adaptive_avg_pool2d_nhwc8_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p);
+    if (dtype == FDNN_F16) FDNN_POOL_GO(adaptive_avg_pool2d_nhwc8_kernel, __half);
+    else FDNN_POOL_GO(adaptive_avg_pool2d_nhwc8_kernel, __nv_bfloat16);
     return cudaGetLastError();
   }
   const int g = grid_for(total);
   switch (dtype) {
-    case FDNN_F16: adaptive_avg_pool2d_kernel<__half><<<g, 256, 0, stream>>>(p); break;
-    case FDNN_BF16: adaptive_avg_pool2d_kernel<__nv_bfloat16><<<g, 256, 0, stream>>>(p); break;
-    case FDNN_F32: adaptive_avg_pool2d_kernel<float><<<g, 256, 0, stream>>>(p); break;
-    case FDNN_F64: adaptive_avg_pool2d_kernel<double><<<g, 256, 0, stream>>>(p); break;
+    case FDNN_F16: FDNN_POOL_GO(adaptive_avg_pool2d_kernel, __half); break;
+    case FDNN_BF16: FDNN_POOL_GO(adaptive_avg_pool2d_kernel, __nv_bfloat16); break;
+    case FDNN_F32: FDNN_POOL_GO(adaptive_avg_pool2d_kernel, float); break;
+    case FDNN_F64: FDNN_POOL_GO(adaptive_avg_pool2d_kernel, double); break;
     default: return cudaErrorInvalidValue;
   }
   return cudaGetLastError();
 }
+#undef FDNN_POOL_GO
 
 }  // namespace fdnn

@@ -56,13 +56,18 @@ def _single_use_producer(graph: Graph, value_id: int, op_type: str):
 
 
 def _channel_scale_input(graph: Graph, mul_node: OpNode, conv_out_channels: int):
-    """The non-conv operand of `conv * scale` if it is a per-channel vector."""
+    """The non-conv operand of `conv * scale` if it is a per-channel vector.
+
+    The captured ``mul`` broadcasts like ``torch.mul``: against a [N, K, H, W] convolution output only
+    shapes (K, 1, 1) and (1, K, 1, 1) multiply along the channels.  A plain (K,) vector broadcasts along
+    W, so it is a per-channel scale only in the degenerate case K == 1 (a one-element vector).
+    """
     if len(mul_node.inputs) != 2:
         return None
     scale_id = mul_node.inputs[1]
     shape = tuple(graph.values[scale_id].spec.shape)
     k = conv_out_channels
-    if shape in ((k,), (k, 1, 1), (1, k, 1, 1)):
+    if shape in ((k, 1, 1), (1, k, 1, 1)) or (k == 1 and shape == (1,)):
         return scale_id
     return None
 

@@ -141,7 +141,7 @@ def _run_fused_conv2d_bias_relu(inputs: list, attrs: dict) -> torch.Tensor:
 
     _require_device(inputs, "fused_conv2d_bias_relu")
     a = _public(attrs)
-    scale = inputs[3].reshape(-1) if len(inputs) > 3 else None  # (K,), (K,1,1) or (1,K,1,1)
+    scale = inputs[3].reshape(-1) if len(inputs) > 3 else None  # captured as (K,1,1) or (1,K,1,1)
     kw = dict(stride=a.get("stride", 1), padding=a.get("padding", 0), dilation=a.get("dilation", 1))
     try:
         return native.fused_conv2d_bias_relu(inputs[0], inputs[1], inputs[2], groups=a.get("groups", 1),

@@ -177,6 +177,21 @@ def test_graph_scale_pattern_folds_with_and_without_relu():
     compiled = flag_dnn.compile(spatial_scale, inputs=specs, options={"cache": None})
     assert [n.op_type for n in compiled.graph.nodes] == ["conv2d", "mul", "fused_bias_relu"]
 
+    # a plain (K,) vector multiplies along W (torch broadcasting), which is only expressible when W == K:
+    # it is not a per-channel scale and must stay a separate node
+    specs_wk = [flag_dnn.TensorSpec("x", (1, 8, 4, 16), "bfloat16"), flag_dnn.TensorSpec("w", (16, 8, 1, 1), "bfloat16"),
+                flag_dnn.TensorSpec("s", (16,), "bfloat16"), flag_dnn.TensorSpec("b", (16,), "bfloat16")]
+    for fn in (no_relu, spatial_scale):
+        compiled = flag_dnn.compile(fn, inputs=specs_wk, options={"cache": None})
+        kinds = [n.op_type for n in compiled.graph.nodes]
+        assert "mul" in kinds and all(len(n.inputs) <= 3 for n in compiled.graph.nodes if n.op_type == "conv2d")
+        assert "conv2d_scale_bias_folded" not in compiled.plan.debug_info["fusion"]
+    # ... except for a single output channel, where the one-element vector is the channel's scale
+    specs_k1 = [flag_dnn.TensorSpec("x", (1, 8, 4, 4), "bfloat16"), flag_dnn.TensorSpec("w", (1, 8, 1, 1), "bfloat16"),
+                flag_dnn.TensorSpec("s", (1,), "bfloat16"), flag_dnn.TensorSpec("b", (1,), "bfloat16")]
+    compiled = flag_dnn.compile(no_relu, inputs=specs_k1, options={"cache": None})
+    assert [n.op_type for n in compiled.graph.nodes] == ["conv2d"] and len(compiled.graph.nodes[0].inputs) == 4
+
 
 def test_graph_residual_tail_becomes_one_node():
     specs = [flag_dnn.TensorSpec("x", (2, 8, 8, 8), "bfloat16"), flag_dnn.TensorSpec("w", (8, 8, 1, 1), "bfloat16"),

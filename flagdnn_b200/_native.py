@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "fdnn_conv2d_host_arena_bytes",
     "fdnn_device_status",
     "fdnn_debug_set_profile_buffer",
+    "fdnn_debug_set_wait_limit",
     "fdnn_conv2d_fwd_static_scratch",
     "fdnn_static_scratch_bytes",
     "fdnn_static_scratch_last_error",
@@ -118,7 +119,7 @@ def load() -> ctypes.CDLL:
     lib.fdnn_conv2d_query.restype = i32
     lib.fdnn_conv2d_query.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, ctypes.POINTER(ConvPlan)]
     lib.fdnn_conv2d_pack_weight.restype = i32
-    lib.fdnn_conv2d_pack_weight.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, i64, vp]
+    lib.fdnn_conv2d_pack_weight.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, i64, vp]
     lib.fdnn_conv2d_fwd.restype = i32
     lib.fdnn_conv2d_fwd.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.fdnn_max_pool2d_fwd.restype = i32
@@ -137,6 +138,8 @@ def load() -> ctypes.CDLL:
     lib.fdnn_static_scratch_last_error.restype = ctypes.c_char_p
     lib.fdnn_debug_set_profile_buffer.restype = i32
     lib.fdnn_debug_set_profile_buffer.argtypes = [vp]
+    lib.fdnn_debug_set_wait_limit.restype = i32
+    lib.fdnn_debug_set_wait_limit.argtypes = [i64, i32]
     lib.fdnn_device_status.restype = i32
     lib.fdnn_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     _lib = lib

@@ -148,7 +148,7 @@ def _plan_for(input, weight, out, stride, padding4, dilation, groups, algo):
     return d, plan
 
 
-def _packed_weight(weight: torch.Tensor, d: nat.ConvDesc, plan: nat.ConvPlan, stream: int) -> torch.Tensor:
+def _packed_weight(weight: torch.Tensor, d: nat.ConvDesc, plan: nat.ConvPlan, stream: int, y_ptr: int) -> torch.Tensor:
     version = int(getattr(weight, "_version", 0))
     # the packed layout depends on the plan: generic [K,R,S,Cpad] or the low-channel quad layout
     if plan.pixel_group > 1:
@@ -167,7 +167,8 @@ def _packed_weight(weight: torch.Tensor, d: nat.ConvDesc, plan: nat.ConvPlan, st
             return value
         del _PACKED_WEIGHT_CACHE[key]
     packed = torch.empty(plan.packed_weight_bytes, dtype=torch.uint8, device=weight.device)
-    nat.check(nat.load().fdnn_conv2d_pack_weight(ctypes.byref(d), weight.data_ptr(), packed.data_ptr(),
+    # y_ptr: only its alignment matters (it selects the plan, and with it the packed layout, as in _plan_for)
+    nat.check(nat.load().fdnn_conv2d_pack_weight(ctypes.byref(d), weight.data_ptr(), y_ptr, packed.data_ptr(),
                                                  plan.packed_weight_bytes, stream))
     _PACKED_WEIGHT_CACHE[key] = (weakref.ref(weight), packed)
     while len(_PACKED_WEIGHT_CACHE) > _PACKED_WEIGHT_CACHE_MAX:
@@ -237,7 +238,7 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         packed_ptr = None
         packed = None
         if plan.algo != nat.ALGO_DIRECT and plan.w_packed:
-            packed = _packed_weight(weight, d, plan, stream)
+            packed = _packed_weight(weight, d, plan, stream, out.data_ptr())
             packed_ptr = packed.data_ptr()
         ws_ptr = None
         ws = None

@@ -145,7 +145,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #endif
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
+    if (lane == 0 && !p.skip_copies) {
       uint32_t stage = 0, phase = 0;
       bool alive = true;
       long long prof_wait = 0, prof_issue = 0, prof_iters = 0, prof_t0 = p.prof ? clock64() : 0;
@@ -195,7 +195,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             for (int cb = 0; cb < p.c_blocks; ++cb) {
               const long long pt0 = p.prof ? clock64() : 0;
               if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
-                                     kIncidentProducerWait)) {
+                                     kIncidentProducerWait, p.wait_limit)) {
                 alive = false;
                 break;
               }
@@ -239,7 +239,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       bool alive = true;
       long long prof_wfull = 0, prof_wtmem = 0, prof_t0 = p.prof ? clock64() : 0;
       if (b_resident && pair_id < total_tiles) {
-        alive = mbar_wait_bounded(bres_bar, 0u, abort_flag, p.status, kIncidentMmaWaitFull);
+        alive = mbar_wait_bounded(bres_bar, 0u, abort_flag, p.status, kIncidentMmaWaitFull, p.wait_limit);
       }
       const uint32_t empty_own = smem_u32(&empty_bar[0]);
       const uint32_t empty_peer = map_to_cta(empty_own, 1);
@@ -250,7 +250,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t bphase = (tcount >> 1) & 1u;
         const long long mt0 = p.prof ? clock64() : 0;
         if (!mbar_wait_bounded(&tmem_empty[buf], bphase ^ 1u, abort_flag, p.status,
-                               kIncidentMmaWaitTmem)) {
+                               kIncidentMmaWaitTmem, p.wait_limit)) {
           alive = false;
           break;
         }
@@ -259,7 +259,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t d_tmem = tmem_base + buf * kPairN;
         for (int kit = 0; kit < k_iters; ++kit) {
           const long long mt1 = p.prof ? clock64() : 0;
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull)) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull, p.wait_limit)) {
             alive = false;
             break;
           }
@@ -336,7 +336,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const int res_rows = p.M - m_first < 32 ? int(p.M - m_first) : 32;
       const T* res_box = (g_res != nullptr && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
       const long long et0 = p.prof ? clock64() : 0;
-      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
+      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (p.prof) prof_ewait += clock64() - et0;
       if (!ok) break;

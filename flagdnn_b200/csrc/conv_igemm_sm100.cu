@@ -223,7 +223,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             const uint32_t phase = (it / kStages) & 1u;
             const long long pt0 = p.prof ? clock64() : 0;
             if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
-                                   kIncidentProducerWait)) {
+                                   kIncidentProducerWait, p.wait_limit)) {
               alive = false;
               break;
             }
@@ -279,10 +279,10 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #endif
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) produce(true, kProducers == 1, true);
+    if (lane == 0 && !p.skip_copies) produce(true, kProducers == 1, true);
   } else if (kProducers == 2 && warp == kFilterProducerWarp) {
     // ---------------------------------------------- producer of the filter copies
-    if (lane == 0) produce(false, true, false);
+    if (lane == 0 && !p.skip_copies) produce(false, true, false);
   } else if (warp == 1) {
     // -------------------------------------------------------------- issuer
     if (lane == 0) {
@@ -295,7 +295,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t bphase = (tcount >> 1) & 1u;
         const long long mt0 = p.prof ? clock64() : 0;
         if (!mbar_wait_bounded(&tmem_empty[buf], bphase ^ 1u, abort_flag, p.status,
-                               kIncidentMmaWaitTmem)) {
+                               kIncidentMmaWaitTmem, p.wait_limit)) {
           alive = false;
           break;
         }
@@ -307,7 +307,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           const uint32_t phase = (it / kStages) & 1u;
           const long long mt1 = p.prof ? clock64() : 0;
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status,
-                                 kIncidentMmaWaitFull)) {
+                                 kIncidentMmaWaitFull, p.wait_limit)) {
             alive = false;
             break;
           }
@@ -399,7 +399,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const int res_rows = p.M - m_first < 32 ? p.M - m_first : 32;
       const T* res_box = (g_res != nullptr && p.tma_store && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
       const long long et0 = p.prof ? clock64() : 0;
-      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait);
+      bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (p.prof) prof_ewait += clock64() - et0;
       if (!ok) break;

@@ -43,12 +43,17 @@ struct IgemmParams {
   int k_real;            // length of bias / scale (GEMM column j uses entry j % k_real)
   uint32_t* status;
   long long* prof;       // optional: 16 cycle counters written by CTA 0 (nullptr = off)
+  long long wait_limit;  // SM clocks after which a wait on a barrier gives up (see fdnn_debug_set_wait_limit)
+  int skip_copies;       // test aid: the copy-issuing role does nothing, so the first wait for data runs out
 };
 
 // Whether the tensor-core kernels are launched with programmatic stream serialization (their set-up
 // overlaps the tail of the launch before them on the stream).  On unless the environment variable
 // FLAGDNN_B200_LAUNCH_OVERLAP is "0" when the library makes its first launch.
 bool launch_overlap_enabled();
+
+// Default for IgemmParams::wait_limit: about two seconds of SM clocks.
+long long default_wait_limit_cycles();
 
 // Launchers (defined in conv_igemm_sm100.cu).  `dtype` is FDNN_F16/BF16/F32.
 // tmA2 / tmB2 are the low-half operands of the split-TF32 path (ignored for

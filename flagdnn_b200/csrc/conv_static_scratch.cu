@@ -23,11 +23,16 @@ namespace {
 static __device__ __align__(256) unsigned char g_static_scratch[FDNN_STATIC_SCRATCH_BYTES];
 
 constexpr int kMaxDevices = 64;
-std::once_flag g_once[kMaxDevices];
-void* g_scratch_ptr[kMaxDevices];
-cudaError_t g_scratch_err[kMaxDevices];
+std::mutex g_lookup_mutex;
+void* g_scratch_ptr[kMaxDevices];  // set once the lookup on that device has succeeded
 
-thread_local char g_msg[256];
+thread_local char g_msg[512];
+
+int pass_through(int status) {
+  // keep the promise of fdnn_static_scratch_last_error for failures of the calls this one is built on
+  if (status != FDNN_OK) snprintf(g_msg, sizeof g_msg, "%s", fdnn_last_error());
+  return status;
+}
 
 }  // namespace
 
@@ -44,7 +49,7 @@ int fdnn_conv2d_fwd_static_scratch(const fdnn_conv_desc* desc, const void* x, co
   fdnn_conv_plan plan;
   // Plan exactly as fdnn_conv2d_fwd will (a packed filter, when given, is used).
   int st = fdnn_conv2d_query(desc, x, w_packed != nullptr ? reinterpret_cast<const void*>(1) : w, y, &plan);
-  if (st != FDNN_OK) return st;
+  if (st != FDNN_OK) return pass_through(st);
   if (plan.workspace_bytes > FDNN_STATIC_SCRATCH_BYTES) {
     snprintf(g_msg, sizeof g_msg,
              "this problem needs %lld bytes of scratch; the built-in scratch holds %lld "
@@ -60,21 +65,28 @@ int fdnn_conv2d_fwd_static_scratch(const fdnn_conv_desc* desc, const void* x, co
     return FDNN_CUDA_ERROR;
   }
   // Set-up, once per device, with that device current: translate the symbol
-  // into the address the kernels can use.
-  std::call_once(g_once[dev], [dev]() {
-    void* p = nullptr;
-    g_scratch_err[dev] = cudaGetSymbolAddress(&p, g_static_scratch);
-    g_scratch_ptr[dev] = (g_scratch_err[dev] == cudaSuccess) ? p : nullptr;
-  });
-  if (g_scratch_err[dev] != cudaSuccess || g_scratch_ptr[dev] == nullptr) {
-    cudaGetLastError();
-    snprintf(g_msg, sizeof g_msg, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(g_scratch_err[dev]));
-    return FDNN_CUDA_ERROR;
+  // into the address the kernels can use.  Only a successful lookup is kept: a
+  // first call that fails (made during a stream capture, say) is retried by the
+  // next call instead of failing that device for good.
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_lookup_mutex);
+    if (g_scratch_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        cudaGetLastError();
+        snprintf(g_msg, sizeof g_msg, "cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        return FDNN_CUDA_ERROR;
+      }
+      g_scratch_ptr[dev] = p;
+    }
+    scratch = g_scratch_ptr[dev];
   }
   // The relayout kernels overwrite every byte of the region they use (channel
   // padding included), so nothing in the array has to be cleared between calls.
-  return fdnn_conv2d_fwd(desc, x, w, w_packed, bias, scale, activation, y, g_scratch_ptr[dev],
-                         FDNN_STATIC_SCRATCH_BYTES, stream);
+  return pass_through(fdnn_conv2d_fwd(desc, x, w, w_packed, bias, scale, activation, y, scratch,
+                                      FDNN_STATIC_SCRATCH_BYTES, stream));
 }
 
 }  // extern "C"

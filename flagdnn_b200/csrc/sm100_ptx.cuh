@@ -100,7 +100,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0xff) == 0) {
+    if ((++spins & 0xf) == 0) {  // a parked poll lasts up to kParkNs, so this is still rare
       if (*abort_flag) return false;
       if (clock64() - t0 > limit_cycles) {
         atomicCAS(status_word, 0u, incident);

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define FDNN_ABI_VERSION 1
+#define FDNN_ABI_VERSION 2
 
 /* Status codes.  The Python shim maps BAD_PARAM / CUDA_ERROR / DEVICE_TIMEOUT /
  * WORKSPACE_TOO_SMALL to RuntimeError and NOT_SUPPORTED / ARCH_MISMATCH to
@@ -113,10 +113,16 @@ int fdnn_conv2d_query(const fdnn_conv_desc* desc, const void* x, const void* w,
 
 /* One-time filter relayout, the counterpart of the reference's packers
  * (src/flag_dnn/ops/conv2d.py:193-276): w[K,C/g,R,S] (any strides) ->
- * [K,R,S,Cpad] with zero padding; for f32 a second copy holds the low TF32
- * halves.  `packed` must hold plan.packed_weight_bytes.  Asynchronous on
- * `stream` (a cudaStream_t passed as void*). */
-int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w,
+ * [K,R,S,Cpad] with zero padding (for f32 a second copy holds the low TF32
+ * halves), or the low-channel / pixel-grouped layout when the plan for `desc`
+ * says plan.low_channel / plan.pixel_group.  `y` is the output pointer the
+ * forward call will write (NULL: a 16-byte aligned one); only its alignment is
+ * read, because it takes part in choosing the plan and with it the layout.
+ * `packed` must hold plan.packed_weight_bytes.  Asynchronous on `stream` (a
+ * cudaStream_t passed as void*).  The library remembers, per `packed` address,
+ * which layout it wrote; fdnn_conv2d_fwd answers FDNN_BAD_PARAM when handed a
+ * buffer whose remembered layout is not the one its own plan reads. */
+int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, const void* y,
                             void* packed, int64_t packed_bytes, void* stream);
 
 /* y = act( conv(x, w) * scale[k] + bias[k] ), fp32 accumulate, one rounding to
@@ -227,6 +233,14 @@ const char* fdnn_static_scratch_last_error(void);
  * issuer: [4] data-wait, [5] accumulator-wait, [6] total, [7] tiles;
  * epilogue: [8] accumulator-wait, [9] total).  NULL switches it off (default). */
 int fdnn_debug_set_profile_buffer(void* device_buffer_16_int64);
+
+/* Test aid for the bounded waits: launches made after this call give up a wait
+ * after `wait_limit_cycles` SM clocks (0 restores the default of about two
+ * seconds); with `skip_copies` non-zero the kernels' copy-issuing role does
+ * nothing, so that the first wait for data runs out.  The kernel then records
+ * its incident code, returns normally and fdnn_device_status reports
+ * FDNN_DEVICE_TIMEOUT once.  Process-wide; not for production use. */
+int fdnn_debug_set_wait_limit(int64_t wait_limit_cycles, int skip_copies);
 
 #ifdef __cplusplus
 }

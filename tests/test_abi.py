@@ -43,7 +43,7 @@ def test_library_exports_every_declared_symbol(native_lib):
     assert declared == sorted(nat.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(native_lib, name), f"{name} is declared in the header but not exported"
-    assert native_lib.fdnn_abi_version() == 1
+    assert native_lib.fdnn_abi_version() == 2
     assert native_lib.fdnn_status_string(0) == b"ok"
     assert b"unknown" in native_lib.fdnn_status_string(12345)
 

@@ -101,7 +101,7 @@ def make_inputs(wl, n, seed, device, torch):
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while a region runs."""
+    """Samples SM clock and throttle reasons through NVML while a region runs (every 2 ms, plus on request)."""
 
     def __init__(self, index):
         self.samples, self.reasons, self.max_mhz = [], set(), None
@@ -115,27 +115,34 @@ class ClockSampler:
             self._nvml = pynvml
             self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self._bits = {
+                "hw_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                "sw_power_cap": getattr(pynvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+                "hw_thermal_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                "hw_power_brake": getattr(pynvml, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
+            }
         except Exception:
             self._nvml = None
 
-    def _loop(self):
+    def sample(self):
+        """One reading now; a region shorter than the sampling period calls this right after its launches are
+        queued (the GPU is then under that load) and once more before it synchronises."""
         nv = self._nvml
-        names = {
-            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
-            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
-            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
-            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
-            "hw_power_brake": getattr(nv, "nvmlClocksThrottleReasonHwPowerBrakeSlowdown", 0x80),
-        }
+        if nv is None:
+            return
+        try:
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+            mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+            for name, bit in self._bits.items():
+                if mask & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _loop(self):
         while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
-                for name, bit in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
+            self.sample()
             time.sleep(0.002)
 
     def __enter__(self):
@@ -165,30 +172,61 @@ def use_all_host_threads(torch):
     return torch.get_num_threads()
 
 
-def cpu_baseline_leg(wl, torch, sample_n, min_seconds=10.0):
-    """The reference's CPU path timed on the host cores; test-infrastructure code (oracle/) as the checker's timer."""
-    import oracle
+def time_cpu_calls(fn, warmup, steps=None, min_seconds=None, min_warm_seconds=3.0, max_warm_seconds=20.0):
+    """Wall-clock times of repeated calls of `fn` on the host.  The warm-up makes at least `warmup` calls, lasts at
+    least `min_warm_seconds` and goes on until two consecutive calls agree within 5 %: a bf16 convolution on the
+    host cores keeps getting faster for about a second of back-to-back calls (2.3x on this pool's hosts: thread
+    pool, matrix-unit clocks, page placement), and only the steady state is a fair baseline.  Then exactly `steps`
+    calls are timed, or as many as fit `min_seconds`."""
+    prev, calls, t_warm = None, 0, time.perf_counter()
+    while True:
+        t0 = time.perf_counter()
+        fn()
+        now = time.perf_counter()
+        dt = now - t0
+        calls += 1
+        steady = prev is not None and abs(dt - prev) <= 0.05 * max(dt, prev)
+        if calls >= max(warmup, 2) and ((now - t_warm >= min_warm_seconds and steady) or now - t_warm >= max_warm_seconds):
+            break
+        prev = dt
+    times, t_all = [], time.perf_counter()
+    while True:
+        if steps is not None and len(times) >= steps:
+            break
+        if steps is None and len(times) >= 3 and (time.perf_counter() - t_all >= min_seconds or len(times) >= 5000):
+            break
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+    return times
 
-    use_all_host_threads(torch)
+
+def _cpu_layer_call(wl, torch, sample_n):
+    """The reference's CPU path for one workload on `sample_n` images: the oracle's torch call, used here as the
+    timed CPU baseline (test-infrastructure code as the checker's timer, never on the product path)."""
+    import oracle
 
     x, w, b = make_inputs(wl, sample_n, 0, "cpu", torch)
     relu = wl["dtype"] != "float32"
     cdt = getattr(torch, wl["dtype"])  # the reference runs F.conv2d in the tensors' own dtype
-    oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
-    times, t_all = [], time.perf_counter()
-    while len(times) < 3 or (time.perf_counter() - t_all < min_seconds and len(times) < 5000):
-        t0 = time.perf_counter()
-        oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
-        times.append(time.perf_counter() - t0)
+    return lambda: oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
+
+
+def cpu_baseline_leg(wl, torch, sample_n, min_seconds=10.0):
+    """The reference's CPU path timed on the host cores for about `min_seconds`; median of the steady-state calls."""
+    use_all_host_threads(torch)
+    times = time_cpu_calls(_cpu_layer_call(wl, torch, sample_n), warmup=3, min_seconds=min_seconds)
     med = statistics.median(times)
     nums = workload_numbers(dict(wl, n=sample_n))
     return dict(value=nums["flops"] / med / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
                 sample=f"{sample_n} of {wl['n']} images, {len(times)} repeats, median; torch.nn.functional.conv2d+relu "
                        f"in {wl['dtype']} on CPU (the call the reference's CPU graph path makes)",
-                ms_per_sample=med * 1e3)
+                ms_per_sample=med * 1e3, ms_per_sample_mean=statistics.fmean(times) * 1e3)
 
 
 def run_reference(args):
+    """The reference arm: the reference's CPU path on the host cores (rank 0 only), exactly --steps timed calls of a
+    bounded sample after a warm-up that runs until the call time is steady; the line's value is the median."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -198,24 +236,17 @@ def run_reference(args):
     wl = WORKLOADS[args.workload]
     sample_n = min(wl["n"], 32)
     nums = workload_numbers(dict(wl, n=sample_n))
-    import oracle
-
-    x, w, b = make_inputs(wl, sample_n, 0, "cpu", torch)
-    relu = wl["dtype"] != "float32"
-    cdt = getattr(torch, wl["dtype"])
-    for _ in range(max(args.warmup, 1)):
-        oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
-    steps = max(1, min(args.steps, 50))
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        oracle.conv2d_torch_cpu(x, w, b, wl["stride"], wl["pad"], 1, 1, relu=relu, compute_dtype=cdt)
-    dt = (time.perf_counter() - t0) / steps
-    value = nums["flops"] / dt / 1e12
+    steps = max(1, args.steps)
+    times = time_cpu_calls(_cpu_layer_call(wl, torch, sample_n), warmup=max(args.warmup, 3), steps=steps)
+    med, mean = statistics.median(times), statistics.fmean(times)
+    value = nums["flops"] / med / 1e12
     sample = (f"each step = {sample_n} of {wl['n']} images through torch.nn.functional.conv2d+relu in {wl['dtype']} "
-              f"on the host CPU (the reference's CPU graph path); {steps} steps timed")
+              f"on the host CPU (the reference's CPU graph path); {steps} steps timed after a warm-up of at least 3 s of "
+              f"back-to-back calls that ended when two consecutive calls agreed within 5 %; value from the median step")
     line = {
         "impl": "reference", "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": med * 1e3,
+        "ms_per_step_mean": mean * 1e3, "value_from_mean": nums["flops"] / mean / 1e12,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": SHORT_DTYPE[wl["dtype"]], "data": "synthetic",
         "config": {"workload": args.workload, "description": wl["desc"], "sample_images": sample_n},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
@@ -226,24 +257,50 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def run_ours(args):
-    import torch
-
-    import flagdnn_b200 as fd
-
+def init_ranks(torch, cpu_leg=None):
+    """Device selection and, under torchrun, the NCCL process group.  `cpu_leg` (rank 0 only) runs BEFORE the
+    group is created: the other ranks then sit in the rendezvous, a blocking socket wait, instead of spinning in
+    an NCCL barrier on the host cores the CPU baseline is being timed on."""
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for this library)")
     torch.cuda.set_device(local_rank)
+    cpu = cpu_leg() if (cpu_leg is not None and rank == 0) else None
     dist = None
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    device = torch.device("cuda", local_rank)
+    return rank, world, local_rank, dist, cpu
+
+
+def max_over_ranks(torch, dist, device, values):
+    if dist is None:
+        return list(values)
+    t = torch.tensor(list(values), device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def count_true_over_ranks(torch, dist, device, flag):
+    if dist is None:
+        return int(bool(flag))
+    t = torch.tensor([1.0 if flag else 0.0], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return int(round(float(t.item())))
+
+
+def run_ours(args):
+    import torch
+
+    import flagdnn_b200 as fd
+
     wl = WORKLOADS[args.workload]
+    rank, world, local_rank, dist, cpu = init_ranks(
+        torch, None if args.kernel_only else (lambda: cpu_baseline_leg(wl, torch, sample_n=min(wl["n"], 32))))
+    device = torch.device("cuda", local_rank)
     nums = workload_numbers(wl)
     peaks, peak_src = load_peaks()
     relu = wl["dtype"] != "float32"
@@ -251,7 +308,7 @@ def run_ours(args):
     # ---- operands: enough rotating (x, y) sets that a set is evicted from L2 before it is reused
     l2_bytes = 126 * 1024 * 1024
     per_set = nums["x_bytes"] + nums["y_bytes"]
-    n_sets = max(2, min(16, -(-3 * l2_bytes // per_set)))
+    n_sets = max(2, min(64, -(-3 * l2_bytes // per_set)))
     xs = []
     w = b = None
     for i in range(n_sets):
@@ -271,36 +328,55 @@ def run_ours(args):
     plan = fd.conv2d_plan(xs[0], w, stride=wl["stride"], padding=wl["pad"])
     launches_per_step = plan["launches"]
 
-    # warm-up through the eager API (also packs the filter and sets kernel attributes)
-    for i in range(max(args.warmup, 3)):
+    # first calls through the eager API (pack the filter, set kernel attributes); not the counted warm-up
+    for i in range(3):
         compiled.run(xs[i % n_sets], w, b)
     torch.cuda.synchronize()
 
-    # ---- device-resident leg: one CUDA graph holding one step per operand set
+    # ---- device-resident leg.  Step i runs on operand set i % n_sets.  One CUDA graph holds a whole cycle of
+    # n_sets steps; a second, shorter graph holds the steps % n_sets steps that remain, so that exactly --steps
+    # (and exactly --warmup) steps run while consecutive launches stay inside a graph.
     stream = torch.cuda.Stream()
     outs = []
 
-    class _EagerCycle:
+    class _EagerSteps:
+        def __init__(self, count):
+            self.count = count
+
         def replay(self):
-            for i in range(n_sets):
+            for i in range(self.count):
                 compiled.run(xs[i], w, b)
 
+    def capture(count, keep=None):
+        if count == 0:
+            return None
+        if args.eager:
+            return _EagerSteps(count)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(count):
+                y = compiled.run(xs[i], w, b)
+                if keep is not None:
+                    keep.append(y)
+        return g
+
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
     with torch.cuda.stream(stream):
         for i in range(n_sets):
             out = compiled.run(xs[i], w, b)
             if args.eager:
                 outs.append(out)
         stream.synchronize()
-        if args.eager:
-            graph = _EagerCycle()
-        else:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(n_sets):
-                    outs.append(compiled.run(xs[i], w, b))
-    replays = max(1, -(-args.steps // n_sets))
-    steps = replays * n_sets
-    warm_replays = max(1, -(-max(args.warmup, 3) // n_sets))
+        cycle = capture(n_sets, outs)
+        tails = {}
+        for r in {steps % n_sets, warmup % n_sets}:
+            tails[r] = capture(r)
+
+    def run_steps(count):
+        for _ in range(count // n_sets):
+            cycle.replay()
+        if count % n_sets:
+            tails[count % n_sets].replay()
 
     def barrier():
         if dist is not None:
@@ -309,24 +385,39 @@ def run_ours(args):
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
-        for _ in range(warm_replays):
-            graph.replay()
+        run_steps(warmup)
         stream.synchronize()
         barrier()
         with ClockSampler(local_rank) as clocks:
             e0.record(stream)
-            for _ in range(replays):
-                graph.replay()
+            run_steps(steps)
             e1.record(stream)
+            clocks.sample()   # the launches are queued: the GPU is executing them now
             stream.synchronize()
+            clocks.sample()
         barrier()
-    elapsed_ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
+    elapsed_ms = max_over_ranks(torch, dist, device, [e0.elapsed_time(e1)])[0]
     ms_per_step = elapsed_ms / steps
     value = world * nums["flops"] / (ms_per_step * 1e-3) / 1e12
+
+    # ---- a region of at least 100 ms of the same steps when the requested one was shorter than 50 ms: the clock
+    # sampler then sees the GPU under sustained load (power cap); reported beside `value`, never instead of it
+    sustained = None
+    if elapsed_ms < 50.0 and not args.eager:
+        long_steps = int(-(-120.0 // ms_per_step))
+        long_steps = -(-long_steps // n_sets) * n_sets
+        with torch.cuda.stream(stream):
+            barrier()
+            with ClockSampler(local_rank) as long_clocks:
+                e0.record(stream)
+                run_steps(long_steps)
+                e1.record(stream)
+                stream.synchronize()
+            barrier()
+        long_ms = max_over_ranks(torch, dist, device, [e0.elapsed_time(e1)])[0]
+        sustained = {"steps": long_steps, "ms_per_step": long_ms / long_steps,
+                     "value": world * nums["flops"] / (long_ms / long_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                     "clocks": long_clocks.summary()}
 
     # ---- the same steps with two streams: independent batches overlap, so the SMs that idle through the last
     # partial wave of tiles of one launch start the next launch's tiles (reported beside `value`, not as it:
@@ -335,6 +426,7 @@ def run_ours(args):
     if not args.eager and n_sets >= 2:
         side = torch.cuda.Stream()
         graph2 = torch.cuda.CUDAGraph()
+        replays = max(1, steps // n_sets)
         with torch.cuda.stream(stream):
             with torch.cuda.graph(graph2, stream=stream):
                 side.wait_stream(stream)
@@ -342,8 +434,7 @@ def run_ours(args):
                     with torch.cuda.stream(side if i % 2 else stream):
                         compiled.run(xs[i], w, b)
                 stream.wait_stream(side)
-            for _ in range(warm_replays):
-                graph2.replay()
+            graph2.replay()
             stream.synchronize()
             barrier()
             e0.record(stream)
@@ -352,27 +443,55 @@ def run_ours(args):
             e1.record(stream)
             stream.synchronize()
             barrier()
-        c_ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([c_ms], device=device, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            c_ms = float(t.item())
-        concurrent = {"streams": 2, "ms_per_step": c_ms / steps,
-                      "value": world * nums["flops"] / (c_ms / steps * 1e-3) / 1e12, "unit": "TFLOP/s"}
+        c_ms = max_over_ranks(torch, dist, device, [e0.elapsed_time(e1)])[0]
+        c_steps = replays * n_sets
+        concurrent = {"streams": 2, "steps": c_steps, "ms_per_step": c_ms / c_steps,
+                      "value": world * nums["flops"] / (c_ms / c_steps * 1e-3) / 1e12, "unit": "TFLOP/s"}
 
-    e2e_value = e2e_ms = None
-    e2e_steps = 0
+    # ---- every step through the eager API (no CUDA graph): what a caller without graphs pays per call
+    eager = None
+    if not args.eager and not args.kernel_only:
+        e_steps = max(n_sets, min(200, steps))
+        for i in range(n_sets):
+            compiled.run(xs[i], w, b)
+        torch.cuda.synchronize()
+        barrier()
+        e0.record()
+        for i in range(e_steps):
+            compiled.run(xs[i % n_sets], w, b)
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        eg_ms = max_over_ranks(torch, dist, device, [e0.elapsed_time(e1)])[0]
+        eager = {"steps": e_steps, "ms_per_step": eg_ms / e_steps}
+
+    # ---- parity of what was timed: image 0 of this rank's first operand set against the CPU oracle (outside
+    # every timed region; the oracle is the checker here)
+    import oracle
+
+    ref = oracle.conv2d_torch_cpu(xs[0][:1], w, b, wl["stride"], wl["pad"], 1, 1, relu=relu)
+    tol = 1e-4 if wl["dtype"] == "float32" else 1e-2
+    parity_ok = bool(torch.allclose(outs[0][:1].float().cpu(), ref.float(), rtol=tol, atol=tol))
+    parity_ranks = count_true_over_ranks(torch, dist, device, parity_ok)
+
+    e2e = None
     if not args.kernel_only:
-        e2e_value, e2e_ms, e2e_steps = _e2e_leg(args, torch, dist, device, compiled, xs, outs, w, b, nums, world, barrier)
+        e2e = _e2e_leg(args, torch, dist, device, compiled, xs, outs, w, b, nums, world, barrier, wl)
+    stack = None
+    if args.workload == "c3" and not args.kernel_only and not args.eager and not args.no_stack:
+        del xs, outs, cycle, tails
+        torch.cuda.empty_cache()
+        stack = _stack_record(args, torch, fd, dist, device, rank, world, local_rank, peaks)
     status_word = fd.device_status()
-    _report(args, torch, rank, world, wl, nums, peaks, peak_src, ms_per_step, value, steps, warm_replays, n_sets,
-            per_set, node_types, plan, launches_per_step, clocks, status_word, e2e_value, e2e_ms, e2e_steps, concurrent)
+    if rank == 0:
+        _report(args, world, wl, nums, peaks, peak_src, ms_per_step, value, steps, warmup, n_sets, per_set, node_types,
+                plan, launches_per_step, clocks, status_word, e2e, concurrent, sustained, eager, cpu, parity_ranks, stack)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def _e2e_leg(args, torch, dist, device, compiled, xs, outs, w, b, nums, world, barrier):
+def _e2e_leg(args, torch, dist, device, compiled, xs, outs, w, b, nums, world, barrier, wl):
     """Pinned host buffers -> device -> fused op -> host, copies inside the timed region."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     # Every step copies its own input from pinned host memory and its own result back; the three
@@ -426,55 +545,96 @@ def _e2e_leg(args, torch, dist, device, compiled, xs, outs, w, b, nums, world, b
         return e0.elapsed_time(e1)
 
     # both orders of the same work are legitimate callers; keep the faster one
-    e2e_ms_candidates = [timed(e2e_step), timed(e2e_step_serial)]
-    if dist is not None:
-        t = torch.tensor(e2e_ms_candidates, device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms_candidates = [float(v) for v in t.tolist()]
-    e2e_ms = min(e2e_ms_candidates)
-    e2e_value = world * nums["flops"] / (e2e_ms / e2e_steps * 1e-3) / 1e12
-    return e2e_value, e2e_ms, e2e_steps
+    candidates = max_over_ranks(torch, dist, device, [timed(e2e_step), timed(e2e_step_serial)])
+    e2e_ms = min(candidates)
+    result = {"value": world * nums["flops"] / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+              "h2d_bytes_per_step": nums["x_bytes"], "d2h_bytes_per_step": nums["y_bytes"], "steps": e2e_steps,
+              "ms_per_step": e2e_ms / e2e_steps,
+              "schedule": "copies overlapped with the neighbouring steps" if candidates[0] <= candidates[1] else "serial"}
+    # the C ABI's own host-buffer entry point, fdnn_conv2d_fwd_host: serial and synchronising by contract
+    # (copy in, pack when the plan asks for it, run, copy out, wait), from the same pinned buffers
+    try:
+        result["c_abi_host_ms"] = _c_abi_host_call_ms(torch, xs[0], x_host, w, b, y_host[0], wl)
+    except Exception as exc:  # reported, never hidden: the Python-API figure above stands on its own
+        result["c_abi_host_ms"] = None
+        result["c_abi_host_error"] = str(exc)[:200]
+    return result
 
 
-def _report(args, torch, rank, world, wl, nums, peaks, peak_src, ms_per_step, value, steps, warm_replays, n_sets,
-            per_set, node_types, plan, launches_per_step, clocks, status_word, e2e_value, e2e_ms, e2e_steps,
-            concurrent=None):
-    if rank == 0:
-        # ---- roofline of the dominant kernel (the implicit-GEMM kernel; one launch per step)
-        if wl["bound"] == "tensor":
-            achieved = nums["flops"] / (ms_per_step * 1e-3) / 1e12
-            peak, unit = peaks["bf16_tflops"], "TFLOP/s"
-            extra = {"frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"]}
-        else:
-            achieved = nums["bytes"] / (ms_per_step * 1e-3) / 1e9
-            peak, unit = peaks["hbm_gbs"], "GB/s"
-            extra = {}
-        roofline = {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
-                    "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peak_src}",
-                    "kernel": "conv_igemm_pair_kernel" if plan["algo"] == 3 else "conv_igemm_kernel", "algorithmic_flops_per_launch": nums["flops"],
-                    "algorithmic_bytes_per_launch": nums["bytes"], **extra}
-        cpu = None if args.kernel_only else cpu_baseline_leg(wl, torch, sample_n=min(wl["n"], 32))
-        e2e = None if e2e_value is None else {
-            "value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": nums["x_bytes"],
-            "d2h_bytes_per_step": nums["y_bytes"], "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps}
-        line = {
-            "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
-            "warmup": warm_replays * n_sets, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": SHORT_DTYPE[wl["dtype"]], "data": "synthetic",
-            "config": {"workload": args.workload, "description": wl["desc"], "graph_nodes": node_types,
-                       "launch": "eager_api_calls" if args.eager else "cuda_graph_replay", "l2": f"{n_sets} rotating (x, y) sets = "
-                       f"{n_sets * per_set / 2**20:.0f} MiB > 126 MiB L2; filter and bias shared",
-                       "per_gpu_batch": wl["n"], "parallelism": f"batch-sharded replicas x{world}, no collective",
-                       "tile": [plan["tile_m"], plan["tile_n"], plan["tile_k"]], "stages": plan["stages"],
-                       "grid": plan["grid"]},
-            "pct_of_bf16_peak": 100.0 * (value / world) / peaks["bf16_tflops"],
-            "roofline": roofline, "cpu_baseline": cpu,
-            "e2e": e2e,
-            "two_stream_throughput": concurrent,
-            "gpu_launches": steps * launches_per_step * world,
-            "clocks": clocks.summary(), "device_status_word": status_word,
-        }
-        print(json.dumps(line))
+def _c_abi_host_call_ms(torch, x_dev, x_host, w, b, y_host, wl, repeats=5):
+    import ctypes
+
+    from flagdnn_b200 import _native as nat
+
+    lib = nat.load()
+    d = nat.ConvDesc()
+    d.dtype = {"bfloat16": nat.BF16, "float16": nat.F16, "float32": nat.F32}[wl["dtype"]]
+    d.n, d.c, d.h, d.w = x_dev.shape
+    d.k, _, d.r, d.s = w.shape
+    d.stride_h = d.stride_w = wl["stride"]
+    d.pad_top = d.pad_bottom = d.pad_left = d.pad_right = wl["pad"]
+    d.dil_h = d.dil_w = 1
+    d.groups = 1
+    d.algo = nat.ALGO_AUTO
+    w_host, b_host = w.cpu().pin_memory(), b.cpu().pin_memory()
+    for i in range(4):
+        d.x_strides[i], d.w_strides[i], d.y_strides[i] = x_host.stride(i), w_host.stride(i), y_host.stride(i)
+    need = ctypes.c_int64(0)
+    nat.check(lib.fdnn_conv2d_host_arena_bytes(ctypes.byref(d), ctypes.byref(need)))
+    arena = torch.empty(need.value, dtype=torch.uint8, device=x_dev.device)
+    stream = torch.cuda.current_stream().cuda_stream
+    act = nat.ACT_RELU if wl["dtype"] != "float32" else nat.ACT_NONE
+    times = []
+    for _ in range(repeats + 1):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        nat.check(lib.fdnn_conv2d_fwd_host(ctypes.byref(d), x_host.data_ptr(), w_host.data_ptr(), b_host.data_ptr(), None,
+                                           act, y_host.data_ptr(), arena.data_ptr(), need.value, stream))
+        times.append((time.perf_counter() - t0) * 1e3)
+    return statistics.median(times[1:])
+
+
+def _report(args, world, wl, nums, peaks, peak_src, ms_per_step, value, steps, warmup, n_sets, per_set, node_types,
+            plan, launches_per_step, clocks, status_word, e2e, concurrent, sustained, eager, cpu, parity_ranks, stack):
+    # ---- roofline of the dominant kernel (the implicit-GEMM kernel; one launch per step)
+    if wl["bound"] == "tensor":
+        achieved = nums["flops"] / (ms_per_step * 1e-3) / 1e12
+        peak, unit = peaks["bf16_tflops"], "TFLOP/s"
+        extra = {"frac_of_sustained_peak": achieved / peaks["bf16_tflops_sustained"]}
+    else:
+        achieved = nums["bytes"] / (ms_per_step * 1e-3) / 1e9
+        peak, unit = peaks["hbm_gbs"], "GB/s"
+        extra = {}
+    roofline = {"bound": wl["bound"], "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_source": f"of {peak_src}",
+                "kernel": "conv_igemm_pair_kernel" if plan["algo"] == 3 else "conv_igemm_kernel",
+                "algorithmic_flops_per_launch": nums["flops"], "algorithmic_bytes_per_launch": nums["bytes"], **extra}
+    if stack is not None:
+        roofline["c5_strong"] = stack
+    cycled_mib = n_sets * per_set / 2 ** 20
+    l2_note = (f"{n_sets} rotating (x, y) sets = {cycled_mib:.0f} MiB "
+               + ("> 126 MiB L2 (cold L2 every step)" if cycled_mib > 126 else "<= 126 MiB L2: WARM L2")
+               + "; filter and bias shared")
+    line = {
+        "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": SHORT_DTYPE[wl["dtype"]], "data": "synthetic",
+        "config": {"workload": args.workload, "description": wl["desc"], "graph_nodes": node_types,
+                   "launch": "eager_api_calls" if args.eager else "cuda_graph_replay", "l2": l2_note,
+                   "per_gpu_batch": wl["n"], "parallelism": f"batch-sharded replicas x{world}, no collective",
+                   "tile": [plan["tile_m"], plan["tile_n"], plan["tile_k"]], "stages": plan["stages"],
+                   "grid": plan["grid"], "parity_checked_ranks": parity_ranks},
+        "pct_of_bf16_peak": 100.0 * (value / world) / peaks["bf16_tflops"],
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": e2e,
+        "sustained": sustained,
+        "two_stream_throughput": concurrent,
+        "eager_api": eager,
+        "parity_checked_ranks": parity_ranks,
+        "gpu_launches": steps * launches_per_step * world,
+        "clocks": clocks.summary(), "device_status_word": status_word,
+    }
+    print(json.dumps(line))
 
 
 # ------------------------------------------------------------------ ResNet-50 conv stack (workload c5)
@@ -510,24 +670,10 @@ def cpu_stack_leg(torch, images, repeats=2):
     return stack_totals(layers, images)["flops"] / med / 1e12, med
 
 
-def run_stack(args):
-    """All 53 ResNet-50 convolutions (scale + bias + ReLU fused), batch 1024 split over the ranks (strong scaling).
-    Every layer runs on an independently generated N(0,1) input of its own shape, so only convolutions are timed."""
-    import torch
-
-    import flagdnn_b200 as fd
-    from flagdnn_b200.convstack import make_layer_params, resnet50_conv_layers, run_layer, stack_totals
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    device = torch.device("cuda", local_rank)
+def _stack_device_leg(args, torch, dist, device, rank, world, local_rank, steps, warmup):
+    """The 53 convolutions of this rank's batch slice replayed from one CUDA graph; returns the timing (max over
+    ranks) and everything the callers report from."""
+    from flagdnn_b200.convstack import make_layer_params, resnet50_conv_layers, run_layer
     from flagdnn_b200.sharding import batch_slice
 
     total_batch = args.batch
@@ -535,7 +681,6 @@ def run_stack(args):
     batch = b1 - b0
     layers = resnet50_conv_layers()
     params = [make_layer_params(l, i, device) for i, l in enumerate(layers)]
-    peaks, peak_src = load_peaks()
     # one shared pool of random activations, viewed per layer as its NHWC input
     max_in = max(batch * l.cin * l.hw_in ** 2 for l in layers)
     g = torch.Generator(device=device).manual_seed(1000 + rank)
@@ -543,10 +688,12 @@ def run_stack(args):
     inputs = [pool[: batch * l.cin * l.hw_in ** 2].view(batch, l.hw_in, l.hw_in, l.cin).permute(0, 3, 1, 2)
               for l in layers]
 
-    def step():
+    def step(keep=None):
         out = None
         for l, prm, x in zip(layers, params, inputs):
             out = run_layer(l, x, prm)
+            if keep is not None:
+                keep.append(out)
         return out
 
     for _ in range(2):
@@ -554,21 +701,21 @@ def run_stack(args):
     torch.cuda.synchronize()
     stream = torch.cuda.Stream()
     graph = torch.cuda.CUDAGraph()
+    outputs = []
     with torch.cuda.stream(stream):
         step()
         stream.synchronize()
         with torch.cuda.graph(graph, stream=stream):
-            last = step()
+            last = step(outputs)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    steps = max(1, args.steps)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(warmup):
             graph.replay()
         stream.synchronize()
         barrier()
@@ -577,14 +724,62 @@ def run_stack(args):
             for _ in range(steps):
                 graph.replay()
             e1.record(stream)
+            clocks.sample()
             stream.synchronize()
+            clocks.sample()
         barrier()
-    elapsed_ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / steps
+    elapsed_ms = max_over_ranks(torch, dist, device, [e0.elapsed_time(e1)])[0]
+
+    # parity of what was timed: image 0 of a spread of layers (every resolution, both filter sizes, the stem)
+    # against the CPU oracle, outside the timed region
+    import oracle
+
+    parity_ok = True
+    picks = {"stem", "s1b0.conv2", "s2b0.conv2", "s2b1.conv1", "s3b1.conv2", "s3b0.conv3", "s4b0.conv2", "s4b1.conv1",
+             "s4b1.conv2", "s4b0.proj"}
+    for l, (w_, sc, bi), x, y in zip(layers, params, inputs, outputs):
+        if l.name not in picks:
+            continue
+        ref = oracle.conv2d_torch_cpu(x[:1], w_, bi, l.stride, l.pad, 1, 1, scale=sc, relu=l.relu)
+        parity_ok = parity_ok and bool(torch.allclose(y[:1].float().cpu(), ref, rtol=1e-2, atol=1e-2))
+    parity_ranks = count_true_over_ranks(torch, dist, device, parity_ok)
+    return dict(ms_per_step=elapsed_ms / steps, batch=batch, total_batch=total_batch, layers=layers, params=params,
+                inputs=inputs, last=last, clocks=clocks, barrier=barrier, parity_ranks=parity_ranks,
+                parity_layers=len(picks))
+
+
+def _stack_record(args, torch, fd, dist, device, rank, world, local_rank, peaks):
+    """Compact strong-scaled record of the ResNet-50 stack (batch 1024 over all ranks) for the default line."""
+    from flagdnn_b200.convstack import stack_totals
+
+    leg = _stack_device_leg(args, torch, dist, device, rank, world, local_rank, steps=10, warmup=3)
+    totals = stack_totals(leg["layers"], leg["total_batch"])
+    roof_s = stack_roofline_seconds(leg["layers"], leg["batch"], peaks)
+    ms = leg["ms_per_step"]
+    return {"workload": "c5", "scaling": "strong", "total_batch": leg["total_batch"], "per_gpu_batch": leg["batch"],
+            "n_gpus": world, "steps": 10, "warmup": 3, "ms_per_step": ms,
+            "value": totals["flops"] / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "frac_of_mixed_roofline": roof_s * 1e3 / ms, "mixed_roofline_ms": roof_s * 1e3,
+            "parity_checked_ranks": leg["parity_ranks"], "parity_checked_layers": leg["parity_layers"],
+            "clocks": leg["clocks"].summary()}
+
+
+def run_stack(args):
+    """All 53 ResNet-50 convolutions (scale + bias + ReLU fused), batch 1024 split over the ranks (strong scaling).
+    Every layer runs on an independently generated N(0,1) input of its own shape, so only convolutions are timed."""
+    import torch
+
+    import flagdnn_b200 as fd
+    from flagdnn_b200.convstack import run_layer, stack_totals
+
+    rank, world, local_rank, dist, cpu_stack = init_ranks(torch, lambda: cpu_stack_leg(torch, images=2))
+    device = torch.device("cuda", local_rank)
+    peaks, peak_src = load_peaks()
+    steps = max(1, args.steps)
+    leg = _stack_device_leg(args, torch, dist, device, rank, world, local_rank, steps=steps, warmup=max(args.warmup, 3))
+    layers, params, inputs, last, clocks, barrier = (leg[k] for k in ("layers", "params", "inputs", "last", "clocks", "barrier"))
+    batch, total_batch, ms_per_step = leg["batch"], leg["total_batch"], leg["ms_per_step"]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     totals = stack_totals(layers, total_batch)
     value = totals["flops"] / (ms_per_step * 1e-3) / 1e12
 
@@ -674,10 +869,7 @@ def run_stack(args):
     e2e_mode = "serial"
     if piped_ms < e2e_ms:
         e2e_ms, e2e_steps, e2e_mode = piped_ms, piped_steps, "copies overlapped with the neighbouring steps' forward"
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(torch, dist, device, [e2e_ms])[0]
     status_word = fd.device_status()
 
     if rank == 0:
@@ -685,7 +877,7 @@ def run_stack(args):
         launches = sum(fd.conv2d_plan(x, p_[0], stride=l.stride, padding=l.pad)["launches"]
                        for l, p_, x in zip(layers, params, inputs))
         slow = sorted(shape_ms.values(), key=lambda t: -t[1])[:6]
-        cpu_value, cpu_s = cpu_stack_leg(torch, images=2)
+        cpu_value, cpu_s = cpu_stack
         line = {
             "metric": "fused_conv2d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -695,8 +887,10 @@ def run_stack(args):
                        "inputs": "each layer reads independently generated N(0,1) activations of its shape; "
                                  "no pooling / residual glue in the timed region",
                        "launch": "cuda_graph_replay", "l2": "activations of every layer exceed the 126 MiB L2",
-                       "parallelism": f"batch-sharded replicas x{world}, no collective"},
+                       "parallelism": f"batch-sharded replicas x{world}, no collective",
+                       "parity_checked_ranks": leg["parity_ranks"], "parity_checked_layers": leg["parity_layers"]},
             "pct_of_bf16_peak": 100.0 * (value / world) / peaks["bf16_tflops"],
+            "parity_checked_ranks": leg["parity_ranks"],
             "roofline": {"bound": "mixed", "achieved": roof_s * 1e3, "peak": ms_per_step, "unit": "ms",
                          "frac": roof_s * 1e3 / ms_per_step, "traffic": None, "peak_source": f"of {peak_src}",
                          "note": "achieved = sum over layers of max(flops/tensor peak, bytes/HBM peak) for this rank's "
@@ -901,6 +1095,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1024, help="total batch of the c5 workload (split over the ranks)")
     ap.add_argument("--eager", action="store_true",
                     help="launch every step through the API instead of replaying a CUDA graph (for profilers)")
+    ap.add_argument("--no-stack", action="store_true",
+                    help="default workload only: leave out the nested strong-scaled ResNet-50 record (roofline.c5_strong)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (short runs under a profiler)")
     args = ap.parse_args()

@@ -38,7 +38,7 @@ def test_peaks_fall_back_when_file_is_missing(tmp_path, monkeypatch):
 def test_reference_arm_prints_one_contract_line(workload):
     env = dict(os.environ, RANK="0", WORLD_SIZE="1")
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--workload", workload,
-                          "--steps", "2", "--warmup", "1"], capture_output=True, text=True, env=env, timeout=600)
+                          "--steps", "2", "--warmup", "1"], capture_output=True, text=True, env=env, timeout=600)  # ~3 s of warm-up
     assert out.returncode == 0, out.stderr
     lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1
@@ -46,6 +46,8 @@ def test_reference_arm_prints_one_contract_line(workload):
     assert d["impl"] == "reference" and d["metric"] == "fused_conv2d_tflops" and d["unit"] == "TFLOP/s"
     assert d["value"] > 0 and d["higher_is_better"] is True and d["config"]["workload"] == workload
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
+    assert d["steps"] == 2 and d["warmup"] == 1, "the arm times exactly the steps it was asked for"
+    assert d["ms_per_step"] <= d["ms_per_step_mean"] * 1.5 and d["value_from_mean"] > 0
     assert d["e2e"] == {"value": d["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
 
 
@@ -54,3 +56,21 @@ def test_reference_arm_other_ranks_stay_silent():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1"],
                          capture_output=True, text=True, env=env, timeout=600)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_cpu_timer_warms_up_until_steady_then_times_exactly_the_requested_calls():
+    calls = []
+    durations = iter([0.030, 0.012, 0.004, 0.0041] + [0.004] * 50)   # slow first calls, then steady
+
+    def fn():
+        d = next(durations)
+        calls.append(d)
+        import time
+        time.sleep(d)
+
+    times = bench.time_cpu_calls(fn, warmup=1, steps=5, min_warm_seconds=0.0)
+    assert len(times) == 5 and len(calls) == 4 + 5, "warm-up ends at the first two calls that agree within 5 %"
+    assert max(times) < 0.012
+    t0 = __import__("time").perf_counter()
+    times = bench.time_cpu_calls(lambda: None, warmup=3, min_seconds=0.05, min_warm_seconds=0.2)
+    assert len(times) >= 3 and __import__("time").perf_counter() - t0 >= 0.2, "the warm-up lasts its minimum time"

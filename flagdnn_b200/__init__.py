@@ -23,6 +23,7 @@ from .conv_host import (  # noqa: F401
     device_status,
     fused_conv2d_bias_relu,
     set_algo,
+    set_stream_k,
 )
 from .graph import (  # noqa: F401
     CompiledGraph,

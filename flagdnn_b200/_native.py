@@ -23,6 +23,8 @@ FDNN_DEVICE_TIMEOUT = 6
 F16, BF16, F32, F64 = 0, 1, 2, 3
 ALGO_AUTO, ALGO_DIRECT, ALGO_IGEMM, ALGO_IGEMM_PAIR = 0, 1, 2, 3
 ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH = 0, 1, 2, 3
+STREAMK_FLAG_BYTES = 8192
+ALGO_FLAG_STREAM_K = 0x100
 
 EXPORTED_SYMBOLS = (
     "fdnn_abi_version",
@@ -32,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "fdnn_conv2d_pack_weight",
     "fdnn_conv2d_fwd",
     "fdnn_conv2d_fwd_residual",
+    "fdnn_conv2d_fwd_ex",
     "fdnn_max_pool2d_fwd",
     "fdnn_adaptive_avg_pool2d_fwd",
     "fdnn_conv2d_fwd_host",
@@ -75,7 +78,9 @@ class ConvPlan(ctypes.Structure):
         ("launches", ctypes.c_int32),
         ("low_channel", ctypes.c_int32),
         ("pixel_group", ctypes.c_int32),
+        ("stream_k", ctypes.c_int32),
         ("workspace_bytes", ctypes.c_int64),
+        ("streamk_bytes", ctypes.c_int64),
         ("packed_weight_bytes", ctypes.c_int64),
         ("smem_bytes", ctypes.c_int64),
         ("flops", ctypes.c_double),
@@ -128,6 +133,8 @@ def load() -> ctypes.CDLL:
     lib.fdnn_adaptive_avg_pool2d_fwd.argtypes = [ctypes.POINTER(PoolDesc), vp, vp, vp]
     lib.fdnn_conv2d_fwd_residual.restype = i32
     lib.fdnn_conv2d_fwd_residual.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, vp, i32, vp, vp, i64, vp]
+    lib.fdnn_conv2d_fwd_ex.restype = i32
+    lib.fdnn_conv2d_fwd_ex.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, vp, vp, i32, vp, vp, i64, vp, i64, vp]
     lib.fdnn_conv2d_fwd_host.restype = i32
     lib.fdnn_conv2d_fwd_host.argtypes = [ctypes.POINTER(ConvDesc), vp, vp, vp, vp, i32, vp, vp, i64, vp]
     lib.fdnn_conv2d_host_arena_bytes.restype = i32

@@ -34,6 +34,37 @@ _PLAN_CACHE_MAX = 256
 
 _FORCED_ALGO = nat.ALGO_AUTO
 
+# Scratch for reduction splitting on CTA pairs (include/flagdnn_b200.h, FDNN_STREAMK_FLAG_BYTES): one buffer per
+# (device, stream), flags zeroed when it is created; every launch leaves them zero, and launches on one stream
+# do not overlap, so the buffer is simply reused.
+_STREAMK_SCRATCH: "dict[tuple, torch.Tensor]" = {}
+_STREAM_K = False
+
+
+def set_stream_k(enabled: bool) -> bool:
+    """Switch reduction splitting on CTA pairs on or off for subsequent calls; returns the previous setting.
+    Off (the default), every tile is computed whole by one pair, and an image's result does not depend on the
+    batch it is computed in down to the last bit.  On, layers whose tiles do not fill whole rounds of the GPU's
+    pairs share the reduction steps evenly; on B200 that measured no faster (the layers are bound by operand
+    traffic from L2, which the split does not reduce), which is why it is off."""
+    global _STREAM_K
+    prev, _STREAM_K = _STREAM_K, bool(enabled)
+    return prev
+
+
+def _streamk_scratch(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    key = (device.index, stream)
+    buf = _STREAMK_SCRATCH.get(key)
+    if buf is not None and buf.numel() >= nbytes:
+        return buf
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    buf[: nat.STREAMK_FLAG_BYTES].zero_()
+    if not torch.cuda.is_current_stream_capturing():
+        # a buffer created during a stream capture belongs to that graph's memory pool and is zeroed by a node
+        # of that graph on every replay: it serves that call only
+        _STREAMK_SCRATCH[key] = buf
+    return buf
+
 
 def set_algo(algo: Union[int, str]) -> int:
     """Force the kernel family for subsequent calls: "auto", "direct", "igemm"
@@ -187,7 +218,7 @@ def conv2d_plan(input, weight, stride=1, padding=0, dilation=1, groups=1, algo=N
     ow = max(_conv_out_dim(w, padding4[2], padding4[3], dilation[1], kw, stride[1]), 0)
     out = _empty_output(input, n, c_out, oh, ow, meta=True)
     _, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups,
-                        _FORCED_ALGO if algo is None else algo)
+                        (_FORCED_ALGO if algo is None else algo) | (nat.ALGO_FLAG_STREAM_K if _STREAM_K else 0))
     return plan.as_dict()
 
 
@@ -233,7 +264,8 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
             if residual.shape != out.shape or residual.dtype != out.dtype or residual.device != out.device:
                 raise RuntimeError("residual must have the shape, dtype and device of the convolution's output")
             fusable = (residual.stride() == out.stride() and residual.data_ptr() % 16 == out.data_ptr() % 16)
-        d, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups, _FORCED_ALGO)
+        d, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups,
+                            _FORCED_ALGO | (nat.ALGO_FLAG_STREAM_K if _STREAM_K else 0))
         stream = torch.cuda.current_stream().cuda_stream
         packed_ptr = None
         packed = None
@@ -245,18 +277,20 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         if plan.workspace_bytes > 0:
             ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=input.device)
             ws_ptr = ws.data_ptr()
-        if residual is not None and fusable and not plan.low_channel:
-            nat.check(lib.fdnn_conv2d_fwd_residual(
-                ctypes.byref(d), input.data_ptr(), weight.data_ptr(), packed_ptr,
-                None if bias is None else bias.data_ptr(),
-                None if scale is None else scale.data_ptr(),
-                residual.data_ptr(), activation, out.data_ptr(), ws_ptr, plan.workspace_bytes, stream))
-            return out
-        nat.check(lib.fdnn_conv2d_fwd(
+        sk_ptr, sk_bytes = None, 0
+        if plan.stream_k:
+            sk = _streamk_scratch(input.device, stream, plan.streamk_bytes)
+            sk_ptr, sk_bytes = sk.data_ptr(), sk.numel()
+        fused_residual = residual is not None and fusable and not plan.low_channel
+        nat.check(lib.fdnn_conv2d_fwd_ex(
             ctypes.byref(d), input.data_ptr(), weight.data_ptr(), packed_ptr,
             None if bias is None else bias.data_ptr(),
             None if scale is None else scale.data_ptr(),
-            activation if residual is None else nat.ACT_NONE, out.data_ptr(), ws_ptr, plan.workspace_bytes, stream))
+            residual.data_ptr() if fused_residual else None,
+            activation if (residual is None or fused_residual) else nat.ACT_NONE,
+            out.data_ptr(), ws_ptr, plan.workspace_bytes, sk_ptr, sk_bytes, stream))
+        if fused_residual:
+            return out
         if residual is not None:
             # the residual's layout differs from the output's (or the low-channel path ran): the add
             # and the activation follow as device-side elementwise steps

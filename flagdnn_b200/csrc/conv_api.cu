@@ -218,6 +218,25 @@ fdnn_conv_desc grouped_desc(const fdnn_conv_desc* d, int q, int oh, int ow) {
   return v;
 }
 
+// Reduction splitting on CTA pairs: T tiles of K reduction steps on P pairs.  Whole tiles cost
+// ceil(T / P) * K steps on the busiest pair, an even split ceil(T * K / P) plus the exchange of one partial
+// tile (about three steps' worth of time).  Ranges shorter than 12 steps are not split (boundaries snap to
+// tile edges within kStreamKMinFrag steps, and every pair must keep a non-empty range).
+constexpr int kStreamKMinFrag = 4;
+struct StreamK {
+  bool worth;
+};
+StreamK plan_stream_k(long long tiles, long long k_steps, int pairs, bool filter_resident) {
+  StreamK r = {false};
+  if (tiles <= 0 || pairs <= 0 || filter_resident) return r;
+  const long long total = tiles * k_steps;
+  const long long whole = (tiles + pairs - 1) / pairs * k_steps;
+  const long long even = (total + pairs - 1) / pairs;
+  if (even < 12) return r;
+  r.worth = double(even + 3) <= 0.95 * double(whole);
+  return r;
+}
+
 int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void* y,
               fdnn_conv_plan* plan, bool allow_group = true) {
   int st = validate(d);
@@ -236,7 +255,8 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   plan->bytes = es * (double(d->n) * d->c * d->h * d->w + double(d->k) * cg * d->r * d->s + d->k + m * d->k);
 
   const bool geom_ok = igemm_geometry_ok(d) && m > 0 && m < 2.0e9;
-  int algo = d->algo;
+  int algo = d->algo & 0xff;
+  const bool split_allowed = (d->algo & FDNN_ALGO_FLAG_STREAM_K) != 0;
   if ((algo == FDNN_ALGO_IGEMM || algo == FDNN_ALGO_IGEMM_PAIR) && !geom_ok)
     return fail(FDNN_NOT_SUPPORTED, "implicit-GEMM path does not support this problem");
   const bool want_auto = algo == FDNN_ALGO_AUTO;
@@ -353,17 +373,24 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   if (algo == FDNN_ALGO_IGEMM_PAIR && !pair_ok)
     return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs f16/bf16 tensors and a dense channels-last output");
   const long long pair_tiles = (long long)((m_tiles + 1) / 2) * ((d->k + 255) / 256);
+  const long long k_steps = (long long)d->r * d->s * ((c_pad + 63) / 64);
+  const int pairs_all = sms / 2;
+  const bool resident = d->k <= 256 && k_steps <= igemm_pair_max_resident_steps();
+  const bool sk_on = split_allowed && plan_stream_k(pair_tiles, k_steps, pairs_all, resident).worth;
   if (algo == FDNN_ALGO_IGEMM_PAIR ||
-      (want_auto && pair_ok && d->k >= 256 && (long long)d->r * d->s * ((c_pad + 63) / 64) >= 16 &&
-       pair_tiles >= sms / 2)) {
+      (want_auto && pair_ok && d->k >= 256 && k_steps >= 16 && (pair_tiles >= pairs_all || sk_on))) {
     plan->algo = FDNN_ALGO_IGEMM_PAIR;
     plan->tile_m = 256;
     plan->tile_n = 256;
     plan->stages = igemm_pair_stages();
     plan->smem_bytes = igemm_pair_smem_bytes();
     plan->block = igemm_pair_threads();
-    const long long pairs = pair_tiles < sms / 2 ? pair_tiles : sms / 2;
+    const long long pairs = (pair_tiles < pairs_all && !sk_on) ? pair_tiles : pairs_all;
     plan->grid = int(2 * pairs);
+    if (sk_on) {
+      plan->stream_k = 1;
+      plan->streamk_bytes = FDNN_STREAMK_FLAG_BYTES + (long long)plan->grid * 128 * 256 * 4;
+    }
   }
   return FDNN_OK;
 }
@@ -767,7 +794,8 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, const voi
 
 static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
                     const void* bias, const void* scale, const void* residual, int activation, void* y,
-                    void* workspace, int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real);
+                    void* workspace, int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real,
+                    void* sk_scratch = nullptr, int64_t sk_bytes = 0);
 
 int fdnn_conv2d_fwd(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
                     const void* bias, const void* scale, int activation, void* y, void* workspace,
@@ -787,11 +815,25 @@ int fdnn_conv2d_fwd_residual(const fdnn_conv_desc* desc, const void* x, const vo
                   true, desc->k);
 }
 
+int fdnn_conv2d_fwd_ex(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
+                       const void* bias, const void* scale, const void* residual, int activation, void* y,
+                       void* workspace, int64_t workspace_bytes, void* streamk_scratch, int64_t streamk_bytes,
+                       void* stream_v) {
+  if (desc == nullptr) return fail(FDNN_BAD_PARAM, "descriptor is NULL");
+  if (residual != nullptr && (reinterpret_cast<uintptr_t>(residual) & 15u) != (reinterpret_cast<uintptr_t>(y) & 15u))
+    return fail(FDNN_NOT_SUPPORTED, "the residual must have y's alignment modulo 16 bytes");
+  if (streamk_scratch != nullptr && (reinterpret_cast<uintptr_t>(streamk_scratch) & 255u) != 0)
+    return fail(FDNN_BAD_PARAM, "the reduction-splitting scratch must be 256-byte aligned");
+  return fwd_impl(desc, x, w, w_packed, bias, scale, residual, activation, y, workspace, workspace_bytes, stream_v,
+                  true, desc->k, streamk_scratch, streamk_bytes);
+}
+
 // k_real: length of bias / scale (differs from desc->k only for the equivalent convolution of a
 // pixel-grouped layer, whose GEMM column j uses entry j % k_real).
 static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, const void* w_packed,
                     const void* bias, const void* scale, const void* residual, int activation, void* y,
-                    void* workspace, int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real) {
+                    void* workspace, int64_t workspace_bytes, void* stream_v, bool allow_group, int k_real,
+                    void* sk_scratch, int64_t sk_bytes) {
   fdnn_conv_plan plan;
   // A caller that hands over a packed filter wants it used even when w itself
   // would qualify for in-place reads; plan accordingly.
@@ -874,7 +916,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
     // run the equivalent convolution; its filter is the packed buffer, consumed in place
     const fdnn_conv_desc v = grouped_desc(&d, plan.pixel_group, plan.oh, plan.ow);
     return fwd_impl(&v, x, w_packed, nullptr, bias, scale, residual, activation, y, workspace, workspace_bytes,
-                    stream_v, false, d.k);
+                    stream_v, false, d.k, sk_scratch, sk_bytes);
   }
   if (plan.low_channel && residual != nullptr)
     return fail(FDNN_NOT_SUPPORTED, "the low-channel path takes no residual; add it in a separate step");
@@ -981,6 +1023,14 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
     if (!p.tma_store) return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs a dense channels-last output");
     p.b_resident = (d.k <= 256 && d.r * d.s * p.c_blocks <= igemm_pair_max_resident_steps()) ? 1 : 0;
+    // reduction splitting when the caller brought the scratch for it
+    if (plan.stream_k && !p.b_resident && sk_scratch != nullptr && sk_bytes >= plan.streamk_bytes &&
+        (reinterpret_cast<uintptr_t>(sk_scratch) & 255u) == 0) {
+      p.stream_k = 1;
+      p.sk_min_frag = kStreamKMinFrag;
+      p.sk_flags = static_cast<uint32_t*>(sk_scratch);
+      p.sk_slots = reinterpret_cast<float*>(static_cast<char*>(sk_scratch) + FDNN_STREAMK_FLAG_BYTES);
+    }
     e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY, tmR, p, plan.grid, stream);
   } else {
     e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, tmR, p, plan.grid, stream);

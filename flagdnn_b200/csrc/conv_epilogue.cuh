@@ -11,6 +11,7 @@
 #include <type_traits>
 
 #include "sm100_ptx.cuh"
+#include "stream_k.cuh"
 
 namespace fdnn {
 
@@ -120,6 +121,10 @@ __device__ __forceinline__ void load_residual_box(const T* box, long long row_st
 //                    (the producer asked for the tile's residual values to be brought into L2 a main loop
 //                    earlier, so these loads are L2 hits; holding a prefetched box in registers across
 //                    column groups does not fit beside the accumulator columns and spills)
+// sk_slot0 / sk_count / sk_slot_stride / sk_row / sk_pc0
+//                    reduction splitting: the accumulator holds only the tile's last reduction steps; add the
+//                    fp32 partial sums of sk_count other CTAs first (slots sk_slot0, sk_slot0 - sk_slot_stride,
+//                    ... in that order; this lane's row sk_row, this warp's first 16-byte piece sk_pc0)
 template <typename T, int BN, bool RES = false, int NBUF = 2>
 __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int kout, int act,
                                                     const float* s_scale, const float* s_bias,
@@ -127,7 +132,9 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
                                                     const CUtensorMap* tm_tail, int st_row, int st_img,
                                                     int st_rows, uint32_t& store_seq,
                                                     const T* res_box = nullptr, long long res_stride = 0,
-                                                    int res_rows = 0, bool use_scale = true) {
+                                                    int res_rows = 0, bool use_scale = true,
+                                                    const float* sk_slot0 = nullptr, int sk_count = 0,
+                                                    long long sk_slot_stride = 0, int sk_row = 0, int sk_pc0 = 0) {
   constexpr int kPerStore = 128 / int(sizeof(T));  // channels per staged row: 64 (16-bit) or 32 (fp32)
   constexpr int kLoads = kPerStore / 32;
   int groups = (kout - n0 + kPerStore - 1) / kPerStore;
@@ -158,6 +165,22 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
       __syncwarp();  // each lane reads its own row back piece by piece while it computes
     }
     tmem_ld_wait();
+    for (int c = 0; c < sk_count; ++c) {  // uniform across the launch's owner tiles; zero otherwise
+      const float* slot = sk_slot0 - c * sk_slot_stride;
+#pragma unroll
+      for (int l = 0; l < kLoads; ++l) {
+        float4 part[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) part[j] = sk_load_piece(slot, sk_pc0 + g * (kPerStore / 4) + l * 8 + j, sk_row);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          raw[l][4 * j + 0] = __float_as_uint(__uint_as_float(raw[l][4 * j + 0]) + part[j].x);
+          raw[l][4 * j + 1] = __float_as_uint(__uint_as_float(raw[l][4 * j + 1]) + part[j].y);
+          raw[l][4 * j + 2] = __float_as_uint(__uint_as_float(raw[l][4 * j + 2]) + part[j].z);
+          raw[l][4 * j + 3] = __float_as_uint(__uint_as_float(raw[l][4 * j + 3]) + part[j].w);
+        }
+      }
+    }
     uint32_t row[32];  // the 128 bytes this lane contributes
 #pragma unroll
     for (int l = 0; l < kLoads; ++l) {
@@ -245,6 +268,21 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
       if (st_rows > 0) tma_store_3d(st_rows >= 32 ? tm_full : tm_tail, buf, n0 + g * kPerStore, st_row, st_img);
       bulk_commit_group();
     }
+  }
+}
+
+// Contributor side of reduction splitting: this warp's 32 rows x WC raw fp32 accumulator columns go to the
+// CTA's slot (piece pc0 onwards, row `row`) instead of through the epilogue.
+template <int WC>
+__device__ __forceinline__ void epilogue_dump_partial(uint32_t t_row, float* slot, int pc0, int row) {
+  uint32_t raw[2][32];
+  tmem_ld_32x32b_x32(t_row, raw[0]);
+#pragma unroll
+  for (int c = 0; c < WC / 32; ++c) {
+    tmem_ld_wait();
+    if (c + 1 < WC / 32) tmem_ld_32x32b_x32(t_row + (c + 1) * 32, raw[(c + 1) & 1]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sk_store_piece(slot, pc0 + c * 8 + j, row, &raw[c & 1][4 * j]);
   }
 }
 

@@ -28,6 +28,7 @@
 #include "conv_epilogue.cuh"
 #include "conv_internal.h"
 #include "sm100_ptx.cuh"
+#include "stream_k.cuh"
 
 namespace fdnn {
 namespace {
@@ -138,6 +139,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int ohw = p.OH * p.OW;
+  const bool split = p.stream_k != 0;  // reduction splitting across pairs (stream_k.cuh)
 
   if (warp < kFirstEpiWarpPair) {
 #ifndef FDNN_NO_REG_REALLOC
@@ -160,7 +162,10 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             for (int cb = 0; cb < p.c_blocks; ++cb, ++kit)
               tma_load_3d_pair(b_res + kit * kBBytes, &tmB, bres, cb * kKB, r * p.S + s, int(rank) * kHalfN);
       }
-      for (int tile = pair_id; tile < total_tiles && alive; tile += num_pairs) {
+      TileWalk walk;
+      walk_init(walk, split, pair_id, num_pairs, total_tiles, k_iters, p.sk_min_frag);
+      while (alive && walk_next(walk)) {
+        const int tile = walk.tile;
         const int m_pair = tile / n_tiles;
         const int n_tile = tile - m_pair * n_tiles;
         const int m_tile = 2 * m_pair + int(rank);  // this CTA's 128-row tile (may lie past the end)
@@ -181,42 +186,49 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
         if constexpr (RES) {
           // this CTA's 128 x 256 residual values of the tile, asked into L2 a whole main loop before the
-          // epilogue reads them
-          if (p.residual != nullptr && !p.lowc) tma_prefetch_l2_3d(&tmR, n_tile * kPairN, m_tile * kRows, 0);
+          // epilogue reads them (only the pair that finishes the tile reads them)
+          if (p.residual != nullptr && !p.lowc && walk.ke == k_iters)
+            tma_prefetch_l2_3d(&tmR, n_tile * kPairN, m_tile * kRows, 0);
         }
         const uint32_t a_tx = p.lowc ? uint32_t(p.a_tx_bytes) : uint32_t(kABytes);
         const uint32_t pair_tx = 2 * (a_tx + (b_resident ? 0u : uint32_t(kBBytes)));
         const int b_row0 = n_tile * kPairN + int(rank) * kHalfN;
-        for (int r = 0; r < p.R && alive; ++r) {
-          for (int s = 0; s < p.S && alive; ++s) {
-            const uint16_t off_w = static_cast<uint16_t>(s * p.dil_w);
-            const uint16_t off_h = static_cast<uint16_t>(r * p.dil_h);
-            const int tap = r * p.S + s;
-            for (int cb = 0; cb < p.c_blocks; ++cb) {
-              const long long pt0 = p.prof ? clock64() : 0;
-              if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
-                                     kIncidentProducerWait, p.wait_limit)) {
-                alive = false;
-                break;
-              }
-              const long long pt1 = p.prof ? clock64() : 0;
-              prof_wait += pt1 - pt0;
-              ++prof_iters;
-              uint8_t* st = stage_base + stage * stage_stride;
-              if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], pair_tx);
-              const uint32_t bar = full0 + stage * 8;
-              const int c0 = cb * kKB;
-              if (p.lowc) {
-                tma_load_4d_pair(st, &tmA, bar, 0, 0, h_base + r * p.dil_h, img);
-              } else {
-                tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, off_w, off_h);
-              }
-              if (!b_resident) tma_load_3d_pair(st + kABytes, &tmB, bar, c0, tap, b_row0);
-              if (p.prof) prof_issue += clock64() - pt1;
-              if (++stage == uint32_t(n_stages)) {
-                stage = 0;
-                phase ^= 1u;
-              }
+        // reduction step kit = (r * S + s) * c_blocks + cb
+        int tap = walk.kb / p.c_blocks;
+        int cb = walk.kb - tap * p.c_blocks;
+        int r = tap / p.S;
+        int s_ = tap - r * p.S;
+        for (int kit = walk.kb; kit < walk.ke; ++kit) {
+          const long long pt0 = p.prof ? clock64() : 0;
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
+                                 kIncidentProducerWait, p.wait_limit)) {
+            alive = false;
+            break;
+          }
+          const long long pt1 = p.prof ? clock64() : 0;
+          prof_wait += pt1 - pt0;
+          ++prof_iters;
+          uint8_t* st = stage_base + stage * stage_stride;
+          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], pair_tx);
+          const uint32_t bar = full0 + stage * 8;
+          const int c0 = cb * kKB;
+          if (p.lowc) {
+            tma_load_4d_pair(st, &tmA, bar, 0, 0, h_base + r * p.dil_h, img);
+          } else {
+            tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, static_cast<uint16_t>(s_ * p.dil_w),
+                                    static_cast<uint16_t>(r * p.dil_h));
+          }
+          if (!b_resident) tma_load_3d_pair(st + kABytes, &tmB, bar, c0, r * p.S + s_, b_row0);
+          if (p.prof) prof_issue += clock64() - pt1;
+          if (++stage == uint32_t(n_stages)) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          if (++cb == p.c_blocks) {
+            cb = 0;
+            if (++s_ == p.S) {
+              s_ = 0;
+              ++r;
             }
           }
         }
@@ -245,7 +257,9 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const uint32_t empty_peer = map_to_cta(empty_own, 1);
       const uint32_t tfull_own = smem_u32(&tmem_full[0]);
       const uint32_t tfull_peer = map_to_cta(tfull_own, 1);
-      for (int tile = pair_id; tile < total_tiles && alive; tile += num_pairs, ++tcount) {
+      TileWalk walk;
+      walk_init(walk, split, pair_id, num_pairs, total_tiles, k_iters, p.sk_min_frag);
+      for (; alive && walk_next(walk); ++tcount) {
         const uint32_t buf = tcount & 1u;
         const uint32_t bphase = (tcount >> 1) & 1u;
         const long long mt0 = p.prof ? clock64() : 0;
@@ -257,7 +271,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if (p.prof) prof_wtmem += clock64() - mt0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kPairN;
-        for (int kit = 0; kit < k_iters; ++kit) {
+        for (int kit = walk.kb; kit < walk.ke; ++kit) {
           const long long mt1 = p.prof ? clock64() : 0;
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull, p.wait_limit)) {
             alive = false;
@@ -271,7 +285,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           for (int k = 0; k < kKB / 16; ++k) {
             const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
             const uint64_t b = make_sw128_kmajor_desc(bt + k * 32);
-            mma_f16_pair(d_tmem, a, b, kIdesc, (kit > 0 || k > 0) ? 1u : 0u);
+            mma_f16_pair(d_tmem, a, b, kIdesc, (kit > walk.kb || k > 0) ? 1u : 0u);
           }
           tc_commit_pair(empty_own + stage * 8);
           tc_commit_pair(empty_peer + stage * 8);
@@ -314,13 +328,20 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     uint32_t store_seq = 0;
     int staged_n_tile = -1;
     long long prof_ewait = 0, prof_t0 = p.prof ? clock64() : 0;
-    for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++tcount) {
+    TileWalk walk;
+    walk_init(walk, split, pair_id, num_pairs, total_tiles, k_iters, p.sk_min_frag);
+    const int my_warp = warp - kFirstEpiWarpPair;
+    const int sk_row = ew * 32 + lane;                   // this lane's row in the CTA's slot
+    const int sk_pc0 = chalf * (kWarpCols / 4);          // this warp's first 16-byte piece of a slot row
+    for (; walk_next(walk); ++tcount) {
+      const int tile = walk.tile;
       const int m_pair = tile / n_tiles;
       const int n_tile = tile - m_pair * n_tiles;
       const int n0 = n_tile * kPairN + chalf * kWarpCols;  // first column this warp owns
       const uint32_t buf = tcount & 1u;
       const uint32_t bphase = (tcount >> 1) & 1u;
-      if (n_tile != staged_n_tile) {
+      const bool finishes = walk.ke == k_iters;            // this pair computes the tile's last reduction steps
+      if (finishes && n_tile != staged_n_tile) {
         __syncwarp();
         for (int j = lane; j < kWarpCols; j += 32) {
           const int col = n0 + j;
@@ -341,6 +362,44 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       if (p.prof) prof_ewait += clock64() - et0;
       if (!ok) break;
       tc_fence_after();
+      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN + chalf * kWarpCols;
+      if (!finishes) {
+        // contributor: the tile's first reduction steps; the raw sums go to this CTA's slot
+        float* slot = p.sk_slots + (long long)blockIdx.x * kSkSlotFloats;
+        epilogue_dump_partial<kWarpCols>(t_row, slot, sk_pc0, sk_row);
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) sk_flag_release(p.sk_flags + blockIdx.x * kSkFlagsPerCta + my_warp, 1u);
+        tc_fence_before();
+        mbar_arrive_cluster(tempty_leader + buf * 8);
+        continue;
+      }
+      int sk_count = 0;
+      if (walk.kb > 0) {
+        // owner of a split tile: pairs pair_id-1, pair_id-2, ... hold its earlier steps, each as the first
+        // thing it computed; wait for this warp's counterpart in each of them
+        const long long L = (long long)total_tiles * k_iters;
+        const long long tile_base = (long long)tile * k_iters;
+        for (int q = pair_id - 1; q >= 0 && ok; --q) {
+          ++sk_count;
+          const uint32_t* flag = p.sk_flags + (2 * q + int(rank)) * kSkFlagsPerCta + my_warp;
+          if (lane == 0) {
+            const long long t0 = clock64();
+            uint32_t spins = 0;
+            while (sk_flag_acquire(flag) == 0u) {
+              if ((++spins & 0x3f) == 0 && (*abort_flag || clock64() - t0 > p.wait_limit)) {
+                atomicCAS(p.status, 0u, uint32_t(kIncidentPartialWait));
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+            }
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (sk_bound(q, L, num_pairs, k_iters, p.sk_min_frag) <= tile_base) break;  // q reaches the tile's first step
+        }
+        if (!ok) break;
+      }
       int st_row, st_img, st_rows;
       if (p.lowc) {
         st_img = m_tile / p.tiles_per_image;
@@ -351,9 +410,17 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         st_row = m_tile * kRows + ew * 32;
         st_rows = 32;
       }
-      const uint32_t t_row = tmem_base + (uint32_t(ew * 32) << 16) + buf * kPairN + chalf * kWarpCols;
+      const float* sk_slot0 = sk_count > 0 ? p.sk_slots + (long long)(2 * (pair_id - 1) + int(rank)) * kSkSlotFloats : nullptr;
       epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.act, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
-                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows, g_scale != nullptr);
+                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows, g_scale != nullptr,
+                                     sk_slot0, sk_count, 2LL * kSkSlotFloats, sk_row, sk_pc0);
+      if (sk_count > 0) {
+        // the slots are read: lower the flags for the next launch
+        __syncwarp();
+        if (lane == 0)
+          for (int c = 0; c < sk_count; ++c)
+            p.sk_flags[(2 * (pair_id - 1 - c) + int(rank)) * kSkFlagsPerCta + my_warp] = 0u;
+      }
       tc_fence_before();
       mbar_arrive_cluster(tempty_leader + buf * 8);
     }

@@ -43,6 +43,13 @@ struct IgemmParams {
   int k_real;            // length of bias / scale (GEMM column j uses entry j % k_real)
   uint32_t* status;
   long long* prof;       // optional: 16 cycle counters written by CTA 0 (nullptr = off)
+  // Reduction splitting on CTA pairs ("stream-K"): the pairs share the linear space (tile, reduction step)
+  // evenly instead of whole tiles; a tile cut by a range boundary is finished by the pair that holds its last
+  // reduction steps, which adds the fp32 partial sums the others left in sk_slots (see stream_k.cuh).
+  int stream_k;          // 1: split as above (pair kernel only), 0: whole tiles, round-robin
+  int sk_min_frag;       // range boundaries closer than this many reduction steps to a tile edge snap to it
+  float* sk_slots;       // one 128 x 256 fp32 slot per CTA
+  uint32_t* sk_flags;    // 8 words per CTA (one per epilogue warp), zero between launches
   long long wait_limit;  // SM clocks after which a wait on a barrier gives up (see fdnn_debug_set_wait_limit)
   int skip_copies;       // test aid: the copy-issuing role does nothing, so the first wait for data runs out
 };

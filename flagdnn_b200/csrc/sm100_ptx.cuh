@@ -15,7 +15,8 @@ enum : uint32_t {
   kIncidentMmaWaitFull = 2,    // MMA issuer: stage never filled
   kIncidentMmaWaitTmem = 3,    // MMA issuer: accumulator never drained
   kIncidentEpilogueWait = 4,   // epilogue: accumulator never completed
-  kIncidentDrainWait = 5       // teardown: outstanding copies never landed
+  kIncidentDrainWait = 5,      // teardown: outstanding copies never landed
+  kIncidentPartialWait = 6     // epilogue of a split tile: another pair's partial sums never arrived
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

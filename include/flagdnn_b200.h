@@ -51,6 +51,10 @@ typedef enum fdnn_status {
 #define FDNN_ALGO_DIRECT 1 /* CUDA-core direct convolution (any dtype, groups) */
 #define FDNN_ALGO_IGEMM 2  /* tcgen05 implicit GEMM, one CTA per tile (f16/bf16, f32 via 3xTF32) */
 #define FDNN_ALGO_IGEMM_PAIR 3 /* tcgen05 implicit GEMM on CTA pairs (f16/bf16, dense NHWC y) */
+/* OR-ed into fdnn_conv_desc.algo: the plan may split reductions across CTA pairs (see FDNN_STREAMK_FLAG_BYTES).
+ * Off by default: measured on B200, the layers it applies to are bound by L2 -> SM operand traffic, which the
+ * split does not change, and it came out 1-3 % slower than whole tiles on the 3x3 256-channel layer. */
+#define FDNN_ALGO_FLAG_STREAM_K 0x100
 
 /* epilogue activation */
 #define FDNN_ACT_NONE 0
@@ -87,12 +91,26 @@ typedef struct fdnn_conv_plan {
   int32_t launches;             /* kernels one fwd call launches (main + repack) */
   int32_t low_channel;          /* 1: C <= 4 path (pixel quads as GEMM rows, 16-pixel input windows) */
   int32_t pixel_group;          /* > 1: that many neighbouring output pixels form one GEMM row (narrow layers) */
+  int32_t stream_k;             /* 1: given streamk_bytes of scratch, fdnn_conv2d_fwd_ex splits reductions over the CTA pairs */
   int64_t workspace_bytes;      /* scratch fwd needs (0 when x is consumed in place) */
+  int64_t streamk_bytes;        /* size of that optional scratch (0: the plan does not split) */
   int64_t packed_weight_bytes;  /* size of the packed filter (0 when w is consumed in place) */
   int64_t smem_bytes;           /* dynamic shared memory of the main kernel */
   double flops;                 /* 2*N*OH*OW*K*(C/groups)*R*S, benchmark/test_conv2d_perf.py:139-148 */
   double bytes;                 /* x + w + bias + y once each, benchmark/base.py:661-668 */
 } fdnn_conv_plan;
+
+/* Reduction splitting ("stream-K", plan.stream_k): when the tiles of a layer do not fill a whole number of
+ * rounds of the GPU's CTA pairs (196 tiles on 74 pairs: 2.65 rounds of work in 3), the pairs share the
+ * (tile, reduction step) space evenly and exchange fp32 partial sums of the tiles cut in between through
+ * plan.streamk_bytes of scratch.  It is optional and explicit: only fdnn_conv2d_fwd_ex takes that scratch;
+ * without it (and through every other entry point) the same kernel runs whole tiles.  The first
+ * FDNN_STREAMK_FLAG_BYTES of the scratch are flags: they must be zero when the scratch is first used, and
+ * every launch leaves them zero, so one scratch buffer serves any number of launches as long as they do not
+ * overlap on the GPU (one buffer per stream).  A launch that ended in FDNN_DEVICE_TIMEOUT may leave flags
+ * raised: zero them again.  Results do not depend on timing, but a tile's fp32 additions are grouped by the
+ * split, so the last bit of an output can differ from the unsplit schedule's. */
+#define FDNN_STREAMK_FLAG_BYTES 8192
 
 /* Library/ABI version (FDNN_ABI_VERSION of the built library). */
 int fdnn_abi_version(void);
@@ -154,6 +172,16 @@ int fdnn_conv2d_fwd_residual(const fdnn_conv_desc* desc, const void* x,
                              const void* residual, int activation, void* y,
                              void* workspace, int64_t workspace_bytes,
                              void* stream);
+
+/* fdnn_conv2d_fwd_residual plus the optional scratch for reduction splitting (see FDNN_STREAMK_FLAG_BYTES):
+ * `streamk_scratch` of at least plan.streamk_bytes, 256-byte aligned, flags zero; NULL runs whole tiles.
+ * No counterpart in the reference, whose Triton kernels assign whole tiles
+ * (src/flag_dnn/graph/kernels/fused_conv.py:145-149). */
+int fdnn_conv2d_fwd_ex(const fdnn_conv_desc* desc, const void* x, const void* w,
+                       const void* w_packed, const void* bias, const void* scale,
+                       const void* residual, int activation, void* y,
+                       void* workspace, int64_t workspace_bytes,
+                       void* streamk_scratch, int64_t streamk_bytes, void* stream);
 
 /* Host-buffer convenience: same as fdnn_conv2d_fwd but x, w, bias, scale and y
  * are HOST pointers (dense, described by the strides in `desc`); copies in,

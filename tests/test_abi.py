@@ -51,7 +51,7 @@ def test_library_exports_every_declared_symbol(native_lib):
 def test_struct_layout_matches_header():
     # 18 int32 + 3 x 4 int64
     assert ctypes.sizeof(nat.ConvDesc) == 18 * 4 + 12 * 8
-    assert ctypes.sizeof(nat.ConvPlan) == 16 * 4 + 3 * 8 + 2 * 8  # 15 ints + padding
+    assert ctypes.sizeof(nat.ConvPlan) == 16 * 4 + 4 * 8 + 2 * 8  # 16 ints, 4 int64, 2 doubles
 
 
 def test_query_plans_headline_configs(native_lib):

@@ -185,7 +185,7 @@ def _packed_weight(weight: torch.Tensor, d: nat.ConvDesc, plan: nat.ConvPlan, st
     if plan.pixel_group > 1:
         layout = ("grouped", plan.pixel_group, d.stride_w)
     elif plan.low_channel:
-        layout = ("lowc", d.stride_w)
+        layout = ("lowc", plan.low_channel, d.stride_w)
     else:
         layout = ("krsc", plan.c_padded)
     key = (layout, id(weight), weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()),

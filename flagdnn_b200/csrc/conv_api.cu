@@ -147,9 +147,25 @@ struct LowChannel {
   bool ok;
   int ow4, ohs, rows_per_tile, tiles_per_image, w_pad;
   int lpad;  // zero pixels stored left of each row: the conv's left padding rounded up to even (16-byte pixels pairs)
+  // Fused variant for a dense 3-channel NHWC input and an even W-stride (the 7x7 stride-2 stem), CTA pairs
+  // only: no relayout pass and no fourth channel.  A quad's window starts every 4 * stride_w * 3 elements,
+  // which is a multiple of 16 bytes; per tile two warps copy the input rows it needs, shifted by
+  // `lead_chunks` zero pieces and zero-padded, into a small per-CTA scratch slot that the window copies
+  // read.  48 elements of a window hold data (three MMAs per filter row instead of four).
+  bool fused3;
+  int raw_rows;      // input rows per tile
+  int row_chunks;    // 16-byte pieces per scratch row
+  int lead_chunks;   // zero pieces before the row's own first piece
+  int shift_elems;   // window element at which the quad's first pixel's first tap sits
+  long long slot_bytes;
 };
 
-LowChannel low_channel_geometry(const fdnn_conv_desc* d, int oh, int ow, const void* y) {
+bool dense_nhwc3(const fdnn_conv_desc* d) {
+  return d->c == 3 && d->x_strides[1] == 1 && (d->w <= 1 || d->x_strides[3] == 3) &&
+         (d->h <= 1 || d->x_strides[2] == 3LL * d->w) && (d->n <= 1 || d->x_strides[0] == 3LL * d->w * d->h);
+}
+
+LowChannel low_channel_geometry(const fdnn_conv_desc* d, int oh, int ow, const void* y, bool pair_kernel = false) {
   LowChannel g = {};
   const bool is16 = elem_size(d->dtype) == 2;
   if (!is16 || d->groups != 1 || d->c > 4 || d->dil_w != 1 || ow < 4 || ow % 4 != 0 || ow / 4 > 128) return g;
@@ -166,6 +182,18 @@ LowChannel low_channel_geometry(const fdnn_conv_desc* d, int oh, int ow, const v
   const int need = d->stride_w * 4 * (g.ow4 - 1) + 16;
   g.w_pad = round_up(need > g.lpad + d->w ? need : g.lpad + d->w, 2);
   g.ok = true;
+  if (pair_kernel && dense_nhwc3(d) && d->stride_w % 2 == 0 && (3 * d->w) % 8 == 0 && d->r <= igemm_pair_max_resident_steps() &&
+      4 * d->k <= 256) {
+    const int lead_elems = round_up(3 * d->pad_left, 8);              // zeros before the row, whole 16-byte pieces
+    g.shift_elems = lead_elems - 3 * d->pad_left;
+    g.lead_chunks = lead_elems / 8;
+    g.raw_rows = (g.ohs - 1) * d->stride_h + (d->r - 1) * d->dil_h + 1;
+    const int span = g.shift_elems + 3 * (3 * d->stride_w + d->s);    // window elements that hold data
+    const int row_elems = round_up(12 * d->stride_w * (g.ow4 - 1) + 64, 8);
+    g.row_chunks = row_elems / 8;
+    g.slot_bytes = round_up(g.raw_rows * row_elems * 2, 256);
+    g.fused3 = span <= 48 && g.raw_rows <= 64 && g.slot_bytes <= 64 * 1024;
+  }
   return g;
 }
 
@@ -276,7 +304,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     return FDNN_OK;
   }
 
-  const LowChannel lc = low_channel_geometry(d, oh, ow, y);
+  LowChannel lc = low_channel_geometry(d, oh, ow, y);
   if (lc.ok) {
     const int sms_lc = sm_count();
     const int m_tiles_lc = d->n * lc.tiles_per_image;
@@ -308,6 +336,16 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
       plan->block = igemm_pair_threads();
       const long long pairs = pair_tiles_lc < sms_lc / 2 ? pair_tiles_lc : sms_lc / 2;
       plan->grid = int(2 * pairs);
+      lc = low_channel_geometry(d, oh, ow, y, true);
+      if (lc.fused3) {
+        // dense 3-channel input: no relayout pass; two small scratch slots per CTA instead of a copy of x
+        plan->low_channel = 2;
+        plan->c_padded = 3;
+        plan->x_repacked = 0;
+        plan->tile_k = 48;
+        plan->workspace_bytes = (long long)plan->grid * 2 * lc.slot_bytes;
+        plan->launches = 1;
+      }
     }
     return FDNN_OK;
   }
@@ -585,15 +623,28 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
                     const void* w_packed, const void* bias, const void* scale, int activation, void* y,
                     void* workspace, cudaStream_t stream) {
   const int es = elem_size(d.dtype);
-  const LowChannel lc = low_channel_geometry(&d, plan.oh, plan.ow, y);
-  if (!lc.ok) return fail(FDNN_BAD_PARAM, "low-channel plan no longer applies to these buffers");
-  cudaError_t e = launch_repack_x_lowc(d.dtype, x, reinterpret_cast<const long long*>(d.x_strides), d.n, d.c, d.h,
-                                       d.w, lc.lpad, lc.w_pad, workspace, stream);
-  if (e != cudaSuccess) return fail_cuda("low-channel repack launch", e);
+  const bool fused3 = plan.low_channel == 2;
+  const LowChannel lc = low_channel_geometry(&d, plan.oh, plan.ow, y, fused3);
+  if (!lc.ok || lc.fused3 != fused3) return fail(FDNN_BAD_PARAM, "low-channel plan no longer applies to these buffers");
+  cudaError_t e = cudaSuccess;
+  if (!fused3) {
+    e = launch_repack_x_lowc(d.dtype, x, reinterpret_cast<const long long*>(d.x_strides), d.n, d.c, d.h, d.w, lc.lpad,
+                             lc.w_pad, workspace, stream);
+    if (e != cudaSuccess) return fail_cuda("low-channel repack launch", e);
+  }
 
   const int n_gemm = 4 * d.k;
   alignas(64) CUtensorMap tmA, tmB, tmY, tmY2;
-  {
+  if (fused3) {
+    // windows of 64 elements every 4 output pixels' worth of input, over the per-CTA scratch slots:
+    // (element, quad, row of the slot, slot)
+    cuuint64_t dims[4] = {64, cuuint64_t(lc.ow4), cuuint64_t(lc.raw_rows), cuuint64_t(plan.grid) * 2};
+    cuuint64_t strides[3] = {cuuint64_t(d.stride_w) * 4 * 3 * es, cuuint64_t(lc.row_chunks) * 16, cuuint64_t(lc.slot_bytes)};
+    cuuint32_t box[4] = {64, cuuint32_t(lc.ow4), cuuint32_t(lc.ohs * d.stride_h), 1};
+    cuuint32_t estr[4] = {1, 1, cuuint32_t(d.stride_h), 1};
+    int st = encode_tiled(&tmA, d.dtype, workspace, 4, dims, strides, box, estr, "low-channel scratch windows");
+    if (st != FDNN_OK) return st;
+  } else {
     // windows of 64 elements that start every 4 output pixels' worth of input (overlapping rows)
     cuuint64_t dims[4] = {64, cuuint64_t(lc.ow4), cuuint64_t(d.h), cuuint64_t(d.n)};
     cuuint64_t strides[3] = {cuuint64_t(d.stride_w) * 4 * 4 * es, cuuint64_t(lc.w_pad) * 4 * es,
@@ -645,6 +696,20 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
   p.tiles_per_image = lc.tiles_per_image;
   p.ohs = lc.ohs;
   p.a_tx_bytes = lc.rows_per_tile * 128;
+  p.k16_per_step = 4;
+  if (fused3) {
+    p.fused3 = 1;
+    p.x3 = x;
+    p.scratch3 = workspace;
+    p.x_h = d.h;
+    p.x_row_chunks = 3 * d.w / 8;
+    p.x_unaligned = (reinterpret_cast<uintptr_t>(x) & 15u) != 0 ? 1 : 0;
+    p.raw_rows = lc.raw_rows;
+    p.row_chunks = lc.row_chunks;
+    p.lead_chunks = lc.lead_chunks;
+    p.slot_elems = int(lc.slot_bytes / es);
+    p.k16_per_step = 3;
+  }
   p.prof = g_prof_buffer;
   fill_debug_params(&p);
   p.status = g_status_ptr[dev];
@@ -664,7 +729,7 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
 // that fdnn_conv2d_fwd can refuse a buffer that was packed for another plan (another descriptor, or a y
 // whose alignment selects a different path) instead of reading it with the wrong geometry.
 struct PackedLayout {
-  int kind;            // 1: [K,R,S,Cpad] (x2 planes for f32), 2: low-channel quads, 3: pixel-grouped
+  int kind;            // 1: [K,R,S,Cpad] (x2 planes for f32), 2 / 4: low-channel quads (4 / 3 stored channels), 3: pixel-grouped
   int a, b;            // kind 1: c_pad, dtype; kind 2: stride_w, left shift; kind 3: pixel group, stride_w
   int k, c, r, s;
   bool operator==(const PackedLayout& o) const {
@@ -676,6 +741,8 @@ PackedLayout packed_layout_of(const fdnn_conv_desc& d, const fdnn_conv_plan& pla
   PackedLayout l = {1, plan.c_padded, d.dtype, d.k, d.c, d.r, d.s};
   if (plan.pixel_group > 1) {
     l.kind = 3; l.a = plan.pixel_group; l.b = d.stride_w;
+  } else if (plan.low_channel == 2) {
+    l.kind = 4; l.a = d.stride_w; l.b = round_up(3 * d.pad_left, 8) - 3 * d.pad_left;
   } else if (plan.low_channel) {
     l.kind = 2; l.a = d.stride_w; l.b = round_up(d.pad_left, 2) - d.pad_left;
   }
@@ -683,7 +750,10 @@ PackedLayout packed_layout_of(const fdnn_conv_desc& d, const fdnn_conv_plan& pla
 }
 
 const char* packed_layout_name(int kind) {
-  return kind == 2 ? "low-channel quad layout" : kind == 3 ? "pixel-grouped layout" : "[K,R,S,Cpad] layout";
+  return kind == 2   ? "low-channel quad layout (4 stored channels)"
+         : kind == 4 ? "low-channel quad layout (3 stored channels)"
+         : kind == 3 ? "pixel-grouped layout"
+                     : "[K,R,S,Cpad] layout";
 }
 
 struct PackedRecord {
@@ -762,12 +832,17 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, const voi
   fdnn_conv_desc d;
   if (desc == nullptr) return fail(FDNN_BAD_PARAM, "descriptor is NULL");
   d = *desc;
-  d.algo = FDNN_ALGO_IGEMM;  // the packed layouts are those of the tensor-core paths (single CTA and pairs share them)
-  // Planned against an unaligned filter pointer so that the answer is "packed", and against the y the
-  // forward call will write: its alignment decides between the generic [K,R,S,Cpad] layout and the
-  // low-channel / pixel-grouped ones exactly as fdnn_conv2d_fwd will decide.
+  // Planned as fdnn_conv2d_fwd will plan (same algo request; an unaligned filter pointer so that the answer
+  // is "packed"; the y it will write, whose alignment decides between the generic [K,R,S,Cpad] layout and
+  // the low-channel / pixel-grouped ones).  Where that plan is the direct kernel, which reads the filter
+  // unpacked, the layout of the single-CTA tensor-core path is written.
+  if ((d.algo & 0xff) == FDNN_ALGO_DIRECT) d.algo = FDNN_ALGO_IGEMM;
   fdnn_conv_plan plan;
   int st = make_plan(&d, nullptr, reinterpret_cast<const void*>(uintptr_t(1)), y, &plan);
+  if (st == FDNN_OK && plan.algo == FDNN_ALGO_DIRECT) {
+    d.algo = FDNN_ALGO_IGEMM;
+    st = make_plan(&d, nullptr, reinterpret_cast<const void*>(uintptr_t(1)), y, &plan);
+  }
   if (st != FDNN_OK) return st;
   if (w == nullptr || packed == nullptr) return fail(FDNN_BAD_PARAM, "w and packed must not be NULL");
   if (packed_bytes < plan.packed_weight_bytes)
@@ -778,10 +853,14 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, const voi
     e = launch_pack_w_grouped(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c, d.r, d.s,
                               d.stride_w, plan.pixel_group, plan.c_padded, packed,
                               static_cast<cudaStream_t>(stream));
+  } else if (plan.low_channel == 2) {
+    const int shift_elems = round_up(3 * d.pad_left, 8) - 3 * d.pad_left;
+    e = launch_pack_w_lowc(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c, d.r, d.s,
+                           d.stride_w, 3, shift_elems, packed, static_cast<cudaStream_t>(stream));
   } else if (plan.low_channel) {
     const int shift = round_up(d.pad_left, 2) - d.pad_left;
     e = launch_pack_w_lowc(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c, d.r, d.s,
-                           d.stride_w, shift, packed, static_cast<cudaStream_t>(stream));
+                           d.stride_w, 4, 4 * shift, packed, static_cast<cudaStream_t>(stream));
   } else {
     const long long plane = (long long)d.k * d.r * d.s * plan.c_padded;
     e = launch_pack_w(d.dtype, w, reinterpret_cast<const long long*>(d.w_strides), d.k, d.c, d.r, d.s,
@@ -978,6 +1057,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   p.M = d.n * plan.oh * plan.ow;
   p.Kout = d.k;
   p.k_real = k_real;
+  p.k16_per_step = 4;
   p.lowc = 0;
   p.rows_per_tile = 128;
   p.OH = plan.oh; p.OW = plan.ow;

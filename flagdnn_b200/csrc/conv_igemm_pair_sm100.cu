@@ -45,6 +45,10 @@ constexpr int kStages = 5;                           // streaming mode: 5 x 32 K
 constexpr int kRingBytes = 184 * 1024;               // operand region (stages, or resident filter + A stages)
 constexpr int kMaxStages = 8;                        // barrier slots
 constexpr int kMaxResidentSteps = 7;                 // resident filter: at most 7 x 16 KB per CTA
+#ifndef FDNN_CONV_BATCH
+#define FDNN_CONV_BATCH 6
+#endif
+constexpr int kConvBatch = FDNN_CONV_BATCH;          // 16-byte pieces a converter thread keeps in flight (fused 3-channel mode)
 #ifndef FDNN_PAIR_EPI_WARPS
 #define FDNN_PAIR_EPI_WARPS 8
 #endif
@@ -55,12 +59,12 @@ constexpr int kOutBufs = kEpiWarpsPair == 8 ? 1 : 2; // TMA-store staging buffer
 constexpr int kFirstEpiWarpPair = 4;                 // warp group 0: producer, issuer, two idle warps
 constexpr int kThreadsPair = 32 * (kFirstEpiWarpPair + kEpiWarpsPair);
 // warp group 0 hands registers to the epilogue warp groups (see conv_igemm_sm100.cu)
-constexpr int kRegsLeanPair = 104;
-constexpr int kRegsEpiloguePair = kEpiWarpsPair == 8 ? 200 : 232;
+constexpr int kRegsLeanPair = 128;
+constexpr int kRegsEpiloguePair = kEpiWarpsPair == 8 ? 184 : 224;
 static_assert(128 * kRegsLeanPair + 32 * kEpiWarpsPair * kRegsEpiloguePair <= 65536, "register file budget");
 constexpr int kOutBytes = kEpiWarpsPair * kOutBufs * 32 * kRowB;
 constexpr int kEpiBytes = kEpiWarpsPair * 2 * kWarpCols * int(sizeof(float));
-constexpr int kBarBytes = (2 * kMaxStages + 6) * 8 + 16;
+constexpr int kBarBytes = (2 * kMaxStages + 11) * 8 + 16;
 constexpr int kSmemPair = kRingBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
 static_assert(kStages * kStageBytes <= kRingBytes, "streaming ring must fit");
 constexpr uint32_t kTmemColsPair = 512;              // two 256-column accumulators
@@ -82,9 +86,13 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int k_iters = p.R * p.S * p.c_blocks;
   const bool b_resident = p.b_resident != 0;
   uint8_t* b_res = smem;
-  uint8_t* stage_base = smem + (b_resident ? k_iters * kBBytes : 0);
+  // fused 3-channel mode: an image of a scratch slot (the tile's input rows, shifted and zero-padded) is put
+  // together here by bulk copies and leaves for global memory in one piece
+  const int conv_bytes = p.fused3 ? (p.slot_elems * 2 + 1023) / 1024 * 1024 : 0;
+  uint8_t* conv_stage = smem + (b_resident ? k_iters * kBBytes : 0);
+  uint8_t* stage_base = conv_stage + conv_bytes;
   const int stage_stride = b_resident ? kABytes : kStageBytes;
-  int n_stages = b_resident ? (kRingBytes - k_iters * kBBytes) / kABytes : kStages;
+  int n_stages = b_resident ? (kRingBytes - k_iters * kBBytes - conv_bytes) / kABytes : kStages;
   if (n_stages > kMaxStages) n_stages = kMaxStages;
   uint8_t* out_stage = smem + kRingBytes;
   float* epi_stage = reinterpret_cast<float*>(out_stage + kOutBytes);
@@ -95,7 +103,10 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   uint64_t* tmem_empty = bars + 2 * kMaxStages + 2;   // [2], used in the leader only
   uint64_t* drain_bar = bars + 2 * kMaxStages + 4;
   uint64_t* bres_bar = bars + 2 * kMaxStages + 5;     // resident filter has landed (leader only)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 6);
+  uint64_t* raw_full = bars + 2 * kMaxStages + 6;     // [2] fused 3-channel mode: a scratch slot holds a tile's input rows
+  uint64_t* raw_empty = bars + 2 * kMaxStages + 8;    // [2] ... and every window copy of the tile that used it has landed
+  uint64_t* conv_in = bars + 2 * kMaxStages + 10;     // the input rows of a tile have landed in conv_stage
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 11);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -110,6 +121,11 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       mbar_init(&empty_bar[i], 1);                 // one commit from the leader's issuer
     }
     mbar_init(bres_bar, 1);
+    mbar_init(&raw_full[0], p.x_unaligned ? 2 : 1);   // converter warps that arrive per tile
+    mbar_init(&raw_full[1], p.x_unaligned ? 2 : 1);
+    mbar_init(conv_in, 1);
+    mbar_init(&raw_empty[0], 1);                   // the leader's issuer
+    mbar_init(&raw_empty[1], 1);
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_full[1], 1);
     mbar_init(&tmem_empty[0], 2 * kEpiWarpsPair * 32);  // epilogue threads of both CTAs
@@ -164,6 +180,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       TileWalk walk;
       walk_init(walk, split, pair_id, num_pairs, total_tiles, k_iters, p.sk_min_frag);
+      uint32_t tiles_done = 0;
       while (alive && walk_next(walk)) {
         const int tile = walk.tile;
         const int m_pair = tile / n_tiles;
@@ -193,6 +210,18 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const uint32_t a_tx = p.lowc ? uint32_t(p.a_tx_bytes) : uint32_t(kABytes);
         const uint32_t pair_tx = 2 * (a_tx + (b_resident ? 0u : uint32_t(kBBytes)));
         const int b_row0 = n_tile * kPairN + int(rank) * kHalfN;
+        if (p.fused3) {
+          // the converter warps have written this tile's input rows into slot (tiles_done & 1)
+          const uint32_t b_ = tiles_done & 1u;
+          if (!mbar_wait_bounded(&raw_full[b_], (tiles_done >> 1) & 1u, abort_flag, p.status, kIncidentProducerWait,
+                                 p.wait_limit)) {
+            alive = false;
+            break;
+          }
+          img = int(blockIdx.x) * 2 + int(b_);     // the slot is the window map's outermost coordinate
+          h_base = 0;
+        }
+        ++tiles_done;
         // reduction step kit = (r * S + s) * c_blocks + cb
         int tap = walk.kb / p.c_blocks;
         int cb = walk.kb - tap * p.c_blocks;
@@ -257,6 +286,8 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const uint32_t empty_peer = map_to_cta(empty_own, 1);
       const uint32_t tfull_own = smem_u32(&tmem_full[0]);
       const uint32_t tfull_peer = map_to_cta(tfull_own, 1);
+      const uint32_t raw_empty_peer = map_to_cta(smem_u32(&raw_empty[0]), 1);
+      const int k16 = p.k16_per_step;  // 16-element reduction slices per step that hold data (4, or 3)
       TileWalk walk;
       walk_init(walk, split, pair_id, num_pairs, total_tiles, k_iters, p.sk_min_frag);
       for (; alive && walk_next(walk); ++tcount) {
@@ -281,11 +312,18 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           tc_fence_after();
           const uint32_t st = smem_u32(stage_base + stage * stage_stride);
           const uint32_t bt = b_resident ? smem_u32(b_res + kit * kBBytes) : st + kABytes;
+          if (p.fused3 && kit == walk.ke - 1) {
+            // every window copy of this tile has landed in both CTAs: their converters may reuse the slot
+            mbar_arrive(&raw_empty[tcount & 1u]);
+            mbar_arrive_cluster(raw_empty_peer + (tcount & 1u) * 8);
+          }
 #pragma unroll
           for (int k = 0; k < kKB / 16; ++k) {
-            const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
-            const uint64_t b = make_sw128_kmajor_desc(bt + k * 32);
-            mma_f16_pair(d_tmem, a, b, kIdesc, (kit > walk.kb || k > 0) ? 1u : 0u);
+            if (k < k16) {
+              const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
+              const uint64_t b = make_sw128_kmajor_desc(bt + k * 32);
+              mma_f16_pair(d_tmem, a, b, kIdesc, (kit > walk.kb || k > 0) ? 1u : 0u);
+            }
           }
           tc_commit_pair(empty_own + stage * 8);
           tc_commit_pair(empty_peer + stage * 8);
@@ -307,6 +345,143 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         tc_commit_pair(smem_u32(drain_bar));
         mbar_wait_bounded(drain_bar, 0u, &never, p.status, kIncidentDrainWait, kWaitLimitCycles / 16);
       }
+    }
+  }
+  else if (p.fused3 && !p.skip_copies && !p.x_unaligned) {
+    // ---------------------------------------------- converter (warp 2), fused 3-channel mode
+    // A tile reads raw_rows input rows of its image.  The image of a scratch slot is assembled in conv_stage:
+    // row hr = lead_chunks zero pieces (the left padding, rounded so that windows start on 16 bytes), the input
+    // row, zeros to the end; rows above or below the image are all zeros.  Input rows arrive by bulk copies
+    // (nothing passes through registers), the finished image leaves by one bulk copy to the CTA's slot in
+    // global memory, where it stays in L2 for the window copies of the producer.
+    if (warp == 2) {
+      const int row_bytes = p.row_chunks * 16;
+      const int lead_bytes = p.lead_chunks * 16;
+      int data_bytes = p.x_row_chunks * 16;
+      if (data_bytes > row_bytes - lead_bytes) data_bytes = row_bytes - lead_bytes;
+      const int slot_bytes = p.slot_elems * 2;
+      for (int i = lane * 16; i < conv_bytes; i += 32 * 16)
+        *reinterpret_cast<uint4*>(conv_stage + i) = make_uint4(0u, 0u, 0u, 0u);   // the padding stays zero for good
+      fence_proxy_async_smem();
+      __syncwarp();
+      const uint8_t* xb = static_cast<const uint8_t*>(p.x3);
+      uint32_t use = 0, in_phase = 0;
+      TileWalk walk;
+      walk_init(walk, false, pair_id, num_pairs, total_tiles, k_iters, 0);
+      while (walk_next(walk)) {
+        const int m_tile = 2 * (walk.tile / n_tiles) + int(rank);
+        const int img = m_tile / p.tiles_per_image;
+        const int ti = m_tile - img * p.tiles_per_image;
+        const int h0 = ti * p.ohs * p.stride_h - p.pad_top;
+        const bool img_ok = m_tile < p.m_tiles;   // the pair's second tile may lie past the last image
+        const uint32_t b_ = use & 1u;
+        // rows outside the image: zeros over whatever an earlier tile left there
+        int rows_in = 0;
+        for (int hr = 0; hr < p.raw_rows; ++hr) {
+          const int h = h0 + hr;
+          if (img_ok && h >= 0 && h < p.x_h) {
+            ++rows_in;
+          } else {
+            for (int i = lane * 16; i < data_bytes; i += 32 * 16)
+              *reinterpret_cast<uint4*>(conv_stage + hr * row_bytes + lead_bytes + i) = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        bool ok = true;
+        if (lane == 0) {
+          if (rows_in > 0) {
+            mbar_arrive_expect_tx(conv_in, uint32_t(rows_in) * uint32_t(data_bytes));
+            for (int hr = 0; hr < p.raw_rows; ++hr) {
+              const int h = h0 + hr;
+              if (h >= 0 && h < p.x_h)
+                bulk_load_1d(conv_stage + hr * row_bytes + lead_bytes,
+                             xb + ((long long)img * p.x_h + h) * (p.x_row_chunks * 16), uint32_t(data_bytes), conv_in);
+            }
+          }
+          // the slot in global memory is free once every window copy of the tile that used it has landed
+          ok = mbar_wait_bounded(&raw_empty[b_], ((use >> 1) & 1u) ^ 1u, abort_flag, p.status, kIncidentProducerWait,
+                                 p.wait_limit);
+          if (rows_in > 0) {
+            ok = mbar_wait_bounded(conv_in, in_phase, abort_flag, p.status, kIncidentProducerWait, p.wait_limit) && ok;
+            in_phase ^= 1u;
+          }
+          if (ok) {
+            bulk_store_1d(static_cast<uint8_t*>(p.scratch3) + (long long)(int(blockIdx.x) * 2 + int(b_)) * slot_bytes,
+                          conv_stage, uint32_t(slot_bytes));
+            bulk_commit_group();
+            bulk_wait_group0();   // written, and conv_stage may be filled again
+            mbar_arrive(&raw_full[b_]);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        ++use;
+      }
+    }
+  }
+  else if (p.fused3 && !p.skip_copies) {
+    // ---------------------------------------------- converters (warps 2 and 3), fused 3-channel mode, input not
+    // 16-byte aligned: the same slot image written piece by piece from registers
+    // A tile reads raw_rows input rows of its image.  Each goes into the CTA's scratch slot as row_chunks
+    // 16-byte pieces: lead_chunks zero pieces (the left padding, rounded so that windows start on 16 bytes),
+    // the row's x_row_chunks pieces, zeros to the end; rows above or below the image are all zeros.
+    const int t = (warp - 2) * 32 + lane;
+    const int per_tile = p.raw_rows * p.row_chunks;
+    const uint4* x16 = static_cast<const uint4*>(p.x3);
+    const uint16_t* x2 = static_cast<const uint16_t*>(p.x3);
+    uint32_t use = 0;
+    bool alive = true;
+    TileWalk walk;
+    walk_init(walk, false, pair_id, num_pairs, total_tiles, k_iters, 0);
+    while (alive && walk_next(walk)) {
+      const int m_tile = 2 * (walk.tile / n_tiles) + int(rank);
+      const int img = m_tile / p.tiles_per_image;
+      const int ti = m_tile - img * p.tiles_per_image;
+      const int h0 = ti * p.ohs * p.stride_h - p.pad_top;
+      const uint32_t b_ = use & 1u;
+      bool ok = mbar_wait_bounded(&raw_empty[b_], ((use >> 1) & 1u) ^ 1u, abort_flag, p.status, kIncidentProducerWait,
+                                  p.wait_limit);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.scratch3) +
+                                            (long long)(int(blockIdx.x) * 2 + int(b_)) * p.slot_elems);
+      const bool img_ok = m_tile < p.m_tiles;   // the pair's second tile may lie past the last image
+      for (int base = t; base < per_tile; base += 64 * kConvBatch) {
+        uint4 v[kConvBatch];
+#pragma unroll
+        for (int u = 0; u < kConvBatch; ++u) {
+          const int idx = base + u * 64;
+          v[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (idx < per_tile) {
+            const int hr = idx / p.row_chunks;
+            const int j = idx - hr * p.row_chunks - p.lead_chunks;
+            const int h = h0 + hr;
+            if (img_ok && h >= 0 && h < p.x_h && j >= 0 && j < p.x_row_chunks) {
+              const long long piece = ((long long)img * p.x_h + h) * p.x_row_chunks + j;
+              if (!p.x_unaligned) {
+                v[u] = __ldg(x16 + piece);
+              } else {
+                const uint16_t* e = x2 + piece * 8;
+                v[u].x = e[0] | (uint32_t(e[1]) << 16);
+                v[u].y = e[2] | (uint32_t(e[3]) << 16);
+                v[u].z = e[4] | (uint32_t(e[5]) << 16);
+                v[u].w = e[6] | (uint32_t(e[7]) << 16);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kConvBatch; ++u) {
+          const int idx = base + u * 64;
+          if (idx < per_tile) dst[idx] = v[u];
+        }
+      }
+      __threadfence();
+      fence_proxy_async_all();   // the window copies (async proxy) read what these threads wrote
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_full[b_]);
+      ++use;
     }
   }
   } else {

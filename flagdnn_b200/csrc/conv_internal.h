@@ -40,6 +40,20 @@ struct IgemmParams {
   int ohs;               // low-channel mode: output rows per tile
   int a_tx_bytes;        // bytes one activation copy delivers (rows_per_tile * 128 in low-channel mode)
   int b_resident;        // pair kernel: the filter half stays in shared memory for the whole launch
+  // Low-channel mode on a dense 3-channel NHWC input (the stem), pair kernel only: no relayout pass.  Two warps
+  // of each CTA copy the tile's input rows, shifted to a 16-byte boundary and zero-padded left and right,
+  // into a per-CTA scratch slot in global memory (it stays in L2); the window copies then read that slot.
+  int fused3;            // 1: this mode
+  const void* x3;        // the input tensor (element type = tensor dtype)
+  void* scratch3;        // 2 slots per CTA of slot_elems elements each
+  int x_h;               // input height
+  int x_row_chunks;      // 16-byte pieces per input row (W * 3 / 8)
+  int x_unaligned;       // 1: x is not 16-byte aligned (pieces are read element by element)
+  int raw_rows;          // input rows a tile reads: (ohs - 1) * stride_h + (R - 1) * dil_h + 1
+  int row_chunks;        // 16-byte pieces per scratch row
+  int lead_chunks;       // zero pieces stored before an input row's first piece
+  int slot_elems;        // elements per scratch slot
+  int k16_per_step;      // MMAs (16 reduction elements each) per reduction step: 4, or 3 in this mode
   int k_real;            // length of bias / scale (GEMM column j uses entry j % k_real)
   uint32_t* status;
   long long* prof;       // optional: 16 cycle counters written by CTA 0 (nullptr = off)
@@ -125,11 +139,12 @@ cudaError_t launch_repack_x(int dtype, const void* x, const long long x_s[4], in
 // x -> [N][H][w_pad][4]: `pad_left` zero pixels, the image row, zeros up to w_pad; channel 4 is zero.
 cudaError_t launch_repack_x_lowc(int dtype, const void* x, const long long x_s[4], int N, int C, int H,
                                  int W, int pad_left, int w_pad, void* dst, cudaStream_t stream);
-// w -> [4*K][R][64]: row (q, k) holds filter k shifted to the q-th output pixel of a quad:
-// element (j*4 + c) of tap row r is w[k][c][r][j - stride_w*q - shift] (zero outside the filter);
-// `shift` = stored left padding minus the convolution's own left padding.
+// w -> [4*K][R][64]: row (q, k) holds filter k shifted to the q-th output pixel of a quad: with `chans`
+// stored channels per pixel (4, or 3 for the fused 3-channel mode), element
+// shift_elems + chans * (stride_w * q + t) + c of tap row r is w[k][c][r][t]; everything else is zero.
+// `shift_elems` = elements stored before the quad's first input pixel.
 cudaError_t launch_pack_w_lowc(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
-                               int S, int stride_w, int shift, void* dst, cudaStream_t stream);
+                               int S, int stride_w, int chans, int shift_elems, void* dst, cudaStream_t stream);
 // Pixel-grouped filter: w -> [q*K][R][S + (q-1)*stride_w][c_pad]; row (g, k) holds filter k
 // shifted by g*stride_w taps (zero where the g-th pixel of the group does not reach).
 cudaError_t launch_pack_w_grouped(int dtype, const void* w, const long long w_s[4], int K, int C, int R,

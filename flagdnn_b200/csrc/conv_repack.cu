@@ -184,7 +184,7 @@ repack_x_lowc_c3_kernel(const uint16_t* __restrict__ x, long long sn, long long 
 template <typename T>
 __global__ void __launch_bounds__(256)
 pack_w_lowc_kernel(const T* __restrict__ w, long long sk, long long sc, long long sr, long long ss, int K,
-                   int C, int R, int S, int stride_w, int shift, T* __restrict__ dst) {
+                   int C, int R, int S, int stride_w, int chans, int shift_elems, T* __restrict__ dst) {
   const long long total = 4LL * K * R * 64;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -193,10 +193,12 @@ pack_w_lowc_kernel(const T* __restrict__ w, long long sk, long long sc, long lon
     const int r = int(t % R); t /= R;
     const int row = int(t);          // q * K + k
     const int q = row / K, k = row - q * K;
-    const int j = e >> 2, c = e & 3;  // window pixel, channel
-    const int s = j - stride_w * q - shift;  // shift: stored left padding beyond the conv's own
+    // element = shift_elems + chans * (stride_w * q + tap) + channel
+    const int rel = e - shift_elems - chans * stride_w * q;
+    const int s = rel >= 0 ? rel / chans : -1;
+    const int c = rel >= 0 ? rel - s * chans : 0;
     T v = T(0.0f);
-    if (c < C && s >= 0 && s < S) v = w[k * sk + c * sc + r * sr + s * ss];
+    if (rel >= 0 && c < C && s < S) v = w[k * sk + c * sc + r * sr + s * ss];
     dst[i] = v;
   }
 }
@@ -295,15 +297,15 @@ cudaError_t launch_repack_x_lowc(int dtype, const void* x, const long long x_s[4
 }
 
 cudaError_t launch_pack_w_lowc(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
-                               int S, int stride_w, int shift, void* dst, cudaStream_t stream) {
+                               int S, int stride_w, int chans, int shift_elems, void* dst, cudaStream_t stream) {
   const long long total = 4LL * K * R * 64;
   const int grid = grid_for(total, 256);
   if (dtype == FDNN_F16) {
     pack_w_lowc_kernel<__half><<<grid, 256, 0, stream>>>(static_cast<const __half*>(w), w_s[0], w_s[1], w_s[2],
-                                                         w_s[3], K, C, R, S, stride_w, shift, static_cast<__half*>(dst));
+                                                         w_s[3], K, C, R, S, stride_w, chans, shift_elems, static_cast<__half*>(dst));
   } else if (dtype == FDNN_BF16) {
     pack_w_lowc_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(w), w_s[0], w_s[1], w_s[2], w_s[3], K, C, R, S, stride_w, shift,
+        static_cast<const __nv_bfloat16*>(w), w_s[0], w_s[1], w_s[2], w_s[3], K, C, R, S, stride_w, chans, shift_elems,
         static_cast<__nv_bfloat16*>(dst));
   } else {
     return cudaErrorInvalidValue;

@@ -77,12 +77,20 @@ def test_query_plans_headline_configs(native_lib):
     assert plan.algo == nat.ALGO_IGEMM and plan.x_repacked == 1 and plan.w_packed == 1 and plan.launches == 2
     assert plan.workspace_bytes == 2 * 4 * 56 * 56 * 64 * 4
     assert plan.packed_weight_bytes == 2 * 64 * 9 * 64 * 4
-    # stem: low-channel path — 3 channels stored as 4, pixel quads as GEMM rows (4 x 64 = 256 columns)
+    # stem on CTA pairs: dense 3-channel input read in place (no relayout pass): pixel quads as GEMM rows
+    # (4 x 64 = 256 columns), 48-element windows, two scratch slots of 13 input rows per CTA
     d = _desc(n=256, c=3, h=224, w=224, k=64, r=7, s=7, stride=2, pad=3)
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert plan.algo == nat.ALGO_IGEMM_PAIR and plan.low_channel == 2 and plan.c_padded == 3
+    assert plan.x_repacked == 0 and plan.w_packed == 1 and plan.launches == 1 and plan.tile_k == 48
+    assert plan.oh == 112 and plan.tile_n == 256
+    assert plan.workspace_bytes == 148 * 2 * 18688               # 13 rows x 712 elements, rounded to 256 bytes
+    assert plan.packed_weight_bytes == 256 * 7 * 64 * 2
+    # the single-CTA kernel keeps the relayout: 3 channels stored as 4, rows padded to 232 stored pixels
+    d.algo = nat.ALGO_IGEMM
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
     assert plan.low_channel == 1 and plan.c_padded == 4 and plan.x_repacked == 1 and plan.w_packed == 1
-    assert plan.oh == 112 and plan.tile_n == 256 and plan.launches == 2
-    assert plan.workspace_bytes == 256 * 224 * 232 * 4 * 2      # rows padded to 232 stored pixels
+    assert plan.launches == 2 and plan.workspace_bytes == 256 * 224 * 232 * 4 * 2
     assert plan.packed_weight_bytes == 256 * 7 * 64 * 2
     # the same layer with an NCHW output cannot use it and falls back to 8-channel padding
     d = _desc(n=256, c=3, h=224, w=224, k=64, r=7, s=7, stride=2, pad=3, channels_last=False)

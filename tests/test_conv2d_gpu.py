@@ -275,9 +275,22 @@ def test_benchmark_configs_full_size_properties(fd, cfg):
     assert torch.equal(out, again)
     assert (out >= 0).all()
     picks = [0, n // 2 + 1, n - 1]
+    plan_full = fd.conv2d_plan(x, w, stride=stride, padding=pad)
     for i in picks:
         alone = fd.fused_conv2d_bias_relu(x[i:i + 1], w, b, stride=stride, padding=pad)
-        assert torch.equal(alone, out[i:i + 1])
+        plan_one = fd.conv2d_plan(x[i:i + 1], w, stride=stride, padding=pad)
+        if (plan_one["low_channel"], plan_one["pixel_group"]) == (plan_full["low_channel"], plan_full["pixel_group"]):
+            # same reduction order in both kernels: bit for bit
+            assert torch.equal(alone, out[i:i + 1])
+        else:
+            # one image alone takes another operand layout (the stem: 4 stored channels instead of 3), which adds
+            # the same products in another order: fp32 sums differ in the last bits, outputs by one bf16 step at most
+            a, bb = alone.float(), out[i:i + 1].float()
+            assert (a - bb).abs().max() <= 2.0 ** -7 * bb.abs().max() and (alone != out[i:i + 1]).float().mean() < 1e-2
+    # two different batch slices of the full plan's own size class agree bit for bit
+    half = fd.fused_conv2d_bias_relu(x[n // 2:], w, b, stride=stride, padding=pad)
+    if fd.conv2d_plan(x[n // 2:], w, stride=stride, padding=pad)["low_channel"] == plan_full["low_channel"]:
+        assert torch.equal(half, out[n // 2:])
     ref = oracle.conv2d_torch_cpu(x[picks], w, b, stride, pad, 1, 1, relu=True)
     _check(out[picks], ref, "bfloat16")
     # all n images, in chunks, against the CPU call in bf16: both sides round once to bf16, so they may differ by
@@ -331,6 +344,10 @@ def test_pair_kernel_matches_single_cta_kernel_bitwise(fd, shape):
     _check(outs["pair"], oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, 1, relu=True), "bfloat16")
 
 
+def _pair2(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
 LOWC = [
     # n, c, h, w, k, r, s, stride, pad, dtype
     (2, 3, 32, 32, 64, 7, 7, 2, 3, "bfloat16"),            # the stem at a small image
@@ -340,11 +357,14 @@ LOWC = [
     (2, 2, 33, 48, 32, 5, 4, 2, (2, 2), "float16"),        # 25 output columns: not whole quads, generic path
     (2, 1, 33, 52, 32, 5, 4, 2, (2, 2), "float16"),        # one channel (torch then reports an NCHW-like view)
     (1, 3, 70, 520, 8, 3, 3, (3, 1), 1, "bfloat16"),       # 130 quads per row: more than one tile may hold
+    (3, 3, 40, 48, 32, 3, 3, 2, 1, "float16"),             # 3x3 stride 2: 128 GEMM columns, 32 window elements used
+    (2, 3, 37, 128, 64, 5, 5, 2, 2, "bfloat16"),           # 5x5 stride 2, 19 output rows in tiles of 8: ragged last tile
+    (5, 3, 64, 64, 64, 7, 7, 2, 3, "bfloat16"),            # the stem, an odd number of tiles for the pairs
 ]
 
 
 @pytest.mark.parametrize("algo", ["igemm", "pair"])
-@pytest.mark.parametrize("case", LOWC, ids=[f"c{c[1]}_{c[5]}x{c[6]}_k{c[4]}" for c in LOWC])
+@pytest.mark.parametrize("case", LOWC, ids=[f"c{c[1]}_{c[5]}x{c[6]}_k{c[4]}_w{c[3]}" for c in LOWC])
 def test_low_channel_path_matches_oracle(fd, case, algo):
     """C <= 4 with channels-last tensors: pixel quads become GEMM rows over 16-pixel input windows."""
     n, c, h, w_, k, r, s_, stride, pad, dtype_name = case
@@ -364,9 +384,39 @@ def test_low_channel_path_matches_oracle(fd, case, algo):
     finally:
         fd.set_algo("auto")
     expect_lowc = channels_last_out and (got.shape[3] % 4 == 0) and got.shape[3] // 4 <= 128
-    assert plan["low_channel"] == int(expect_lowc)
+    assert bool(plan["low_channel"]) == expect_lowc
+    # on CTA pairs a dense 3-channel input with an even W-stride is read without the relayout pass (mode 2)
+    fused3 = algo == "pair" and c == 3 and expect_lowc and _pair2(stride)[1] % 2 == 0 and (3 * w_) % 8 == 0
+    assert plan["low_channel"] == (2 if fused3 else int(expect_lowc))
     assert torch.equal(got, again)
     _check(got, oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, 1, scale=sc, relu=True), dtype_name)
+
+
+def test_stem_without_relayout_many_tiles_and_unaligned_input(fd):
+    """The 3-channel mode of the pair kernel over enough tiles that every CTA reuses both of its scratch slots
+    several times (slot hand-over between the converter warps, the copy-issuing thread and the MMA issuer), and on
+    an input whose first element is not 16-byte aligned (pieces are then read element by element)."""
+    n, hw, k = 96, 112, 64
+    store = _rand((n * hw * hw * 3 + 8,), 64, dist="uniform").to(torch.bfloat16).cuda()
+    w = _rand((k, 3, 7, 7), 65, std=147 ** -0.5).to(torch.bfloat16).cuda().contiguous(memory_format=torch.channels_last)
+    b = _rand((k,), 66, std=0.1).to(torch.bfloat16).cuda()
+    fd.set_algo("pair")
+    try:
+        for offset in (0, 1):
+            x = store[offset:offset + n * hw * hw * 3].view(n, hw, hw, 3).permute(0, 3, 1, 2)
+            assert (x.data_ptr() % 16 != 0) == bool(offset)
+            plan = fd.conv2d_plan(x, w, stride=2, padding=3)
+            assert plan["low_channel"] == 2 and plan["launches"] == 1 and plan["x_repacked"] == 0
+            assert plan["grid"] == 148 and n * 56 * 56 // 4 // 112 > 4 * 148, "several tiles per CTA"
+            got = fd.fused_conv2d_bias_relu(x, w, b, stride=2, padding=3)
+            again = fd.fused_conv2d_bias_relu(x, w, b, stride=2, padding=3)
+            assert torch.equal(got, again)
+            ref16 = oracle.conv2d_torch_cpu(x, w, b, 2, 3, 1, 1, relu=True, compute_dtype=torch.bfloat16)
+            torch.testing.assert_close(got.float().cpu(), ref16.float(), rtol=1e-2, atol=1e-2)
+            picks = [0, 17, n - 1]
+            _check(got[picks], oracle.conv2d_torch_cpu(x[picks], w, b, 2, 3, 1, 1, relu=True), "bfloat16")
+    finally:
+        fd.set_algo("auto")
 
 
 GROUPED = [

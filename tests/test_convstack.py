@@ -111,3 +111,87 @@ def test_bottleneck_block_graph_replays_as_one_cuda_graph(native_lib):
     y = oracle.conv2d_torch_cpu(y, w3, b3, 1, 0, 1, 1, scale=s3.reshape(-1))   # fp32: the fused tail rounds once
     ref = torch.relu(y + x.float().cpu())
     torch.testing.assert_close(expect.float().cpu(), ref, rtol=2e-2, atol=3e-2)
+
+
+# What the planner chooses for the ResNet-50 layers whose tile counts depend on the batch, at the batches the
+# ranks of a strong-scaled run hold (1024 images over 8 and 4 GPUs): (kernel family, tile rows, tile columns,
+# pixel group, low-channel mode, grid) on a 148-SM GPU.  A planner change shows up here before it shows up as a
+# silent change of tile shape under the parity check below.
+RANK_BATCH_PLANS = {
+    ("stem", 128): (3, 256, 256, 0, 2, 148),
+    ("s2b0.conv2", 128): (3, 256, 256, 2, 0, 148),
+    ("s3b0.conv2", 128): (3, 256, 256, 0, 0, 148),
+    ("s3b0.conv3", 128): (2, 128, 256, 0, 0, 148),
+    ("s3b0.proj", 128): (2, 128, 256, 0, 0, 148),
+    ("s3b1.conv1", 128): (3, 256, 256, 0, 0, 148),
+    ("s3b1.conv2", 128): (3, 256, 256, 0, 0, 148),
+    ("s4b0.conv1", 128): (3, 256, 256, 0, 0, 148),
+    ("s4b0.conv2", 128): (2, 128, 256, 0, 0, 98),      # 49 row tiles x 2 column tiles: under one round of 148 SMs
+    ("s4b0.conv3", 128): (2, 128, 256, 0, 0, 148),
+    ("s4b0.proj", 128): (3, 256, 256, 0, 0, 148),
+    ("s4b1.conv1", 128): (2, 128, 256, 0, 0, 98),
+    ("s4b1.conv2", 128): (2, 128, 256, 0, 0, 98),
+    ("stem", 256): (3, 256, 256, 0, 2, 148),
+    ("s2b0.conv2", 256): (3, 256, 256, 2, 0, 148),
+    ("s3b0.conv2", 256): (3, 256, 256, 0, 0, 148),
+    ("s3b0.conv3", 256): (2, 128, 256, 0, 0, 148),
+    ("s3b0.proj", 256): (2, 128, 256, 0, 0, 148),
+    ("s3b1.conv1", 256): (3, 256, 256, 0, 0, 148),
+    ("s3b1.conv2", 256): (3, 256, 256, 0, 0, 148),
+    ("s4b0.conv1", 256): (3, 256, 256, 0, 0, 148),
+    ("s4b0.conv2", 256): (3, 256, 256, 0, 0, 148),
+    ("s4b0.conv3", 256): (2, 128, 256, 0, 0, 148),
+    ("s4b0.proj", 256): (3, 256, 256, 0, 0, 148),
+    ("s4b1.conv1", 256): (3, 256, 256, 0, 0, 148),
+    ("s4b1.conv2", 256): (3, 256, 256, 0, 0, 148),
+}
+
+
+def _plan_tuple(fd, x, w, layer):
+    p = fd.conv2d_plan(x, w, stride=layer.stride, padding=layer.pad)
+    return (p["algo"], p["tile_m"], p["tile_n"], p["pixel_group"], p["low_channel"], p["grid"])
+
+
+def test_rank_batch_plans_are_the_recorded_ones():
+    """CPU side of the table: the planner needs no GPU (148 SMs are assumed when no device is visible)."""
+    import flagdnn_b200 as fd
+
+    if torch.cuda.is_available() and torch.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("the table is for a 148-SM GPU")
+    by_name = {l.name: l for l in resnet50_conv_layers()}
+    for (name, batch), want in RANK_BATCH_PLANS.items():
+        l = by_name[name]
+        x = torch.empty(batch, l.cin, l.hw_in, l.hw_in, dtype=torch.bfloat16, device="meta", memory_format=torch.channels_last)
+        w = torch.empty(l.cout, l.cin, l.k, l.k, dtype=torch.bfloat16, device="meta", memory_format=torch.channels_last)
+        assert _plan_tuple(fd, x, w, l) == want, f"{name} at batch {batch}"
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch", [128, 256])
+def test_batch_dependent_layers_at_the_batches_ranks_hold(native_lib, batch):
+    """The stem, the stride-2 3x3 layers and every 14x14 / 7x7 layer at 128 and 256 images: the planned tile
+    shape is the recorded one, every image agrees with the reference's CPU call in bf16 and sampled images
+    (first, last, and two whose rows straddle tile boundaries) with the fp32 oracle."""
+    import flagdnn_b200 as fd
+    from flagdnn_b200.convstack import make_layer_params, run_layer
+
+    by_name = {l.name: (i, l) for i, l in enumerate(resnet50_conv_layers())}
+    g = torch.Generator(device="cuda").manual_seed(batch)
+    for (name, b_), want in RANK_BATCH_PLANS.items():
+        if b_ != batch:
+            continue
+        index, l = by_name[name]
+        w, scale, bias = make_layer_params(l, index, "cuda")
+        x = torch.randn(batch, l.hw_in, l.hw_in, l.cin, generator=g, device="cuda").to(torch.bfloat16).permute(0, 3, 1, 2)
+        assert _plan_tuple(fd, x, w, l) == want, f"{name} at batch {batch}"
+        y = run_layer(l, x, (w, scale, bias))
+        y_cpu = y.float().cpu()
+        for i0 in range(0, batch, 64):
+            ref16 = oracle.conv2d_torch_cpu(x[i0:i0 + 64], w, bias, l.stride, l.pad, 1, 1, scale=scale, relu=l.relu,
+                                            compute_dtype=torch.bfloat16)
+            torch.testing.assert_close(y_cpu[i0:i0 + 64], ref16.float(), rtol=1.6e-2, atol=2e-2,
+                                       msg=lambda m: f"{name} batch {batch} images {i0}..: {m}")
+        picks = [0, batch // 3, batch // 2 + 1, batch - 1]
+        ref = oracle.conv2d_torch_cpu(x[picks], w, bias, l.stride, l.pad, 1, 1, scale=scale, relu=l.relu)
+        torch.testing.assert_close(y_cpu[picks], ref, rtol=1e-2, atol=1e-2, msg=lambda m: f"{name} batch {batch}: {m}")
+    assert fd.device_status() == 0

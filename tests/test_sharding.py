@@ -59,3 +59,45 @@ def test_two_rank_sharded_run_reassembles(tmp_path, n_total):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), n_total, str(tmp_path)), nprocs=world, join=True)
     assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+
+
+def _worker_partner_leaves(rank, world, port, result_dir):
+    """Rank 1 leaves between steps (after a completed gather, with nothing in flight); rank 0's next gather must
+    end with an error within the process group's timeout instead of waiting forever."""
+    import datetime
+    import time
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    y_local = torch.full((2, 3), float(rank))
+    first = gather_batch(y_local, 4)                      # step 1: both ranks take part
+    assert first.shape == (4, 3) and first[:2].eq(0).all() and first[2:].eq(1).all()
+    if rank == 1:
+        open(os.path.join(result_dir, "left1"), "w").close()
+        os._exit(0)                                       # gone: no further collective, no clean shutdown
+    t0 = time.monotonic()
+    try:
+        gather_batch(y_local, 4)                          # step 2: the partner never joins
+        outcome = "returned"
+    except Exception as exc:                              # gloo reports a timeout or a closed connection
+        outcome = f"error:{type(exc).__name__}"
+    took = time.monotonic() - t0
+    with open(os.path.join(result_dir, "rank0"), "w") as fh:
+        fh.write(f"{outcome} {took:.1f}")
+    os._exit(0)                                           # the group cannot be torn down cleanly without its partner
+
+
+def test_gather_with_a_departed_rank_fails_within_the_timeout(tmp_path):
+    world = 2
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_partner_leaves, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode is not None, "a rank is still waiting: the departed partner hung it"
+    assert os.path.exists(tmp_path / "left1")
+    outcome, took = open(tmp_path / "rank0").read().split()
+    assert outcome.startswith("error:"), outcome
+    assert float(took) < 60.0

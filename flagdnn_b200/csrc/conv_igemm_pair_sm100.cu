@@ -46,7 +46,7 @@ constexpr int kRingBytes = 184 * 1024;               // operand region (stages, 
 constexpr int kMaxStages = 8;                        // barrier slots
 constexpr int kMaxResidentSteps = 7;                 // resident filter: at most 7 x 16 KB per CTA
 #ifndef FDNN_CONV_BATCH
-#define FDNN_CONV_BATCH 6
+#define FDNN_CONV_BATCH 4
 #endif
 constexpr int kConvBatch = FDNN_CONV_BATCH;          // 16-byte pieces a converter thread keeps in flight (fused 3-channel mode)
 #ifndef FDNN_PAIR_EPI_WARPS
@@ -59,9 +59,19 @@ constexpr int kOutBufs = kEpiWarpsPair == 8 ? 1 : 2; // TMA-store staging buffer
 constexpr int kFirstEpiWarpPair = 4;                 // warp group 0: producer, issuer, two idle warps
 constexpr int kThreadsPair = 32 * (kFirstEpiWarpPair + kEpiWarpsPair);
 // warp group 0 hands registers to the epilogue warp groups (see conv_igemm_sm100.cu)
-constexpr int kRegsLeanPair = 128;
-constexpr int kRegsEpiloguePair = kEpiWarpsPair == 8 ? 184 : 224;
-static_assert(128 * kRegsLeanPair + 32 * kEpiWarpsPair * kRegsEpiloguePair <= 65536, "register file budget");
+#ifndef FDNN_PAIR_REGS_LEAN
+#define FDNN_PAIR_REGS_LEAN 128
+#endif
+#ifndef FDNN_PAIR_REGS_EPI
+#define FDNN_PAIR_REGS_EPI 184
+#endif
+constexpr int kRegsLeanPair = FDNN_PAIR_REGS_LEAN;
+constexpr int kRegsEpiloguePair = kEpiWarpsPair == 8 ? FDNN_PAIR_REGS_EPI : 224;
+// The warp groups can only re-divide what the launch allocated: 168 registers per thread (64 K registers / 384
+// threads, rounded down to a multiple of 8).  A split that adds up to more than that makes the epilogue groups'
+// setmaxnreg.inc wait forever for registers that never come, even if it is within the 64 K of the register file.
+static_assert(128 * kRegsLeanPair + 32 * kEpiWarpsPair * kRegsEpiloguePair <= kThreadsPair * (65536 / kThreadsPair / 8 * 8),
+              "register reallocation exceeds the launch allocation");
 constexpr int kOutBytes = kEpiWarpsPair * kOutBufs * 32 * kRowB;
 constexpr int kEpiBytes = kEpiWarpsPair * 2 * kWarpCols * int(sizeof(float));
 constexpr int kBarBytes = (2 * kMaxStages + 11) * 8 + 16;
@@ -302,39 +312,53 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if (p.prof) prof_wtmem += clock64() - mt0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kPairN;
-        for (int kit = walk.kb; kit < walk.ke; ++kit) {
-          const long long mt1 = p.prof ? clock64() : 0;
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull, p.wait_limit)) {
-            alive = false;
-            break;
-          }
-          if (p.prof) prof_wfull += clock64() - mt1;
-          tc_fence_after();
-          const uint32_t st = smem_u32(stage_base + stage * stage_stride);
-          const uint32_t bt = b_resident ? smem_u32(b_res + kit * kBBytes) : st + kABytes;
-          if (p.fused3 && kit == walk.ke - 1) {
-            // every window copy of this tile has landed in both CTAs: their converters may reuse the slot
-            mbar_arrive(&raw_empty[tcount & 1u]);
-            mbar_arrive_cluster(raw_empty_peer + (tcount & 1u) * 8);
-          }
+        // The reduction loop is the hot path of every layer and is sensitive to anything beside the wait, the
+        // MMAs and the commits (a conditional barrier arrive in it cost 17 % on the 3x3 256-channel layer):
+        // it exists once with four MMAs per step and once with a runtime count for the 3-channel mode.
+        auto reduce = [&](auto four_tag) {
+          constexpr bool kFour = decltype(four_tag)::value;
+          for (int kit = walk.kb; kit < walk.ke; ++kit) {
+            const long long mt1 = p.prof ? clock64() : 0;
+            if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull, p.wait_limit)) {
+              alive = false;
+              break;
+            }
+            if (p.prof) prof_wfull += clock64() - mt1;
+            tc_fence_after();
+            const uint32_t st = smem_u32(stage_base + stage * stage_stride);
+            const uint32_t bt = b_resident ? smem_u32(b_res + kit * kBBytes) : st + kABytes;
+            if constexpr (kFour) {
 #pragma unroll
-          for (int k = 0; k < kKB / 16; ++k) {
-            if (k < k16) {
-              const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
-              const uint64_t b = make_sw128_kmajor_desc(bt + k * 32);
-              mma_f16_pair(d_tmem, a, b, kIdesc, (kit > walk.kb || k > 0) ? 1u : 0u);
+              for (int k = 0; k < kKB / 16; ++k) {
+                const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
+                const uint64_t b = make_sw128_kmajor_desc(bt + k * 32);
+                mma_f16_pair(d_tmem, a, b, kIdesc, (kit > walk.kb || k > 0) ? 1u : 0u);
+              }
+            } else {
+              for (int k = 0; k < k16; ++k) {
+                const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
+                const uint64_t b = make_sw128_kmajor_desc(bt + k * 32);
+                mma_f16_pair(d_tmem, a, b, kIdesc, (kit > walk.kb || k > 0) ? 1u : 0u);
+              }
+            }
+            tc_commit_pair(empty_own + stage * 8);
+            tc_commit_pair(empty_peer + stage * 8);
+            if (++stage == uint32_t(n_stages)) {
+              stage = 0;
+              phase ^= 1u;
             }
           }
-          tc_commit_pair(empty_own + stage * 8);
-          tc_commit_pair(empty_peer + stage * 8);
-          if (++stage == uint32_t(n_stages)) {
-            stage = 0;
-            phase ^= 1u;
-          }
-        }
+        };
+        if (k16 == kKB / 16) reduce(std::true_type{}); else reduce(std::false_type{});
         if (alive) {
           tc_commit_pair(tfull_own + buf * 8);
           tc_commit_pair(tfull_peer + buf * 8);
+          if (p.fused3) {
+            // every window copy of this tile has landed in both CTAs (all of its "stage full" barriers were
+            // passed above): their converters may reuse the scratch slot
+            mbar_arrive(&raw_empty[tcount & 1u]);
+            mbar_arrive_cluster(raw_empty_peer + (tcount & 1u) * 8);
+          }
         }
       }
       if (p.prof && blockIdx.x == 0) {

@@ -65,7 +65,10 @@ constexpr int kFirstEpiWarp = 4;
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
 constexpr int kRegsLean = 104;
 constexpr int kRegsEpilogue = kEpiWarps == 8 ? 200 : 232;  // 128 * 104 + 256 * 200 = 384 * 168
-static_assert(128 * kRegsLean + 32 * kEpiWarps * kRegsEpilogue <= 65536, "register file budget");
+// the warp groups re-divide the launch allocation (168 registers x 384 threads); more than that and the
+// epilogue groups' setmaxnreg.inc would wait forever
+static_assert(128 * kRegsLean + 32 * kEpiWarps * kRegsEpilogue <= kThreads * (65536 / kThreads / 8 * 8),
+              "register reallocation exceeds the launch allocation");
 
 template <typename T, int BN>
 struct TileCfg {

@@ -237,40 +237,47 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         int cb = walk.kb - tap * p.c_blocks;
         int r = tap / p.S;
         int s_ = tap - r * p.S;
-        for (int kit = walk.kb; kit < walk.ke; ++kit) {
-          const long long pt0 = p.prof ? clock64() : 0;
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
-                                 kIncidentProducerWait, p.wait_limit)) {
-            alive = false;
-            break;
-          }
-          const long long pt1 = p.prof ? clock64() : 0;
-          prof_wait += pt1 - pt0;
-          ++prof_iters;
-          uint8_t* st = stage_base + stage * stage_stride;
-          if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], pair_tx);
-          const uint32_t bar = full0 + stage * 8;
-          const int c0 = cb * kKB;
-          if (p.lowc) {
-            tma_load_4d_pair(st, &tmA, bar, 0, 0, h_base + r * p.dil_h, img);
-          } else {
-            tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, static_cast<uint16_t>(s_ * p.dil_w),
-                                    static_cast<uint16_t>(r * p.dil_h));
-          }
-          if (!b_resident) tma_load_3d_pair(st + kABytes, &tmB, bar, c0, r * p.S + s_, b_row0);
-          if (p.prof) prof_issue += clock64() - pt1;
-          if (++stage == uint32_t(n_stages)) {
-            stage = 0;
-            phase ^= 1u;
-          }
-          if (++cb == p.c_blocks) {
-            cb = 0;
-            if (++s_ == p.S) {
-              s_ = 0;
-              ++r;
+        auto copy_steps = [&](auto prof_tag) {
+          constexpr bool kProf = decltype(prof_tag)::value;
+          for (int kit = walk.kb; kit < walk.ke; ++kit) {
+            long long pt0 = 0, pt1 = 0;
+            if constexpr (kProf) pt0 = clock64();
+            if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, p.status,
+                                   kIncidentProducerWait, p.wait_limit)) {
+              alive = false;
+              break;
+            }
+            if constexpr (kProf) {
+              pt1 = clock64();
+              prof_wait += pt1 - pt0;
+              ++prof_iters;
+            }
+            uint8_t* st = stage_base + stage * stage_stride;
+            if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], pair_tx);
+            const uint32_t bar = full0 + stage * 8;
+            const int c0 = cb * kKB;
+            if (p.lowc) {
+              tma_load_4d_pair(st, &tmA, bar, 0, 0, h_base + r * p.dil_h, img);
+            } else {
+              tma_load_im2col_4d_pair(st, &tmA, bar, c0, w_base, h_base, img, static_cast<uint16_t>(s_ * p.dil_w),
+                                      static_cast<uint16_t>(r * p.dil_h));
+            }
+            if (!b_resident) tma_load_3d_pair(st + kABytes, &tmB, bar, c0, r * p.S + s_, b_row0);
+            if constexpr (kProf) prof_issue += clock64() - pt1;
+            if (++stage == uint32_t(n_stages)) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            if (++cb == p.c_blocks) {
+              cb = 0;
+              if (++s_ == p.S) {
+                s_ = 0;
+                ++r;
+              }
             }
           }
-        }
+        };
+        if (p.prof == nullptr) copy_steps(std::false_type{}); else copy_steps(std::true_type{});
       }
       if (p.prof && blockIdx.x == 0) {
         p.prof[0] = prof_wait; p.prof[1] = prof_issue; p.prof[2] = clock64() - prof_t0; p.prof[3] = prof_iters;
@@ -315,15 +322,17 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         // The reduction loop is the hot path of every layer and is sensitive to anything beside the wait, the
         // MMAs and the commits (a conditional barrier arrive in it cost 17 % on the 3x3 256-channel layer):
         // it exists once with four MMAs per step and once with a runtime count for the 3-channel mode.
-        auto reduce = [&](auto four_tag) {
+        auto reduce = [&](auto four_tag, auto prof_tag) {
           constexpr bool kFour = decltype(four_tag)::value;
+          constexpr bool kProf = decltype(prof_tag)::value;
           for (int kit = walk.kb; kit < walk.ke; ++kit) {
-            const long long mt1 = p.prof ? clock64() : 0;
+            long long mt1 = 0;
+            if constexpr (kProf) mt1 = clock64();
             if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status, kIncidentMmaWaitFull, p.wait_limit)) {
               alive = false;
               break;
             }
-            if (p.prof) prof_wfull += clock64() - mt1;
+            if constexpr (kProf) prof_wfull += clock64() - mt1;
             tc_fence_after();
             const uint32_t st = smem_u32(stage_base + stage * stage_stride);
             const uint32_t bt = b_resident ? smem_u32(b_res + kit * kBBytes) : st + kABytes;
@@ -349,7 +358,13 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             }
           }
         };
-        if (k16 == kKB / 16) reduce(std::true_type{}); else reduce(std::false_type{});
+        if (k16 != kKB / 16) {
+          reduce(std::false_type{}, std::false_type{});
+        } else if (p.prof == nullptr) {
+          reduce(std::true_type{}, std::false_type{});
+        } else {
+          reduce(std::true_type{}, std::true_type{});   // cycle counters of the role (development aid)
+        }
         if (alive) {
           tc_commit_pair(tfull_own + buf * 8);
           tc_commit_pair(tfull_peer + buf * 8);

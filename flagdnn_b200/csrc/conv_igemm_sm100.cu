@@ -305,38 +305,45 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (p.prof) prof_wtmem += clock64() - mt0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kit = 0; kit < k_iters; ++kit, ++it) {
-          const uint32_t stage = it % kStages;
-          const uint32_t phase = (it / kStages) & 1u;
-          const long long mt1 = p.prof ? clock64() : 0;
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status,
-                                 kIncidentMmaWaitFull, p.wait_limit)) {
-            alive = false;
-            break;
-          }
-          if (p.prof) prof_wfull += clock64() - mt1;
-          tc_fence_after();
-          const uint32_t st = smem_u32(stage_base + stage * Cfg::kStageBytes);
-#pragma unroll
-          for (int k = 0; k < Cfg::kKB / Cfg::kUK; ++k) {
-            const uint32_t acc = (kit > 0 || k > 0) ? 1u : 0u;
-            if constexpr (Cfg::kSplit) {
-              const uint64_t a_hi = make_sw128_kmajor_desc(st + k * 32);
-              const uint64_t a_lo = make_sw128_kmajor_desc(st + Cfg::kABytes + k * 32);
-              const uint64_t b_hi = make_sw128_kmajor_desc(st + 2 * Cfg::kABytes + k * 32);
-              const uint64_t b_lo =
-                  make_sw128_kmajor_desc(st + 2 * Cfg::kABytes + Cfg::kBBytes + k * 32);
-              mma_tf32(d_tmem, a_lo, b_hi, kIdesc, acc);
-              mma_tf32(d_tmem, a_hi, b_lo, kIdesc, 1u);
-              mma_tf32(d_tmem, a_hi, b_hi, kIdesc, 1u);
-            } else {
-              const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
-              const uint64_t b = make_sw128_kmajor_desc(st + Cfg::kABytes + k * 32);
-              mma_f16(d_tmem, a, b, kIdesc, acc);
+        // the reduction loop holds the wait, the MMAs and the commit and nothing else: the issuing thread is on
+        // the critical path of every step (cycle counters are compiled into a second copy of the loop)
+        auto reduce = [&](auto prof_tag) {
+          constexpr bool kProf = decltype(prof_tag)::value;
+          for (int kit = 0; kit < k_iters; ++kit, ++it) {
+            const uint32_t stage = it % kStages;
+            const uint32_t phase = (it / kStages) & 1u;
+            long long mt1 = 0;
+            if constexpr (kProf) mt1 = clock64();
+            if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, p.status,
+                                   kIncidentMmaWaitFull, p.wait_limit)) {
+              alive = false;
+              break;
             }
+            if constexpr (kProf) prof_wfull += clock64() - mt1;
+            tc_fence_after();
+            const uint32_t st = smem_u32(stage_base + stage * Cfg::kStageBytes);
+#pragma unroll
+            for (int k = 0; k < Cfg::kKB / Cfg::kUK; ++k) {
+              const uint32_t acc = (kit > 0 || k > 0) ? 1u : 0u;
+              if constexpr (Cfg::kSplit) {
+                const uint64_t a_hi = make_sw128_kmajor_desc(st + k * 32);
+                const uint64_t a_lo = make_sw128_kmajor_desc(st + Cfg::kABytes + k * 32);
+                const uint64_t b_hi = make_sw128_kmajor_desc(st + 2 * Cfg::kABytes + k * 32);
+                const uint64_t b_lo =
+                    make_sw128_kmajor_desc(st + 2 * Cfg::kABytes + Cfg::kBBytes + k * 32);
+                mma_tf32(d_tmem, a_lo, b_hi, kIdesc, acc);
+                mma_tf32(d_tmem, a_hi, b_lo, kIdesc, 1u);
+                mma_tf32(d_tmem, a_hi, b_hi, kIdesc, 1u);
+              } else {
+                const uint64_t a = make_sw128_kmajor_desc(st + k * 32);
+                const uint64_t b = make_sw128_kmajor_desc(st + Cfg::kABytes + k * 32);
+                mma_f16(d_tmem, a, b, kIdesc, acc);
+              }
+            }
+            tc_commit(&empty_bar[stage]);
           }
-          tc_commit(&empty_bar[stage]);
-        }
+        };
+        if (p.prof == nullptr) reduce(std::false_type{}); else reduce(std::true_type{});
         if (alive) tc_commit(&tmem_full[buf]);
       }
       if (p.prof && blockIdx.x == 0) {

@@ -982,6 +982,12 @@ EXTRA = {
     # mm on the same kernels: a 1x1 convolution over a row of M pixels
     "mm": dict(desc="mm bf16 [8192 x 4096] @ [4096 x 4096] as a 1x1 convolution over a row of M pixels",
                bound="tensor"),
+    # depthwise 3x3 at 64 channels, 56 x 56 (the shape of benchmark/test_conv2d_perf.py:51 of the reference at a
+    # batch larger than L2), NCHW as the reference benchmarks it and channels-last
+    "dw": dict(desc="depthwise 3x3 conv (groups = C = K = 64) 56x56 N=256 bf16 NCHW + bias, stride 1 pad 1",
+               bound="hbm"),
+    "dwcl": dict(desc="depthwise 3x3 conv (groups = C = K = 64) 56x56 N=256 bf16 channels-last + bias, stride 1 pad 1",
+                 bound="hbm"),
 }
 
 
@@ -992,7 +998,7 @@ def run_extra(args):
     import flagdnn_b200 as fd
 
     if int(os.environ.get("WORLD_SIZE", "1")) != 1:
-        raise RuntimeError("the 'res' and 'mm' workloads are single-GPU measurements")
+        raise RuntimeError("the 'res', 'mm' and 'dw' workloads are single-GPU measurements")
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
     wl = EXTRA[args.workload]
@@ -1029,6 +1035,32 @@ def run_extra(args):
             return run, 2.0 * m * hw * hw * k * c, f"{m} of {n} images, conv2d*scale+bias, add, relu in bf16 on CPU"
         h2d, d2h = 2 * n * hw * hw * (c + k), 2 * n * hw * hw * k
         host_in = [t.contiguous(memory_format=torch.channels_last).cpu().pin_memory() for t in sets[0]]
+    elif args.workload in ("dw", "dwcl"):
+        n, c, hw = 256, 64, 56
+        cl = args.workload == "dwcl"
+        w = rnd(c, 1, 3, 3, std=1 / 3)
+        bias = rnd(c, std=0.1)
+        per_set = 2 * 2 * n * c * hw * hw
+        n_sets = max(2, -(-3 * 126 * 2 ** 20 // per_set))
+
+        def make_x():
+            x = rnd(n, c, hw, hw)
+            return x.contiguous(memory_format=torch.channels_last) if cl else x
+        sets = [(make_x(),) for _ in range(n_sets)]
+        flops = 2.0 * n * c * hw * hw * 9
+        nbytes = per_set + 2 * (c * 9 + c)
+
+        def step(i):
+            return fd.conv2d(sets[i][0], w, bias, stride=1, padding=1, groups=c)
+
+        def cpu_once(m):
+            import oracle
+
+            x, wc, bc = sets[0][0][:m].cpu(), w.cpu(), bias.cpu()
+            return ((lambda: oracle.conv2d_torch_cpu(x, wc, bc, 1, 1, 1, c, compute_dtype=bf)),
+                    2.0 * m * c * hw * hw * 9, f"{m} of {n} images, F.conv2d(groups={c}) in bf16 on CPU")
+        h2d, d2h = 2 * n * c * hw * hw, 2 * n * c * hw * hw
+        host_in = [sets[0][0].cpu().pin_memory()]
     else:
         m_, k_, n_ = 8192, 4096, 4096
         b_mat = rnd(k_, n_, std=k_ ** -0.5)
@@ -1074,15 +1106,15 @@ def run_extra(args):
 
     # end to end: operands from pinned host memory, the result back, every step
     dev_in = [torch.empty_like(t, device=device) for t in host_in]
-    host_out = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    if args.workload == "res":
-        host_out = torch.empty(out.shape, dtype=out.dtype).contiguous(memory_format=torch.channels_last).pin_memory()
+    host_out = torch.empty_like(out, device="cpu").pin_memory()   # keeps the result's memory format
 
     def e2e_step():
         for d, h in zip(dev_in, host_in):
             d.copy_(h, non_blocking=True)
         if args.workload == "res":
             y = fd.conv2d_bias_act(dev_in[0], w, bias, scale=scale, relu=True, residual=dev_in[1])
+        elif args.workload in ("dw", "dwcl"):
+            y = fd.conv2d(dev_in[0], w, bias, stride=1, padding=1, groups=dev_in[0].shape[1])
         else:
             y = fd.mm(dev_in[0], b_mat)
         host_out.copy_(y, non_blocking=True)
@@ -1097,7 +1129,7 @@ def run_extra(args):
     e2e_ms = e0.elapsed_time(e1) / 5
 
     use_all_host_threads(torch)
-    run, cpu_flops, sample = cpu_once(8 if args.workload == "res" else 256)
+    run, cpu_flops, sample = cpu_once(256 if args.workload == "mm" else 8)
     run()
     times, t_all = [], time.perf_counter()
     while len(times) < 3 or time.perf_counter() - t_all < 10.0:

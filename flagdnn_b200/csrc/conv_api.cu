@@ -941,7 +941,8 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
     }
     p.x = x; p.w = w; p.bias = bias; p.scale = scale; p.residual = residual; p.y = y;
     p.act = activation;
-    cudaError_t e = launch_direct(d.dtype, p, stream);
+    const int dw = (d.algo & 0xff) == FDNN_ALGO_AUTO ? depthwise_kind(d.dtype, p) : 0;  // a forced "direct" stays direct
+    cudaError_t e = dw != 0 ? launch_depthwise(d.dtype, p, dw, stream) : launch_direct(d.dtype, p, stream);
     if (e != cudaSuccess) return fail_cuda("direct conv launch", e);
     return FDNN_OK;
   }

@@ -115,6 +115,11 @@ struct DirectParams {
   int act;  // FDNN_ACT_*
 };
 cudaError_t launch_direct(int dtype, const DirectParams& p, cudaStream_t stream);
+// Depthwise layers (groups == C == K) in f16 / bf16 / f32 (conv_depthwise.cu): `depthwise_kind` answers 0 when
+// the problem is not one of its cases (the direct kernel then runs), 1 for the channels-last kernel (16 bytes
+// of channels per thread), 2 for the kernel that gives every (image, channel) plane a block.
+int depthwise_kind(int dtype, const DirectParams& p);
+cudaError_t launch_depthwise(int dtype, const DirectParams& p, int kind, cudaStream_t stream);
 
 // Pooling (pool.cu): element strides of x and y in (n, c, h, w) order; idx (max pooling only) may be null.
 struct PoolParams {

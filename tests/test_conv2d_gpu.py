@@ -699,3 +699,46 @@ def test_host_buffer_entry_point(fd, native_lib):
     nat.check(native_lib.fdnn_conv2d_fwd_host(ctypes.byref(d), x.data_ptr(), w.data_ptr(), b.data_ptr(), None,
                                               nat.ACT_RELU, y.data_ptr(), arena.data_ptr(), need.value, None))
     _check(y, oracle.conv2d_torch_cpu(x, w, b, 1, 1, 1, 1, relu=True), "bfloat16")
+
+
+DEPTHWISE = [
+    # n, c, h, w, r, s, stride, pad, dilation, dtype, channels_last
+    (4, 32, 112, 112, 3, 3, 1, 1, 1, "bfloat16", False),     # the reference's depthwise perf shapes (benchmark/test_conv2d_perf.py:50-52)
+    (4, 64, 56, 56, 3, 3, 1, 1, 1, "bfloat16", False),
+    (4, 128, 28, 28, 5, 5, 1, 2, 1, "float16", False),
+    (4, 64, 56, 56, 3, 3, 1, 1, 1, "bfloat16", True),
+    (3, 128, 28, 28, 5, 5, 1, 2, 1, "float16", True),
+    (2, 40, 31, 29, 3, 3, 2, 1, 1, "bfloat16", True),        # stride 2, odd sizes, odd output width
+    (2, 24, 20, 23, 3, 5, (1, 2), (2, 3), (2, 1), "float32", True),   # dilation, rectangular filter, fp32 vectors of 4
+    (2, 16, 17, 19, 3, 3, 1, 1, (1, 2), "float32", False),   # dilation along W on planes
+    (2, 12, 14, 14, 3, 3, 1, 1, 1, "bfloat16", True),        # 12 channels: not whole 16-byte vectors -> plane kernel
+    (1, 8, 9, 11, 7, 7, 1, 3, 1, "float16", False),
+]
+
+
+@pytest.mark.parametrize("case", DEPTHWISE, ids=[f"c{c[1]}_{c[4]}x{c[5]}_{c[9]}_{'cl' if c[10] else 'nchw'}" for c in DEPTHWISE])
+def test_depthwise_kernels_match_oracle_and_direct_kernel(fd, case):
+    """groups == C == K: the channels-last and the per-plane depthwise kernels against the oracle and against
+    the one-thread-per-output direct kernel they replace, with scale, bias, a residual and ReLU."""
+    n, c, h, w_, r, s_, stride, pad, dil, dtype_name, cl = case
+    dtype = DTYPES[dtype_name]
+    x = _to_dev(_rand((n, c, h, w_), 80), dtype, cl)
+    w = _to_dev(_rand((c, 1, r, s_), 81, std=(r * s_) ** -0.5), dtype, False)
+    b = _to_dev(_rand((c,), 82, std=0.1), dtype, False)
+    sc = (torch.rand(c, generator=torch.Generator().manual_seed(83)) + 0.5).to(dtype).cuda()
+    got = fd.conv2d(x, w, b, stride=stride, padding=pad, dilation=dil, groups=c)
+    ref = oracle.conv2d_torch_cpu(x, w, b, stride, pad, dil, c)
+    _check(got, ref, dtype_name)
+    assert got.is_contiguous(memory_format=torch.channels_last) == cl or c == 1
+    fd.set_algo("direct")
+    try:
+        plain = fd.conv2d(x, w, b, stride=stride, padding=pad, dilation=dil, groups=c)
+    finally:
+        fd.set_algo("auto")
+    torch.testing.assert_close(got.float(), plain.float(), **TOL[dtype_name])
+    shortcut = _to_dev(_rand(tuple(got.shape), 84), dtype, cl)
+    fused = fd.conv2d_bias_act(x, w, b, stride=stride, padding=pad, dilation=dil, groups=c, scale=sc, relu=True,
+                               residual=shortcut)
+    ref = torch.relu(oracle.conv2d_torch_cpu(x, w, b, stride, pad, dil, c, scale=sc) + shortcut.float().cpu())
+    _check(fused, ref, dtype_name)
+    assert fd.device_status() == 0

@@ -25,6 +25,7 @@ ALGO_AUTO, ALGO_DIRECT, ALGO_IGEMM, ALGO_IGEMM_PAIR = 0, 1, 2, 3
 ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH = 0, 1, 2, 3
 STREAMK_FLAG_BYTES = 8192
 ALGO_FLAG_STREAM_K = 0x100
+ALGO_FLAG_OUT_F32 = 0x200
 
 EXPORTED_SYMBOLS = (
     "fdnn_abi_version",

@@ -239,7 +239,7 @@ def _empty_output(input, n, c_out, oh, ow, meta=False):
 
 
 def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activation, residual=None,
-         out=None) -> torch.Tensor:
+         out=None, out_f32=False) -> torch.Tensor:
     n, _, h, w = input.shape
     c_out, _, kh, kw = weight.shape
     oh = _conv_out_dim(h, padding4[0], padding4[1], dilation[0], kh, stride[0])
@@ -256,16 +256,19 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
     with torch.cuda.device(input.device):
         if out is None:
             out = _empty_output(input, n, c_out, oh, ow)
-        elif tuple(out.shape) != (n, c_out, oh, ow) or out.dtype != input.dtype or out.device != input.device:
-            raise RuntimeError(f"out must be a {input.dtype} tensor of shape {(n, c_out, oh, ow)} on {input.device}")
+        elif (tuple(out.shape) != (n, c_out, oh, ow) or out.device != input.device
+              or out.dtype != (torch.float32 if out_f32 else input.dtype)):
+            raise RuntimeError(f"out must be a {torch.float32 if out_f32 else input.dtype} tensor of shape "
+                               f"{(n, c_out, oh, ow)} on {input.device}")
         if n == 0:
             return out
         if residual is not None:
             if residual.shape != out.shape or residual.dtype != out.dtype or residual.device != out.device:
                 raise RuntimeError("residual must have the shape, dtype and device of the convolution's output")
             fusable = (residual.stride() == out.stride() and residual.data_ptr() % 16 == out.data_ptr() % 16)
-        d, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups,
-                            _FORCED_ALGO | (nat.ALGO_FLAG_STREAM_K if _STREAM_K else 0))
+        # a float32 result from 16-bit operands has one kernel family (the request for another is dropped)
+        algo = nat.ALGO_FLAG_OUT_F32 if out_f32 else (_FORCED_ALGO | (nat.ALGO_FLAG_STREAM_K if _STREAM_K else 0))
+        d, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups, algo)
         stream = torch.cuda.current_stream().cuda_stream
         packed_ptr = None
         packed = None
@@ -516,8 +519,8 @@ def mm(
     """Drop-in for ``flag_dnn.ops.mm`` (src/flag_dnn/ops/mm.py:336) on real tensors: ``input @ mat2`` is a
     1x1 convolution over a row of M pixels with K channels whose filter is ``mat2`` transposed, so it runs
     on the same kernels (fp64 on the direct one).  Checks and messages follow src/flag_dnn/ops/mm.py:100-140,
-    the ``out`` handling src/flag_dnn/ops/mm.py:153-181.  Complex tensors and an fp32 result from 16-bit
-    operands are not implemented on this path."""
+    the ``out`` handling src/flag_dnn/ops/mm.py:153-181.  ``out_dtype=torch.float32`` with fp16 / bf16 operands
+    stores the fp32 accumulators unrounded.  Complex tensors are not implemented on this path."""
     if input.dim() != 2:
         raise RuntimeError("self must be a matrix")
     if mat2.dim() != 2:
@@ -535,11 +538,12 @@ def mm(
         raise NotImplementedError("flag_dnn mm: complex tensors are not implemented on the convolution kernels")
     if input.dtype not in (torch.float16, torch.bfloat16, torch.float32, torch.float64):
         raise NotImplementedError(f"flag_dnn mm does not support dtype={input.dtype}")
+    wide = False
     if out_dtype is not None and out_dtype != input.dtype:
-        if input.dtype in (torch.float16, torch.bfloat16) and out_dtype == torch.float32:
-            raise NotImplementedError("flag_dnn mm: an fp32 result from fp16/bf16 operands is not implemented "
-                                      "on the convolution kernels")
-        raise RuntimeError("out_dtype must be the same as input dtype or fp32 for fp16/bf16 inputs")
+        if not (input.dtype in (torch.float16, torch.bfloat16) and out_dtype == torch.float32):
+            raise RuntimeError("out_dtype must be the same as input dtype or fp32 for fp16/bf16 inputs")
+        wide = True
+    y_dtype = torch.float32 if wide else input.dtype
     if not input.is_cuda:
         raise NotImplementedError("flag_dnn mm CUDA implementation requires CUDA input")
     m, k = input.shape
@@ -547,11 +551,11 @@ def mm(
     if out is not None:
         if out.device != input.device:
             raise RuntimeError(f"mm out tensor device mismatch: expected {input.device}, got {out.device}")
-        if out.dtype != input.dtype:
-            raise RuntimeError(f"Expected out tensor to have dtype {input.dtype}, but got {out.dtype} instead")
+        if out.dtype != y_dtype:
+            raise RuntimeError(f"Expected out tensor to have dtype {y_dtype}, but got {out.dtype} instead")
         if out.dim() != 2 or tuple(out.shape) != (m, n):
             out.resize_((m, n))
-    y = out if out is not None and out.is_contiguous() else torch.empty((m, n), dtype=input.dtype, device=input.device)
+    y = out if out is not None and out.is_contiguous() else torch.empty((m, n), dtype=y_dtype, device=input.device)
     if y.numel() > 0:
         if k == 0:
             y.zero_()
@@ -561,7 +565,7 @@ def mm(
             x4 = input.t().unsqueeze(0).unsqueeze(2)               # [1, K, 1, M]
             w4 = mat2.t().unsqueeze(-1).unsqueeze(-1)              # [N, K, 1, 1]: the filter is mat2 transposed
             _run(x4, w4, None, None, (1, 1), (0, 0, 0, 0), (1, 1), 1, nat.ACT_NONE,
-                 out=y.t().unsqueeze(0).unsqueeze(2))              # [1, N, 1, M] over y's memory
+                 out=y.t().unsqueeze(0).unsqueeze(2), out_f32=wide)   # [1, N, 1, M] over y's memory
     if out is not None and y is not out:
         out.copy_(y)
         return out

@@ -285,6 +285,14 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   const bool geom_ok = igemm_geometry_ok(d) && m > 0 && m < 2.0e9;
   int algo = d->algo & 0xff;
   const bool split_allowed = (d->algo & FDNN_ALGO_FLAG_STREAM_K) != 0;
+  const bool out_f32 = (d->algo & FDNN_ALGO_FLAG_OUT_F32) != 0;
+  if (out_f32) {
+    if (es != 2) return fail(FDNN_BAD_PARAM, "a float32 output is an option of f16 / bf16 operands");
+    if (algo == FDNN_ALGO_DIRECT || algo == FDNN_ALGO_IGEMM_PAIR || !igemm_geometry_ok(d))
+      return fail(FDNN_NOT_SUPPORTED, "a float32 output from 16-bit operands runs on the single-CTA tensor-core path only");
+    algo = FDNN_ALGO_IGEMM;
+    plan->bytes += 2.0 * m * d->k;  // y is four bytes per element
+  }
   if ((algo == FDNN_ALGO_IGEMM || algo == FDNN_ALGO_IGEMM_PAIR) && !geom_ok)
     return fail(FDNN_NOT_SUPPORTED, "implicit-GEMM path does not support this problem");
   const bool want_auto = algo == FDNN_ALGO_AUTO;
@@ -305,6 +313,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   }
 
   LowChannel lc = low_channel_geometry(d, oh, ow, y);
+  if (out_f32) lc.ok = false;   // quads and pixel groups rely on y's 16-bit layout
   if (lc.ok) {
     const int sms_lc = sm_count();
     const int m_tiles_lc = d->n * lc.tiles_per_image;
@@ -350,7 +359,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     return FDNN_OK;
   }
 
-  if (allow_group) {
+  if (allow_group && !out_f32) {
     const int q = choose_pixel_group(d, oh, ow, y);
     if (q > 1) {
       fdnn_conv_desc v = grouped_desc(d, q, oh, ow);
@@ -407,7 +416,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
 
   // CTA pairs: 16-bit types writing a dense NHWC y.  Worth it when the layer is
   // wide enough for 256-channel tiles and has at least one full wave of pairs.
-  const bool pair_ok = is16 && y_is_dense_nhwc(d, oh, ow, y) && (sms % 2 == 0);
+  const bool pair_ok = is16 && !out_f32 && y_is_dense_nhwc(d, oh, ow, y) && (sms % 2 == 0);
   if (algo == FDNN_ALGO_IGEMM_PAIR && !pair_ok)
     return fail(FDNN_NOT_SUPPORTED, "the CTA-pair kernel needs f16/bf16 tensors and a dense channels-last output");
   const long long pair_tiles = (long long)((m_tiles + 1) / 2) * ((d->k + 255) / 256);
@@ -1072,7 +1081,10 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   p.bias = bias; p.scale = scale; p.y = y;
   p.residual = residual;
   p.act = activation;
-  const int gran = 16 / es;
+  const bool out_f32 = (d.algo & FDNN_ALGO_FLAG_OUT_F32) != 0;
+  if (out_f32 && residual != nullptr) return fail(FDNN_NOT_SUPPORTED, "no residual with a float32 output from 16-bit operands");
+  p.out_f32 = out_f32 ? 1 : 0;
+  const int gran = out_f32 ? 4 : 16 / es;   // output elements per 16 bytes
   p.vec_store = (d.y_strides[1] == 1 && d.y_strides[0] % gran == 0 && d.y_strides[2] % gran == 0 &&
                  d.y_strides[3] % gran == 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0)
                     ? 1
@@ -1081,7 +1093,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   alignas(64) CUtensorMap tmY;
   p.tma_store = 0;
   {
-    const long long row = y_pixel_stride(&d, plan.oh, plan.ow);
+    const long long row = out_f32 ? 0 : y_pixel_stride(&d, plan.oh, plan.ow);
     if (row > 0 && (reinterpret_cast<uintptr_t>(y) & 15u) == 0) {
       st = encode_output_map(&tmY, d.dtype, y, d.k, p.M, row);
       if (st != FDNN_OK) return st;

@@ -452,7 +452,18 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (p.act) a = apply_activation(a, p.act);
           v[j] = a;
         }
-        if (row_ok) {
+        if (row_ok && p.out_f32) {
+          // 16-bit operands, float32 result: the finished values are stored as they are
+          float* yf = static_cast<float*>(p.y);
+          if (p.vec_store && col0 + 32 <= p.Kout) {
+            store32_contig<float>(yf + y_off + col0, v);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.Kout) yf[y_off + (long long)(col0 + j) * p.y_sk] = v[j];
+            }
+          }
+        } else if (row_ok) {
           if (p.vec_store && col0 + 32 <= p.Kout) {
             store32_contig<T>(y + y_off + col0, v);
           } else {

@@ -31,6 +31,7 @@ struct IgemmParams {
   int act;               // FDNN_ACT_* applied after scale, bias and residual
   int vec_store;         // 1: y is channel-contiguous and 16-byte aligned per pixel
   int tma_store;         // 1: y is dense NHWC; the epilogue writes it through the tmY tensor map
+  int out_f32;           // 1: y is float32 although the operands are 16-bit (per-thread store path only)
   // Low-channel mode (C <= 4): one GEMM row is a quad of 4 output pixels of one
   // image row, its reduction operand a 16-pixel window of the repacked input;
   // a tile is `ohs` output rows x OW/4 quads and never crosses an image.

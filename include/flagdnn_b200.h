@@ -55,6 +55,11 @@ typedef enum fdnn_status {
  * Off by default: measured on B200, the layers it applies to are bound by L2 -> SM operand traffic, which the
  * split does not change, and it came out 1-3 % slower than whole tiles on the 3x3 256-channel layer. */
 #define FDNN_ALGO_FLAG_STREAM_K 0x100
+/* OR-ed into fdnn_conv_desc.algo: x, w, bias and scale are f16 / bf16 as desc->dtype says, but y is float32
+ * (y_strides in float elements): the fp32 accumulators are stored after scale, bias and activation without the
+ * rounding to 16 bits.  What the reference's mm offers as out_dtype=float32 (src/flag_dnn/ops/mm.py:336).
+ * Tensor-core path on one CTA per tile only; no residual. */
+#define FDNN_ALGO_FLAG_OUT_F32 0x200
 
 /* epilogue activation */
 #define FDNN_ACT_NONE 0

@@ -113,6 +113,27 @@ def test_query_routes_unsupported_geometry_to_direct(native_lib):
         nat.check(nat.FDNN_NOT_SUPPORTED)
 
 
+def test_query_float32_output_flag(native_lib):
+    """FDNN_ALGO_FLAG_OUT_F32: 16-bit operands only, single-CTA tensor-core kernel, no pixel groups / quads."""
+    plan, wide = nat.ConvPlan(), nat.ConvPlan()
+    d = _desc(n=1, c=1024, h=1, w=4096, k=256, r=1, s=1, pad=0)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    d.algo = nat.ALGO_FLAG_OUT_F32
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(wide)) == nat.FDNN_OK
+    assert wide.algo == nat.ALGO_IGEMM and wide.low_channel == 0 and wide.pixel_group <= 1
+    assert wide.bytes == plan.bytes + 2.0 * 4096 * 256          # y costs four bytes an element
+    d = _desc(algo=nat.ALGO_FLAG_OUT_F32, c=3, h=32, w=32, k=64, r=7, s=7, stride=2, pad=3)   # a stem: no quads
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(wide)) == nat.FDNN_OK
+    assert wide.algo == nat.ALGO_IGEMM and wide.low_channel == 0
+    d = _desc(dtype=nat.F32, algo=nat.ALGO_FLAG_OUT_F32)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(wide)) == nat.FDNN_BAD_PARAM
+    for algo in (nat.ALGO_DIRECT, nat.ALGO_IGEMM_PAIR):
+        d = _desc(algo=algo | nat.ALGO_FLAG_OUT_F32)
+        assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(wide)) == nat.FDNN_NOT_SUPPORTED
+    d = _desc(groups=2, algo=nat.ALGO_FLAG_OUT_F32)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(wide)) == nat.FDNN_NOT_SUPPORTED
+
+
 def test_query_unaligned_pointer_forces_repack(native_lib):
     plan = nat.ConvPlan()
     d = _desc()

@@ -180,6 +180,32 @@ def test_mm_matches_torch_cpu(fd, case, dtype_name, use_out):
     assert torch.equal(a, a0) and torch.equal(b, b0)
 
 
+@pytest.mark.parametrize("use_out", [False, True])
+@pytest.mark.parametrize("dtype_name", ["bfloat16", "float16"])
+@pytest.mark.parametrize("case", MM_CASES, ids=["x".join(map(str, c)) for c in MM_CASES])
+def test_mm_float32_result_from_16_bit_operands(fd, case, dtype_name, use_out):
+    """out_dtype=torch.float32 with fp16 / bf16 operands (src/flag_dnn/ops/mm.py:123-131): the fp32 accumulators
+    are stored unrounded, so the result is within fp32 summation-order error of an fp32 product of the same
+    (already rounded) operands, far inside what a 16-bit output could hold."""
+    m, k, n = case
+    dtype = getattr(torch, dtype_name)
+    a = torch.empty(m, k).uniform_(-1, 1, generator=torch.Generator().manual_seed(7)).to(dtype).cuda()
+    b = torch.empty(k, n).uniform_(-1, 1, generator=torch.Generator().manual_seed(8)).to(dtype).cuda()
+    ref = torch.mm(a.cpu().double(), b.cpu().double())
+    if use_out:
+        buf = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        got = fd.mm(a, b, torch.float32, out=buf)
+        assert got.data_ptr() == buf.data_ptr()
+    else:
+        got = fd.mm(a, b, out_dtype=torch.float32)
+    assert got.shape == (m, n) and got.dtype == torch.float32
+    torch.testing.assert_close(got.cpu().double(), ref, rtol=1e-5, atol=2e-6 * max(1.0, k ** 0.5))
+    if m * n * k:
+        # and it is not the 16-bit result widened: a rounded output differs from this one
+        narrow = fd.mm(a, b).float()
+        assert (narrow - got).abs().max().item() > 0 or k == 1
+
+
 def test_mm_strided_operands_and_checks(fd):
     a = torch.randn(64, 96, device="cuda")[:, ::2]            # non-contiguous left operand
     b = torch.randn(40, 48, device="cuda").t()                # transposed right operand: [48, 40]
@@ -196,9 +222,9 @@ def test_mm_strided_operands_and_checks(fd):
         fd.mm(torch.randn(2, 3, device="cuda"), torch.randn(3, 5, device="cuda", dtype=torch.float16))
     with pytest.raises(NotImplementedError):
         fd.mm(torch.randn(2, 3, device="cuda", dtype=torch.complex64), torch.randn(3, 5, device="cuda", dtype=torch.complex64))
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(RuntimeError, match="Expected out tensor to have dtype torch.float32"):
         fd.mm(torch.randn(2, 3, device="cuda", dtype=torch.float16), torch.randn(3, 5, device="cuda", dtype=torch.float16),
-              out_dtype=torch.float32)
+              out_dtype=torch.float32, out=torch.empty(2, 5, device="cuda", dtype=torch.float16))
     with pytest.raises(RuntimeError, match="out_dtype must be"):
         fd.mm(torch.randn(2, 3, device="cuda"), torch.randn(3, 5, device="cuda"), out_dtype=torch.float16)
 

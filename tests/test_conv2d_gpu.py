@@ -739,6 +739,15 @@ DEPTHWISE = [
     (2, 16, 17, 19, 3, 3, 1, 1, (1, 2), "float32", False),   # dilation along W on planes
     (2, 12, 14, 14, 3, 3, 1, 1, 1, "bfloat16", True),        # 12 channels: not whole 16-byte vectors -> plane kernel
     (1, 8, 9, 11, 7, 7, 1, 3, 1, "float16", False),
+    (2, 16, 32, 32, 3, 3, 2, 1, 1, "bfloat16", False),       # NCHW rows as 16-byte vectors, stride 2
+    (2, 16, 24, 24, 5, 5, 2, 2, 1, "float16", False),        # output rows of 12: 8-byte vectors
+    (2, 8, 16, 16, 3, 3, 1, 1, 1, "float32", False),         # fp32 rows, vectors of 4
+    (2, 8, 10, 6, 3, 3, 1, 1, 1, "float32", False),          # rows of 24 bytes: fp32 vectors of 2
+    (3, 24, 28, 28, 3, 3, 1, 1, 1, "bfloat16", False),       # rows of 56 bytes: 8-byte vectors
+    (1, 4096, 9, 9, 3, 3, 1, 1, 1, "bfloat16", True),        # more channels than one block's shared memory holds
+    (32, 64, 56, 56, 3, 3, 1, 1, 1, "bfloat16", True),       # more units than the resident blocks take in one round
+    (2, 1024, 14, 14, 3, 3, 1, 1, 1, "float16", True),
+    (2, 32, 30, 30, 5, 5, 2, 2, 1, "bfloat16", True),
 ]
 
 

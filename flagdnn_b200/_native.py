@@ -43,6 +43,7 @@ EXPORTED_SYMBOLS = (
     "fdnn_device_status",
     "fdnn_debug_set_profile_buffer",
     "fdnn_debug_set_wait_limit",
+    "fdnn_debug_tensor_map_counters",
     "fdnn_conv2d_fwd_static_scratch",
     "fdnn_static_scratch_bytes",
     "fdnn_static_scratch_last_error",
@@ -148,6 +149,8 @@ def load() -> ctypes.CDLL:
     lib.fdnn_debug_set_profile_buffer.argtypes = [vp]
     lib.fdnn_debug_set_wait_limit.restype = i32
     lib.fdnn_debug_set_wait_limit.argtypes = [i64, i32]
+    lib.fdnn_debug_tensor_map_counters.restype = i32
+    lib.fdnn_debug_tensor_map_counters.argtypes = [ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
     lib.fdnn_device_status.restype = i32
     lib.fdnn_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     _lib = lib

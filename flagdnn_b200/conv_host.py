@@ -66,6 +66,27 @@ def _streamk_scratch(device: torch.device, stream: int, nbytes: int) -> torch.Te
     return buf
 
 
+_WORKSPACE: "dict[tuple, torch.Tensor]" = {}
+_WORKSPACE_KEEP_BYTES = 256 << 20
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    """Scratch for one call's relayouts.  Calls on one stream run in order, so they share one buffer per
+    (device, stream) that grows to the largest request up to 256 MiB; larger requests, and requests made while
+    the stream is being captured into a graph, get a buffer of their own from the caching allocator."""
+    if torch.cuda.is_current_stream_capturing():
+        # the graph keeps the address: the buffer must come from the graph's own memory pool
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    key = (device.index, stream)
+    buf = _WORKSPACE.get(key)
+    if buf is not None and buf.numel() >= nbytes:
+        return buf
+    buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    if nbytes <= _WORKSPACE_KEEP_BYTES:
+        _WORKSPACE[key] = buf
+    return buf
+
+
 def set_algo(algo: Union[int, str]) -> int:
     """Force the kernel family for subsequent calls: "auto", "direct", "igemm"
     (one CTA per tile) or "pair" (CTA pairs).
@@ -140,6 +161,15 @@ def _check_conv2d_inputs(input, weight, bias, stride, padding, dilation, groups)
         raise RuntimeError("weight.shape[1] must match input_channels // groups")
     if bias is not None and (bias.dim() != 1 or bias.numel() != c_out):
         raise RuntimeError(f"bias shape mismatch, expected ({c_out},)")
+
+
+def _current_stream(device: torch.device) -> int:
+    """The raw handle of torch's current stream on `device` (the accessor the stream object is built from;
+    an order of magnitude cheaper than building the object on every call)."""
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is not None and device.index is not None:
+        return raw(device.index)
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def _ptr(t: torch.Tensor) -> int:
@@ -269,7 +299,7 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         # a float32 result from 16-bit operands has one kernel family (the request for another is dropped)
         algo = nat.ALGO_FLAG_OUT_F32 if out_f32 else (_FORCED_ALGO | (nat.ALGO_FLAG_STREAM_K if _STREAM_K else 0))
         d, plan = _plan_for(input, weight, out, stride, padding4, dilation, groups, algo)
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = _current_stream(input.device)
         packed_ptr = None
         packed = None
         if plan.algo != nat.ALGO_DIRECT and plan.w_packed:
@@ -278,7 +308,7 @@ def _run(input, weight, bias, scale, stride, padding4, dilation, groups, activat
         ws_ptr = None
         ws = None
         if plan.workspace_bytes > 0:
-            ws = torch.empty(plan.workspace_bytes, dtype=torch.uint8, device=input.device)
+            ws = _workspace(input.device, stream, plan.workspace_bytes)
             ws_ptr = ws.data_ptr()
         sk_ptr, sk_bytes = None, 0
         if plan.stream_k:

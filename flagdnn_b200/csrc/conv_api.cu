@@ -467,6 +467,86 @@ void load_driver_entry_points() {
   g_driver_ok = ok;
 }
 
+// Encoded tensor maps are remembered per thread, keyed by every argument of the encode call: a layer that is run
+// again on the same buffers (the steady state of an eager loop or of a compiled plan) costs a table lookup
+// instead of a driver call per map.  128 direct-mapped entries; a collision simply re-encodes.
+struct MapKey {
+  uint64_t w[30];
+};
+struct MapSlot {
+  MapKey key;
+  alignas(64) CUtensorMap map;
+  bool used;
+};
+constexpr int kMapSlots = 128;
+std::atomic<long long> g_map_hits{0}, g_map_misses{0};
+
+inline uint64_t map_key_hash(const MapKey& k) {
+  uint64_t h = 0x9e3779b97f4a7c15ull;
+  for (uint64_t v : k.w) {
+    h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+    h *= 0xff51afd7ed558ccdull;
+  }
+  return h ^ (h >> 32);
+}
+
+template <typename Encode>
+CUresult memo_lookup(CUtensorMap* tm, const MapKey& key, Encode&& encode) {
+  thread_local MapSlot slots[kMapSlots];
+  MapSlot& slot = slots[map_key_hash(key) % kMapSlots];
+  if (slot.used && std::memcmp(&slot.key, &key, sizeof key) == 0) {
+    *tm = slot.map;
+    g_map_hits.fetch_add(1, std::memory_order_relaxed);
+    return CUDA_SUCCESS;
+  }
+  g_map_misses.fetch_add(1, std::memory_order_relaxed);
+  const CUresult r = encode();
+  if (r == CUDA_SUCCESS) {
+    slot.key = key;
+    slot.map = *tm;
+    slot.used = true;
+  }
+  return r;
+}
+
+CUresult memo_encode_tiled(CUtensorMap* tm, CUtensorMapDataType dt, cuuint32_t rank, void* base, const cuuint64_t* dims,
+                           const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* estr,
+                           CUtensorMapInterleave il, CUtensorMapSwizzle sw, CUtensorMapL2promotion l2,
+                           CUtensorMapFloatOOBfill oob) {
+  MapKey k{};
+  int n = 0;
+  k.w[n++] = 1;
+  k.w[n++] = uint64_t(dt) | uint64_t(rank) << 8 | uint64_t(il) << 16 | uint64_t(sw) << 24 | uint64_t(l2) << 32 |
+             uint64_t(oob) << 40;
+  k.w[n++] = reinterpret_cast<uint64_t>(base);
+  for (cuuint32_t i = 0; i < rank && i < 5; ++i) k.w[n++] = dims[i];
+  for (cuuint32_t i = 0; i + 1 < rank && i < 4; ++i) k.w[n++] = strides[i];
+  for (cuuint32_t i = 0; i < rank && i < 5; ++i) k.w[n++] = uint64_t(box[i]) | uint64_t(estr[i]) << 32;
+  return memo_lookup(tm, k, [&]() { return g_encode_tiled(tm, dt, rank, base, dims, strides, box, estr, il, sw, l2, oob); });
+}
+
+CUresult memo_encode_im2col(CUtensorMap* tm, CUtensorMapDataType dt, cuuint32_t rank, void* base,
+                            const cuuint64_t* dims, const cuuint64_t* strides, const int* lower, const int* upper,
+                            cuuint32_t channels_per_pixel, cuuint32_t pixels_per_column, const cuuint32_t* estr,
+                            CUtensorMapInterleave il, CUtensorMapSwizzle sw, CUtensorMapL2promotion l2,
+                            CUtensorMapFloatOOBfill oob) {
+  MapKey k{};
+  int n = 0;
+  k.w[n++] = 2;
+  k.w[n++] = uint64_t(dt) | uint64_t(rank) << 8 | uint64_t(il) << 16 | uint64_t(sw) << 24 | uint64_t(l2) << 32 |
+             uint64_t(oob) << 40;
+  k.w[n++] = reinterpret_cast<uint64_t>(base);
+  k.w[n++] = uint64_t(channels_per_pixel) | uint64_t(pixels_per_column) << 32;
+  for (cuuint32_t i = 0; i < rank && i < 5; ++i) k.w[n++] = dims[i];
+  for (cuuint32_t i = 0; i + 1 < rank && i < 4; ++i) k.w[n++] = strides[i];
+  for (cuuint32_t i = 0; i + 2 < rank && i < 3; ++i) k.w[n++] = uint64_t(uint32_t(lower[i])) | uint64_t(uint32_t(upper[i])) << 32;
+  for (cuuint32_t i = 0; i < rank && i < 5; ++i) k.w[n++] = estr[i];
+  return memo_lookup(tm, k, [&]() {
+    return g_encode_im2col(tm, dt, rank, base, dims, strides, lower, upper, channels_per_pixel, pixels_per_column, estr,
+                           il, sw, l2, oob);
+  });
+}
+
 CUtensorMapDataType tm_dtype(int dtype) {
   switch (dtype) {
     case FDNN_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -487,7 +567,7 @@ int encode_activation_map(CUtensorMap* tm, int dtype, const void* base, int C, i
   cuuint32_t trav[4] = {1, cuuint32_t(d->stride_w), cuuint32_t(d->stride_h), 1};
   const cuuint32_t channels_per_pixel = 128 / es;
   const cuuint32_t pixels_per_column = 128;
-  CUresult r = g_encode_im2col(tm, tm_dtype(dtype), 4, const_cast<void*>(base), dims, strides, lower,
+  CUresult r = memo_encode_im2col(tm, tm_dtype(dtype), 4, const_cast<void*>(base), dims, strides, lower,
                                upper, channels_per_pixel, pixels_per_column, trav,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -518,7 +598,7 @@ int encode_filter_map(CUtensorMap* tm, int dtype, const void* base, int C, int t
   cuuint64_t strides[2] = {cuuint64_t(s_tap) * es, cuuint64_t(s_k) * es};
   cuuint32_t box[3] = {cuuint32_t(128 / es), 1, cuuint32_t(tile_n)};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = memo_encode_tiled(tm, tm_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -538,7 +618,7 @@ int encode_output_map(CUtensorMap* tm, int dtype, void* base, int K, long long M
   cuuint64_t strides[2] = {cuuint64_t(row_stride) * es, cuuint64_t(row_stride) * es * cuuint64_t(M)};
   cuuint32_t box[3] = {cuuint32_t(128 / es), 32, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), 3, base, dims, strides, box, estr,
+  CUresult r = memo_encode_tiled(tm, tm_dtype(dtype), 3, base, dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -558,7 +638,7 @@ int encode_residual_map(CUtensorMap* tm, int dtype, const void* base, int K, lon
   cuuint64_t strides[2] = {cuuint64_t(row_stride) * es, cuuint64_t(row_stride) * es * cuuint64_t(M)};
   cuuint32_t box[3] = {cuuint32_t(box_cols), 128, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = memo_encode_tiled(tm, tm_dtype(dtype), 3, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -615,7 +695,7 @@ namespace {
 
 int encode_tiled(CUtensorMap* tm, int dtype, const void* base, int rank, const cuuint64_t* dims,
                  const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* estr, const char* what) {
-  CUresult r = g_encode_tiled(tm, tm_dtype(dtype), rank, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = memo_encode_tiled(tm, tm_dtype(dtype), rank, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -1141,6 +1221,12 @@ int fdnn_debug_set_wait_limit(int64_t wait_limit_cycles, int skip_copies) {
   if (wait_limit_cycles < 0) return fail(FDNN_BAD_PARAM, "wait limit must not be negative");
   g_wait_limit.store(wait_limit_cycles, std::memory_order_relaxed);
   g_skip_copies.store(skip_copies != 0 ? 1 : 0, std::memory_order_relaxed);
+  return FDNN_OK;
+}
+
+int fdnn_debug_tensor_map_counters(int64_t* reused, int64_t* encoded) {
+  if (reused != nullptr) *reused = g_map_hits.load(std::memory_order_relaxed);
+  if (encoded != nullptr) *encoded = g_map_misses.load(std::memory_order_relaxed);
   return FDNN_OK;
 }
 

@@ -95,9 +95,11 @@ __device__ __forceinline__ Words<VB> load_words(const void* ptr) {
   if constexpr (VB == 16) {
     const uint4 q = __ldg(static_cast<const uint4*>(ptr));
     r.w[0] = q.x; r.w[1] = q.y; r.w[2] = q.z; r.w[3] = q.w;
-  } else {
+  } else if constexpr (VB == 8) {
     const uint2 q = __ldg(static_cast<const uint2*>(ptr));
     r.w[0] = q.x; r.w[1] = q.y;
+  } else {
+    r.w[0] = __ldg(static_cast<const uint32_t*>(ptr));
   }
   return r;
 }
@@ -105,8 +107,10 @@ template <int VB>
 __device__ __forceinline__ void store_words_streaming(void* ptr, const Words<VB>& r) {
   if constexpr (VB == 16) {
     __stcs(static_cast<uint4*>(ptr), make_uint4(r.w[0], r.w[1], r.w[2], r.w[3]));
-  } else {
+  } else if constexpr (VB == 8) {
     __stcs(static_cast<uint2*>(ptr), make_uint2(r.w[0], r.w[1]));
+  } else {
+    __stcs(static_cast<uint32_t*>(ptr), r.w[0]);
   }
 }
 // Two fp32 values of neighbouring channels in one 64-bit register, the operand form of fma.rn.f32x2 (two
@@ -618,6 +622,9 @@ cudaError_t go_static(const DirectParams& p, int kind, cudaStream_t stream) {
   if constexpr (KR != 0) {
     if (kind == 3) return launch_rowvec<T, KR, KS, KSTRIDE, 16>(p, stream);
     if (kind == 4) return launch_rowvec<T, KR, KS, KSTRIDE, 8>(p, stream);
+    if constexpr (sizeof(T) == 2) {
+      if (kind == 5) return launch_rowvec<T, KR, KS, KSTRIDE, 4>(p, stream);
+    }
   }
   if (channels_last) {
     constexpr int VB = 16;
@@ -644,7 +651,7 @@ cudaError_t go(const DirectParams& p, int channels_last, cudaStream_t stream) { 
 }  // namespace
 
 // 0: not a case for these kernels (the caller uses the direct kernel); 1: channels-last kernel; 2: plane kernel;
-// 3 / 4: row-vector kernel (NCHW) on 16- / 8-byte vectors.
+// 3 / 4 / 5: row-vector kernel (NCHW) on 16- / 8- / 4-byte vectors.
 int depthwise_kind(int dtype, const DirectParams& p) {
   if (p.groups != p.C || p.K != p.C || p.C < 1) return 0;
   if (dtype != FDNN_F16 && dtype != FDNN_BF16 && dtype != FDNN_F32) return 0;
@@ -660,19 +667,19 @@ int depthwise_kind(int dtype, const DirectParams& p) {
                   p.C > 1 && (long long)p.N * p.OH * p.OW < 2147483647LL && p.C / v < 65536LL * 8;
   if (cl) return 1;
   // W-contiguous planes with vector-aligned rows and "same" padding of an unrolled filter: the row-vector kernel
-  // on 16-byte vectors, or on 8-byte ones where only those are aligned (rows of 28 or 14 16-bit values)
+  // on the widest vectors the rows are aligned for (16 bytes; 8 for rows of 28 16-bit values; 4 for rows of 14)
   const bool unrolled = p.dil_h == 1 && p.dil_w == 1 && p.stride_h == p.stride_w && p.R == p.S &&
                         (p.R == 3 || p.R == 5) && (p.stride_w == 1 || p.stride_w == 2);
   if (unrolled && p.pad_left == p.S / 2 && p.x_s[3] == 1 && p.y_s[3] == 1) {
-    for (int vb = 16; vb >= 8; vb /= 2) {
+    for (int vb = 16; vb >= 4; vb /= 2) {
       const int vv = vb / es;
-      if (vv < 2 && es == 2) break;
+      if (vv < 2) break;
       const bool al = ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y) |
                         reinterpret_cast<uintptr_t>(p.residual)) & uintptr_t(vb - 1)) == 0;
       auto m = [vv](long long extent, long long stride) { return extent <= 1 || stride % vv == 0; };
       if (al && m(p.N, p.x_s[0]) && m(p.C, p.x_s[1]) && m(p.H, p.x_s[2]) && m(p.N, p.y_s[0]) && m(p.C, p.y_s[1]) &&
           m(p.OH, p.y_s[2]) && p.W >= vv && (long long)p.N * p.C * p.OH * ((p.OW + vv - 1) / vv) < 2147483647LL * 128)
-        return vb == 16 ? 3 : 4;
+        return vb == 16 ? 3 : (vb == 8 ? 4 : 5);
     }
   }
   if ((long long)p.N * p.C < 2147483647LL && p.R * p.S <= kDwMaxSmemFloats) return 2;

@@ -118,7 +118,8 @@ struct DirectParams {
 cudaError_t launch_direct(int dtype, const DirectParams& p, cudaStream_t stream);
 // Depthwise layers (groups == C == K) in f16 / bf16 / f32 (conv_depthwise.cu): `depthwise_kind` answers 0 when
 // the problem is not one of its cases (the direct kernel then runs), 1 for the channels-last kernel (16 bytes
-// of channels per thread), 2 for the kernel that gives every (image, channel) plane a block.
+// of channels per thread), 2 for the kernel that gives every (image, channel) plane a block, 3 / 4 / 5 for the
+// NCHW kernel that reads rows as 16- / 8- / 4-byte vectors.
 int depthwise_kind(int dtype, const DirectParams& p);
 cudaError_t launch_depthwise(int dtype, const DirectParams& p, int kind, cudaStream_t stream);
 

@@ -438,14 +438,31 @@ def execute_plan(plan: ExecutionPlan, inputs: tuple, workspace: Optional[torch.T
     graph_obj = plan.graph
     if len(inputs) != len(graph_obj.inputs):
         raise RuntimeError(f"graph expects {len(graph_obj.inputs)} inputs, got {len(inputs)}")
-    for index, (spec, tensor) in enumerate(zip(plan.input_specs, inputs)):
-        _validate_input(spec, tensor, index)
+    checks = getattr(plan, "_input_checks", None)
+    if checks is None:
+        # what _validate_input compares, precomputed once per plan
+        checks = [(tuple(spec.shape), torch_dtype(spec.dtype), None if spec.stride is None else tuple(spec.stride),
+                   None if spec.device is None else torch.device(spec.device).type) for spec in plan.input_specs]
+        plan._input_checks = checks
+    for index, (tensor, (shape, dtype, stride, dev_type)) in enumerate(zip(inputs, checks)):
+        if not (isinstance(tensor, torch.Tensor) and tensor.shape == shape and tensor.dtype == dtype
+                and (stride is None or tensor.stride() == stride)
+                and (dev_type is None or tensor.device.type == dev_type)):
+            _validate_input(plan.input_specs[index], tensor, index)   # raises with the precise message
     if len(plan.steps) == 1:  # single fused node: skip the environment bookkeeping
-        step = plan.steps[0]
-        if all(v in graph_obj.inputs for v in step.inputs) and graph_obj.outputs == step.outputs:
-            args = [inputs[graph_obj.inputs.index(v)] for v in step.inputs]
-            out = get_op_schema(step.op_type).run(args, step.attrs)
-            return _rebuild_outputs(plan.debug_info.get("output_structure") or ("leaf",), [out])
+        single = getattr(plan, "_single_step", None)
+        if single is None:
+            step = plan.steps[0]
+            if all(v in graph_obj.inputs for v in step.inputs) and graph_obj.outputs == step.outputs:
+                single = (get_op_schema(step.op_type).run, [graph_obj.inputs.index(v) for v in step.inputs],
+                          step.attrs, plan.debug_info.get("output_structure") or ("leaf",))
+            else:
+                single = False
+            plan._single_step = single
+        if single:
+            run, arg_index, attrs, structure = single
+            out = run([inputs[i] for i in arg_index], attrs)
+            return out if structure == ("leaf",) else _rebuild_outputs(structure, [out])
     env: dict = dict(zip(graph_obj.inputs, inputs))
     for value in graph_obj.values.values():
         if value.is_constant:

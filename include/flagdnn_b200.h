@@ -275,6 +275,14 @@ int fdnn_debug_set_profile_buffer(void* device_buffer_16_int64);
  * FDNN_DEVICE_TIMEOUT once.  Process-wide; not for production use. */
 int fdnn_debug_set_wait_limit(int64_t wait_limit_cycles, int skip_copies);
 
+/* Encoded tensor maps are remembered per calling thread, keyed by every
+ * argument of the encode call, so a layer run again on the same buffers does
+ * not go back to the driver (the reference keeps its tuned launch
+ * configurations per shape in a similar table, src/flag_dnn/utils/libentry.py:499-579).
+ * This reports, process-wide since load, how many maps were taken from the
+ * table (`reused`) and how many had to be encoded (`encoded`); either may be NULL. */
+int fdnn_debug_tensor_map_counters(int64_t* reused, int64_t* encoded);
+
 #ifdef __cplusplus
 }
 #endif

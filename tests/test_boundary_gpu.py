@@ -189,3 +189,42 @@ def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(native_lib
         assert fd.device_status() == 0
     finally:
         fd.set_algo("auto")
+
+
+def _map_counters(lib):
+    reused, encoded = ctypes.c_int64(0), ctypes.c_int64(0)
+    assert lib.fdnn_debug_tensor_map_counters(ctypes.byref(reused), ctypes.byref(encoded)) == nat.FDNN_OK
+    return reused.value, encoded.value
+
+
+@pytest.mark.parametrize("shape", [((8, 64, 28, 28), (128, 64, 3, 3), 1, 1), ((4, 3, 64, 64), (32, 3, 7, 7), 2, 3),
+                                   ((16, 256, 14, 14), (256, 256, 3, 3), 1, 1)],
+                         ids=["generic", "stem", "pairs"])
+def test_a_repeated_layer_encodes_no_tensor_map(native_lib, shape):
+    """The steady state of an eager loop: the same layer on the same buffers takes every tensor map from the
+    library's table (no driver call), a new output buffer encodes only the maps that name it, and the results
+    stay those of the first call."""
+    import flagdnn_b200 as fd
+
+    xs, ws, stride, pad = shape
+    x = _nhwc(_rand(xs, 21).to(BF).cuda())
+    w = _nhwc(_rand(ws, 22, std=(ws[1] * ws[2] * ws[3]) ** -0.5).to(BF).cuda())
+    b = _rand((ws[0],), 23, std=0.1).to(BF).cuda()
+    out = fd.fused_conv2d_bias_relu(x, w, b, stride=stride, padding=pad)
+    first = out.clone()
+    buf = torch.empty_like(out)
+    fd.conv2d_bias_act(x, w, b, stride=stride, padding=pad, relu=True, out=buf)      # maps over `buf` are new
+    r0, e0 = _map_counters(native_lib)
+    for _ in range(3):
+        fd.conv2d_bias_act(x, w, b, stride=stride, padding=pad, relu=True, out=buf)
+    r1, e1 = _map_counters(native_lib)
+    assert e1 == e0, "a repeated call went back to the driver for a tensor map"
+    assert r1 > r0
+    assert torch.equal(buf, first)
+    other = torch.empty_like(out)
+    fd.conv2d_bias_act(x, w, b, stride=stride, padding=pad, relu=True, out=other)
+    r2, e2 = _map_counters(native_lib)
+    assert 0 < e2 - e1 <= 3, "only the maps over the new output are encoded"
+    assert torch.equal(other, first)
+    ref = oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, 1, relu=True)
+    torch.testing.assert_close(first.float().cpu(), ref, rtol=1e-2, atol=1e-2)

@@ -747,6 +747,8 @@ DEPTHWISE = [
     (1, 4096, 9, 9, 3, 3, 1, 1, 1, "bfloat16", True),        # more channels than one block's shared memory holds
     (32, 64, 56, 56, 3, 3, 1, 1, 1, "bfloat16", True),       # more units than the resident blocks take in one round
     (2, 1024, 14, 14, 3, 3, 1, 1, 1, "float16", True),
+    (2, 64, 14, 14, 3, 3, 1, 1, 1, "bfloat16", False),        # rows of 28 bytes: 4-byte vectors
+    (2, 32, 14, 14, 5, 5, 2, 2, 1, "float16", False),
     (2, 32, 30, 30, 5, 5, 2, 2, 1, "bfloat16", True),
 ]
 

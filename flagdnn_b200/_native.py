@@ -26,6 +26,10 @@ ACT_NONE, ACT_RELU, ACT_GELU, ACT_GELU_TANH = 0, 1, 2, 3
 STREAMK_FLAG_BYTES = 8192
 ALGO_FLAG_STREAM_K = 0x100
 ALGO_FLAG_OUT_F32 = 0x200
+ALGO_FLAG_TILE_N_64 = 0x400
+ALGO_FLAG_TILE_N_128 = 0x800
+ALGO_FLAG_TILE_N_256 = 0xC00
+ALGO_FLAG_NO_PIXEL_GROUP = 0x1000
 
 EXPORTED_SYMBOLS = (
     "fdnn_abi_version",

@@ -102,6 +102,14 @@ bool igemm_geometry_ok(const fdnn_conv_desc* d) {
   return true;
 }
 
+// Tile width asked for through FDNN_ALGO_FLAG_TILE_N_* (0: none; fp32 tiles stop at 128 columns).
+int forced_tile_n(const fdnn_conv_desc* d) {
+  const int code = (d->algo & FDNN_ALGO_FLAG_TILE_N_MASK) >> 10;
+  if (code == 0) return 0;
+  const int bn = 32 << code;
+  return (d->dtype == FDNN_F32 && bn > 128) ? 128 : bn;
+}
+
 int choose_tile_n(int dtype, int m_tiles, int kout, int sms) {
   const int max_bn = (dtype == FDNN_F32) ? 128 : 256;
   int best = 64;
@@ -327,6 +335,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     plan->tile_m = 128;
     plan->tile_k = 64;
     plan->tile_n = choose_tile_n(d->dtype, m_tiles_lc, n_gemm, sms_lc);
+    if (forced_tile_n(d) != 0) plan->tile_n = forced_tile_n(d);
     plan->stages = igemm_stages(d->dtype, plan->tile_n);
     plan->smem_bytes = igemm_smem_bytes(d->dtype, plan->tile_n);
     const long long tiles_lc = (long long)m_tiles_lc * ((n_gemm + plan->tile_n - 1) / plan->tile_n);
@@ -359,7 +368,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
     return FDNN_OK;
   }
 
-  if (allow_group && !out_f32) {
+  if (allow_group && !out_f32 && (d->algo & FDNN_ALGO_FLAG_NO_PIXEL_GROUP) == 0) {
     const int q = choose_pixel_group(d, oh, ow, y);
     if (q > 1) {
       fdnn_conv_desc v = grouped_desc(d, q, oh, ow);
@@ -407,6 +416,7 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   const int m_tiles = int(((long long)m + 127) / 128);
   const int sms = sm_count();
   plan->tile_n = choose_tile_n(d->dtype, m_tiles, d->k, sms);
+  if (forced_tile_n(d) != 0) plan->tile_n = forced_tile_n(d);
   plan->stages = igemm_stages(d->dtype, plan->tile_n);
   plan->smem_bytes = igemm_smem_bytes(d->dtype, plan->tile_n);
   const long long tiles = (long long)m_tiles * ((d->k + plan->tile_n - 1) / plan->tile_n);

@@ -60,6 +60,16 @@ typedef enum fdnn_status {
  * rounding to 16 bits.  What the reference's mm offers as out_dtype=float32 (src/flag_dnn/ops/mm.py:336).
  * Tensor-core path on one CTA per tile only; no residual. */
 #define FDNN_ALGO_FLAG_OUT_F32 0x200
+/* OR-ed into fdnn_conv_desc.algo, for tuning runs: fix the width of the single-CTA kernel's tiles to 64 / 128 /
+ * 256 output channels instead of the planner's choice (fp32 tiles stop at 128), and keep the planner from
+ * grouping output pixels of narrow layers.  The reference fixes its launch configurations per shape from a
+ * tuned table (src/flag_dnn/utils/libentry.py:499-579, tune_configs.yaml:1326-1466); here the planner decides,
+ * `python -m flagdnn_b200.tune` measures every alternative beside its choice through these flags. */
+#define FDNN_ALGO_FLAG_TILE_N_64 0x400
+#define FDNN_ALGO_FLAG_TILE_N_128 0x800
+#define FDNN_ALGO_FLAG_TILE_N_256 0xC00
+#define FDNN_ALGO_FLAG_TILE_N_MASK 0xC00
+#define FDNN_ALGO_FLAG_NO_PIXEL_GROUP 0x1000
 
 /* epilogue activation */
 #define FDNN_ACT_NONE 0

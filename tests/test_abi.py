@@ -134,6 +134,27 @@ def test_query_float32_output_flag(native_lib):
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(wide)) == nat.FDNN_NOT_SUPPORTED
 
 
+def test_query_tile_override_flags(native_lib):
+    """FDNN_ALGO_FLAG_TILE_N_* fix the single-CTA kernel's tile width, FDNN_ALGO_FLAG_NO_PIXEL_GROUP keeps a
+    narrow layer ungrouped; without them the planner's own choice stands."""
+    plan = nat.ConvPlan()
+    for flag, width in ((nat.ALGO_FLAG_TILE_N_64, 64), (nat.ALGO_FLAG_TILE_N_128, 128), (nat.ALGO_FLAG_TILE_N_256, 256)):
+        d = _desc(n=128, c=512, h=7, w=7, k=512, algo=nat.ALGO_IGEMM | flag)
+        assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+        assert plan.algo == nat.ALGO_IGEMM and plan.tile_n == width
+        assert plan.grid == min(148, 49 * (512 // width))
+    d = _desc(dtype=nat.F32, n=8, c=64, h=28, w=28, k=256, algo=nat.ALGO_IGEMM | nat.ALGO_FLAG_TILE_N_256)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert plan.tile_n == 128                                    # fp32 tiles stop at 128 columns
+    narrow = dict(n=256, c=64, h=56, w=56, k=64, r=3, s=3, pad=1)
+    d = _desc(**narrow)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    grouped = plan.pixel_group
+    d = _desc(algo=nat.ALGO_FLAG_NO_PIXEL_GROUP, **narrow)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert plan.pixel_group <= 1 and grouped > 1, "the 64-channel 3x3 layer is the case pixel grouping exists for"
+
+
 def test_query_unaligned_pointer_forces_repack(native_lib):
     plan = nat.ConvPlan()
     d = _desc()

@@ -434,8 +434,11 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   const int pairs_all = sms / 2;
   const bool resident = d->k <= 256 && k_steps <= igemm_pair_max_resident_steps();
   const bool sk_on = split_allowed && plan_stream_k(pair_tiles, k_steps, pairs_all, resident).worth;
-  if (algo == FDNN_ALGO_IGEMM_PAIR ||
-      (want_auto && pair_ok && d->k >= 256 && k_steps >= 16 && (pair_tiles >= pairs_all || sk_on))) {
+  // Measured on the ResNet-50 layers (python -m flagdnn_b200.tune): with at least 16 reduction steps pairs win
+  // whenever every pair has a tile; with 32 or more steps they still win with half the pairs idle (a pair reads
+  // each operand byte from L2 once for two tiles: 512 -> 512 3x3 stride 2 at 128 images 38.5 -> 32.1 us).
+  const bool pairs_fill = pair_tiles >= pairs_all || (k_steps >= 32 && 2 * pair_tiles >= pairs_all);
+  if (algo == FDNN_ALGO_IGEMM_PAIR || (want_auto && pair_ok && d->k >= 256 && k_steps >= 16 && (pairs_fill || sk_on))) {
     plan->algo = FDNN_ALGO_IGEMM_PAIR;
     plan->tile_m = 256;
     plan->tile_n = 256;

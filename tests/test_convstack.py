@@ -126,11 +126,11 @@ RANK_BATCH_PLANS = {
     ("s3b1.conv1", 128): (3, 256, 256, 0, 0, 148),
     ("s3b1.conv2", 128): (3, 256, 256, 0, 0, 148),
     ("s4b0.conv1", 128): (3, 256, 256, 0, 0, 148),
-    ("s4b0.conv2", 128): (2, 128, 256, 0, 0, 98),      # 49 row tiles x 2 column tiles: under one round of 148 SMs
+    ("s4b0.conv2", 128): (3, 256, 256, 0, 0, 100),     # 25 x 2 pair tiles on 74 pairs: long reductions still favour pairs
     ("s4b0.conv3", 128): (2, 128, 256, 0, 0, 148),
     ("s4b0.proj", 128): (3, 256, 256, 0, 0, 148),
-    ("s4b1.conv1", 128): (2, 128, 256, 0, 0, 98),
-    ("s4b1.conv2", 128): (2, 128, 256, 0, 0, 98),
+    ("s4b1.conv1", 128): (3, 256, 256, 0, 0, 100),
+    ("s4b1.conv2", 128): (3, 256, 256, 0, 0, 100),
     ("stem", 256): (3, 256, 256, 0, 2, 148),
     ("s2b0.conv2", 256): (3, 256, 256, 2, 0, 148),
     ("s3b0.conv2", 256): (3, 256, 256, 0, 0, 148),

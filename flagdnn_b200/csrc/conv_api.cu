@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <atomic>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <string>
 
@@ -482,16 +483,17 @@ void load_driver_entry_points() {
 
 // Encoded tensor maps are remembered per thread, keyed by every argument of the encode call: a layer that is run
 // again on the same buffers (the steady state of an eager loop or of a compiled plan) costs a table lookup
-// instead of a driver call per map.  128 direct-mapped entries; a collision simply re-encodes.
+// instead of a driver call per map.  512 entries, four-way set-associative; a miss simply re-encodes.
 struct MapKey {
   uint64_t w[30];
 };
 struct MapSlot {
   MapKey key;
   alignas(64) CUtensorMap map;
+  uint32_t stamp;
   bool used;
 };
-constexpr int kMapSlots = 128;
+constexpr int kMapSets = 128, kMapWays = 4;
 std::atomic<long long> g_map_hits{0}, g_map_misses{0};
 
 inline uint64_t map_key_hash(const MapKey& k) {
@@ -505,19 +507,30 @@ inline uint64_t map_key_hash(const MapKey& k) {
 
 template <typename Encode>
 CUresult memo_lookup(CUtensorMap* tm, const MapKey& key, Encode&& encode) {
-  thread_local MapSlot slots[kMapSlots];
-  MapSlot& slot = slots[map_key_hash(key) % kMapSlots];
-  if (slot.used && std::memcmp(&slot.key, &key, sizeof key) == 0) {
-    *tm = slot.map;
-    g_map_hits.fetch_add(1, std::memory_order_relaxed);
-    return CUDA_SUCCESS;
+  // sets of four entries; within a set the entry used longest ago is replaced
+  thread_local std::unique_ptr<MapSlot[]> slots;   // on the heap, made on a thread's first call
+  thread_local uint32_t tick = 0;
+  if (!slots) slots.reset(new MapSlot[kMapSets * kMapWays]());
+  MapSlot* set = &slots[(map_key_hash(key) % kMapSets) * kMapWays];
+  ++tick;
+  MapSlot* victim = &set[0];
+  for (int w = 0; w < kMapWays; ++w) {
+    MapSlot& slot = set[w];
+    if (slot.used && std::memcmp(&slot.key, &key, sizeof key) == 0) {
+      *tm = slot.map;
+      slot.stamp = tick;
+      g_map_hits.fetch_add(1, std::memory_order_relaxed);
+      return CUDA_SUCCESS;
+    }
+    if (!slot.used || (victim->used && int32_t(slot.stamp - victim->stamp) < 0)) victim = &slot;
   }
   g_map_misses.fetch_add(1, std::memory_order_relaxed);
   const CUresult r = encode();
   if (r == CUDA_SUCCESS) {
-    slot.key = key;
-    slot.map = *tm;
-    slot.used = true;
+    victim->key = key;
+    victim->map = *tm;
+    victim->used = true;
+    victim->stamp = tick;
   }
   return r;
 }
@@ -818,10 +831,10 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
   if (plan.algo == FDNN_ALGO_IGEMM_PAIR) {
     p.b_resident = (n_gemm <= 256 && d.r <= igemm_pair_max_resident_steps()) ? 1 : 0;
-    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY2, tmY, p, plan.grid, stream);
+    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY2, tmY, tmY, p, plan.grid, stream);
   } else {
     // the single-CTA kernel has no fifth 16-bit map slot: the tail map travels in the unused tmA2 slot
-    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmY2, tmB, tmB, tmY, tmY, p, plan.grid, stream);
+    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmY2, tmB, tmB, tmY, tmY, tmY, p, plan.grid, stream);
   }
   if (e != cudaSuccess) return fail_cuda("low-channel igemm launch", e);
   return FDNN_OK;
@@ -1197,9 +1210,13 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
     }
   }
   alignas(64) CUtensorMap tmR = tmY;
+  alignas(64) CUtensorMap tmRbox = tmY;
   if (residual != nullptr && p.tma_store) {
     const int box_cols = plan.algo == FDNN_ALGO_IGEMM_PAIR ? 256 : plan.tile_n;
     st = encode_residual_map(&tmR, d.dtype, residual, d.k, p.M, p.y_row, box_cols);
+    if (st != FDNN_OK) return st;
+    // the same tensor once more, boxed and swizzled like y: the epilogue warps copy from it
+    st = encode_output_map(&tmRbox, d.dtype, const_cast<void*>(residual), d.k, p.M, p.y_row);
     if (st != FDNN_OK) return st;
   }
   p.prof = g_prof_buffer;
@@ -1217,9 +1234,9 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
       p.sk_flags = static_cast<uint32_t*>(sk_scratch);
       p.sk_slots = reinterpret_cast<float*>(static_cast<char*>(sk_scratch) + FDNN_STREAMK_FLAG_BYTES);
     }
-    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY, tmR, p, plan.grid, stream);
+    e = launch_igemm_pair(d.dtype, tmA, tmB, tmY, tmY, tmR, tmRbox, p, plan.grid, stream);
   } else {
-    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, tmR, p, plan.grid, stream);
+    e = launch_igemm(d.dtype, plan.tile_n, tmA, tmA2, tmB, tmB2, tmY, tmR, tmRbox, p, plan.grid, stream);
   }
   if (e != cudaSuccess) return fail_cuda("igemm launch", e);
   return FDNN_OK;

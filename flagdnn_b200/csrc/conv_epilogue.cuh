@@ -85,25 +85,18 @@ __device__ __forceinline__ void unpack2<float>(uint32_t w, float& a, float& b) {
   b = 0.0f;
 }
 
-// One 32-row x 128-byte box of the residual tensor, fetched so that every load instruction of the warp
-// covers four whole 128-byte rows: lane L takes the 16-byte piece L % 8 of rows 4 i + L / 8, i = 0..7.
-// `box` points at the box's first row and column (element units), `row_stride` is the distance between
-// rows, `rows` how many of the 32 exist, `col0` the box's first column; columns at or beyond `kout` and
-// missing rows read zeros (kout is a multiple of the 16-byte piece).
-template <typename T>
-__device__ __forceinline__ void load_residual_box(const T* box, long long row_stride, int rows, int col0, int kout,
-                                                  int lane, uint4 (&res)[8]) {
-  constexpr int kPiece = 16 / int(sizeof(T));
-  const int piece = lane & 7;
-  const bool col_ok = col0 + piece * kPiece < kout;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int row = 4 * i + (lane >> 3);
-    res[i] = make_uint4(0u, 0u, 0u, 0u);
-    if (box != nullptr && col_ok && row < rows)
-      res[i] = __ldg(reinterpret_cast<const uint4*>(box + row * row_stride + piece * kPiece));
-  }
-}
+// How an epilogue warp gets its residual values: the TMA unit copies the 32-row x 128-byte box of the residual
+// tensor (seen exactly like y, same swizzle) straight into the staging buffer the outputs will leave from; the
+// lane then reads its own row, adds, and writes the finished row back in place.  With two staging buffers the
+// box of the next column group is on its way while this one is computed.
+struct ResidualFetch {
+  const CUtensorMap* tm;          // nullptr: no residual for this warp's rows
+  uint64_t* bars;                 // this warp's mbarriers, one per staging buffer
+  uint32_t* phases;               // bit b: the parity bars[b] completes next
+  volatile uint32_t* abort_flag;  // bounded waits, as everywhere in the kernels
+  uint32_t* status_word;
+  long long wait_limit;
+};
 
 // t_row     tensor-memory address of this warp's lane quarter, first column of the tile
 // n0        first GEMM column of the tile; kout: number of valid GEMM columns overall
@@ -116,11 +109,8 @@ __device__ __forceinline__ void load_residual_box(const T* box, long long row_st
 // store_seq          running count of this warp's staged boxes (selects the staging buffer)
 // use_scale          false when the launch has no per-channel scale (s_scale then holds ones and is not read)
 // RES                a residual tensor (same layout as y) is added before the activation
-// res_box            the residual at this warp's first row and column n0 (nullptr: no valid row);
-//                    res_stride: elements between its rows; res_rows: how many of the 32 rows exist
-//                    (the producer asked for the tile's residual values to be brought into L2 a main loop
-//                    earlier, so these loads are L2 hits; holding a prefetched box in registers across
-//                    column groups does not fit beside the accumulator columns and spills)
+// rf                 how the residual box reaches the staging buffer (see ResidualFetch; the producer asked for
+//                    the tile's residual values to be brought into L2 a main loop earlier)
 // sk_slot0 / sk_count / sk_slot_stride / sk_row / sk_pc0
 //                    reduction splitting: the accumulator holds only the tile's last reduction steps; add the
 //                    fp32 partial sums of sk_count other CTAs first (slots sk_slot0, sk_slot0 - sk_slot_stride,
@@ -131,8 +121,7 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
                                                     uint8_t* my_out, int lane, const CUtensorMap* tm_full,
                                                     const CUtensorMap* tm_tail, int st_row, int st_img,
                                                     int st_rows, uint32_t& store_seq,
-                                                    const T* res_box = nullptr, long long res_stride = 0,
-                                                    int res_rows = 0, bool use_scale = true,
+                                                    const ResidualFetch* rf = nullptr, bool use_scale = true,
                                                     const float* sk_slot0 = nullptr, int sk_count = 0,
                                                     long long sk_slot_stride = 0, int sk_row = 0, int sk_pc0 = 0) {
   constexpr int kPerStore = 128 / int(sizeof(T));  // channels per staged row: 64 (16-bit) or 32 (fp32)
@@ -148,21 +137,28 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_row, int n0, int 
     uint8_t* buf = my_out + (NBUF == 2 ? (store_seq & 1u) * (32 * 128) : 0u);  // alternates across groups AND tiles
     ++store_seq;
     if constexpr (RES) {
-      // the box goes through the staging buffer: stored as fetched (four rows per instruction), read back
-      // row per lane, with the swizzle of the output so that neither side has bank conflicts
-      uint4 res[8];
-      load_residual_box<T>(res_box != nullptr ? res_box + g * kPerStore : nullptr, res_stride, res_rows,
-                           n0 + g * kPerStore, kout, lane, res);
+      const bool have = rf != nullptr && rf->tm != nullptr && st_rows > 0;   // uniform across the warp
+      const uint32_t b = NBUF == 2 ? ((store_seq - 1u) & 1u) : 0u;
       if (lane == 0) {
-        if constexpr (NBUF == 2) bulk_wait_group_read1(); else bulk_wait_group_read0();
+        bulk_wait_group_read0();   // every staged box has left: both buffers may be written
+        if (have) {
+          if (g == 0 || NBUF == 1) {
+            mbar_arrive_expect_tx(&rf->bars[b], 32 * 128);
+            tma_load_3d(buf, rf->tm, &rf->bars[b], n0 + g * kPerStore, st_row, st_img);
+          }
+          if (NBUF == 2 && g + 1 < groups) {
+            mbar_arrive_expect_tx(&rf->bars[b ^ 1u], 32 * 128);
+            tma_load_3d(my_out + (b ^ 1u) * (32 * 128), rf->tm, &rf->bars[b ^ 1u], n0 + (g + 1) * kPerStore, st_row,
+                        st_img);
+          }
+        }
       }
       __syncwarp();
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = 4 * i + (lane >> 3);
-        *reinterpret_cast<uint4*>(buf + row * 128 + (((lane & 7) ^ (row & 7)) << 4)) = res[i];
+      if (have) {
+        mbar_wait_bounded(&rf->bars[b], (*rf->phases >> b) & 1u, rf->abort_flag, rf->status_word,
+                          kIncidentResidualWait, rf->wait_limit);
+        *rf->phases ^= 1u << b;
       }
-      __syncwarp();  // each lane reads its own row back piece by piece while it computes
     }
     tmem_ld_wait();
     for (int c = 0; c < sk_count; ++c) {  // uniform across the launch's owner tiles; zero otherwise

@@ -74,7 +74,7 @@ static_assert(128 * kRegsLeanPair + 32 * kEpiWarpsPair * kRegsEpiloguePair <= kT
               "register reallocation exceeds the launch allocation");
 constexpr int kOutBytes = kEpiWarpsPair * kOutBufs * 32 * kRowB;
 constexpr int kEpiBytes = kEpiWarpsPair * 2 * kWarpCols * int(sizeof(float));
-constexpr int kBarBytes = (2 * kMaxStages + 11) * 8 + 16;
+constexpr int kBarBytes = (2 * kMaxStages + 11 + 1 + kEpiWarpsPair) * 8 + 16;   // ... slot words, one residual-box barrier per epilogue warp
 constexpr int kSmemPair = kRingBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
 static_assert(kStages * kStageBytes <= kRingBytes, "streaming ring must fit");
 constexpr uint32_t kTmemColsPair = 512;              // two 256-column accumulators
@@ -84,7 +84,8 @@ template <typename T, bool RES>
 __global__ void __launch_bounds__(kThreadsPair, 1)
 conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmY2,
-                       const __grid_constant__ CUtensorMap tmR, const IgemmParams p) {
+                       const __grid_constant__ CUtensorMap tmR, const __grid_constant__ CUtensorMap tmRbox,
+                       const IgemmParams p) {
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : 1u;
   constexpr uint32_t kIdesc = make_idesc(kFmt, 2 * kRows, kPairN);
 
@@ -118,6 +119,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   uint64_t* conv_in = bars + 2 * kMaxStages + 10;     // the input rows of a tile have landed in conv_stage
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 11);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint64_t* res_bar = bars + 2 * kMaxStages + 12;     // [epilogue warps] a residual box has landed in the staging buffer
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -141,6 +143,9 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     mbar_init(&tmem_empty[0], 2 * kEpiWarpsPair * 32);  // epilogue threads of both CTAs
     mbar_init(&tmem_empty[1], 2 * kEpiWarpsPair * 32);
     mbar_init(drain_bar, 1);
+    if constexpr (RES) {
+      for (int i = 0; i < kEpiWarpsPair; ++i) mbar_init(&res_bar[i], 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -540,6 +545,14 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const uint32_t tempty_leader = map_to_cta(smem_u32(&tmem_empty[0]), 0);
     uint32_t tcount = 0;
     uint32_t store_seq = 0;
+    uint32_t res_phases = 0;
+    ResidualFetch rf;
+    rf.tm = g_res != nullptr ? &tmRbox : nullptr;
+    rf.bars = res_bar + (warp - kFirstEpiWarpPair);
+    rf.phases = &res_phases;
+    rf.abort_flag = abort_flag;
+    rf.status_word = p.status;
+    rf.wait_limit = p.wait_limit;
     int staged_n_tile = -1;
     long long prof_ewait = 0, prof_t0 = p.prof ? clock64() : 0;
     TileWalk walk;
@@ -566,10 +579,6 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         staged_n_tile = n_tile;
       }
       const int m_tile = 2 * m_pair + int(rank);
-      // where this warp's residual rows start: y is dense NHWC here, output pixel m is at element m * y_row
-      const long long m_first = (long long)m_tile * kRows + ew * 32;
-      const int res_rows = p.M - m_first < 32 ? int(p.M - m_first) : 32;
-      const T* res_box = (g_res != nullptr && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
       const long long et0 = p.prof ? clock64() : 0;
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
@@ -626,7 +635,7 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       const float* sk_slot0 = sk_count > 0 ? p.sk_slots + (long long)(2 * (pair_id - 1) + int(rank)) * kSkSlotFloats : nullptr;
       epilogue_store_tile<T, kWarpCols, RES, kOutBufs>(t_row, n0, p.Kout, p.act, s_scale, s_bias, my_out, lane, &tmY, &tmY2,
-                                     st_row, st_img, st_rows, store_seq, res_box, p.y_row, res_rows, g_scale != nullptr,
+                                     st_row, st_img, st_rows, store_seq, &rf, g_scale != nullptr,
                                      sk_slot0, sk_count, 2LL * kSkSlotFloats, sk_row, sk_pc0);
       if (sk_count > 0) {
         // the slots are read: lower the flags for the next launch
@@ -658,7 +667,8 @@ conv_igemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
 template <typename T>
 cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY,
-                          const CUtensorMap& tmY2, const CUtensorMap& tmR, const IgemmParams& p, int grid,
+                          const CUtensorMap& tmY2, const CUtensorMap& tmR, const CUtensorMap& tmRbox, const IgemmParams& p,
+                          int grid,
                           cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -674,8 +684,8 @@ cudaError_t launch_pair_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = launch_overlap_enabled() ? 2 : 1;
-  if (p.residual != nullptr) return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, true>, tmA, tmB, tmY, tmY2, tmR, p);
-  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, false>, tmA, tmB, tmY, tmY2, tmR, p);
+  if (p.residual != nullptr) return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, true>, tmA, tmB, tmY, tmY2, tmR, tmRbox, p);
+  return cudaLaunchKernelEx(&cfg, conv_igemm_pair_kernel<T, false>, tmA, tmB, tmY, tmY2, tmR, tmRbox, p);
 }
 
 }  // namespace
@@ -702,9 +712,10 @@ int igemm_pair_max_resident_steps() { return kMaxResidentSteps; }
 
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
                               const CUtensorMap& tmY, const CUtensorMap& tmY2, const CUtensorMap& tmR,
+                              const CUtensorMap& tmRbox,
                               const IgemmParams& p, int grid, cudaStream_t stream) {
-  if (dtype == FDNN_F16) return launch_pair_t<__half>(tmA, tmB, tmY, tmY2, tmR, p, grid, stream);
-  if (dtype == FDNN_BF16) return launch_pair_t<__nv_bfloat16>(tmA, tmB, tmY, tmY2, tmR, p, grid, stream);
+  if (dtype == FDNN_F16) return launch_pair_t<__half>(tmA, tmB, tmY, tmY2, tmR, tmRbox, p, grid, stream);
+  if (dtype == FDNN_BF16) return launch_pair_t<__nv_bfloat16>(tmA, tmB, tmY, tmY2, tmR, tmRbox, p, grid, stream);
   return cudaErrorInvalidValue;
 }
 

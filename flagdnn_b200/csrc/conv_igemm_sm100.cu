@@ -93,7 +93,7 @@ struct TileCfg {
   static constexpr int kMaxStages = 16;
   static constexpr int kRingBudget = 227 * 1024 - kOutBytes - kEpiBytes - (2 * kMaxStages + 8) * 8 - 1024;
   static constexpr int kStages = kRingBudget / kStageBytes < kMaxStages ? kRingBudget / kStageBytes : kMaxStages;
-  static constexpr int kBarBytes = (2 * kStages + 4 + 1) * 8 + 16;
+  static constexpr int kBarBytes = (2 * kStages + 4 + 1 + 1 + 16) * 8 + 16;   // ring, accumulators, drain, slot words, residual boxes
   static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + kEpiBytes + kBarBytes + 1024;
   static_assert(kStages >= 2, "pipeline needs at least two stages");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                   const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmB2,
                   const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmR,
-                  const IgemmParams p) {
+                  const __grid_constant__ CUtensorMap tmRbox, const IgemmParams p) {
   using Cfg = TileCfg<T, BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr uint32_t kFmt = std::is_same<T, __half>::value ? 0u : (std::is_same<T, __nv_bfloat16>::value ? 1u : 2u);
@@ -145,6 +145,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   uint64_t* drain_bar = bars + 2 * kStages + 4;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 5);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint64_t* res_bar = bars + 2 * kStages + 6;     // [8 epilogue warps][2 staging buffers]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -160,6 +161,9 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     mbar_init(&tmem_empty[0], Cfg::kActiveEpiWarps * 32);
     mbar_init(&tmem_empty[1], Cfg::kActiveEpiWarps * 32);
     mbar_init(drain_bar, 1);
+    if constexpr (RES) {
+      for (int i = 0; i < 16; ++i) mbar_init(&res_bar[i], 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
@@ -374,6 +378,14 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const T* g_res = (RES && !p.lowc) ? static_cast<const T*>(p.residual) : nullptr;
     uint32_t tcount = 0;
     uint32_t store_seq = 0;
+    uint32_t res_phases = 0;
+    ResidualFetch rf;
+    rf.tm = (g_res != nullptr && p.tma_store) ? &tmRbox : nullptr;
+    rf.bars = res_bar + (warp - kFirstEpiWarp) * 2;
+    rf.phases = &res_phases;
+    rf.abort_flag = abort_flag;
+    rf.status_word = p.status;
+    rf.wait_limit = p.wait_limit;
     int staged_n_tile = -1;
     long long prof_ewait = 0, prof_t0 = p.prof ? clock64() : 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
@@ -404,10 +416,6 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int ow = rem - oh * p.OW;
         y_off = img * p.y_sn + oh * p.y_sh + ow * p.y_sw;
       }
-      // where this warp's residual rows start: with a dense NHWC y, output pixel m is at element m * y_row
-      const int m_first = m_tile * kBM + ew * 32;
-      const int res_rows = p.M - m_first < 32 ? p.M - m_first : 32;
-      const T* res_box = (g_res != nullptr && p.tma_store && res_rows > 0) ? g_res + m_first * p.y_row + n0 : nullptr;
       const long long et0 = p.prof ? clock64() : 0;
       bool ok = mbar_wait_bounded(&tmem_full[buf], bphase, abort_flag, p.status, kIncidentEpilogueWait, p.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
@@ -433,7 +441,7 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         // output map whose box is exactly that short (low-channel mode, 16-bit only)
         epilogue_store_tile<T, WC, RES>(t_row, n0, p.Kout, p.act, s_scale, s_bias,
                                    out_stage + (warp - kFirstEpiWarp) * 2 * 32 * kRowBytes, lane, &tmY, &tmA2, st_row,
-                                   st_img, st_rows, store_seq, res_box, p.y_row, res_rows, g_scale != nullptr);
+                                   st_img, st_rows, store_seq, &rf, g_scale != nullptr);
       } else {
 #pragma unroll 1
       for (int chunk = 0; chunk < WC / 32; ++chunk) {
@@ -495,7 +503,8 @@ conv_igemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <typename T, int BN>
 cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CUtensorMap& tmB,
-                       const CUtensorMap& tmB2, const CUtensorMap& tmY, const CUtensorMap& tmR, const IgemmParams& p,
+                       const CUtensorMap& tmB2, const CUtensorMap& tmY, const CUtensorMap& tmR, const CUtensorMap& tmRbox,
+                       const IgemmParams& p,
                        int grid, cudaStream_t stream) {
   using Cfg = TileCfg<T, BN>;
   cudaLaunchConfig_t cfg = {};
@@ -509,8 +518,8 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmA2, const CU
   cfg.attrs = attr;
   cfg.numAttrs = launch_overlap_enabled() ? 1 : 0;
   if (p.residual != nullptr)
-    return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, true>, tmA, tmA2, tmB, tmB2, tmY, tmR, p);
-  return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, false>, tmA, tmA2, tmB, tmB2, tmY, tmR, p);
+    return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, true>, tmA, tmA2, tmB, tmB2, tmY, tmR, tmRbox, p);
+  return cudaLaunchKernelEx(&cfg, conv_igemm_kernel<T, BN, false>, tmA, tmA2, tmB, tmB2, tmY, tmR, tmRbox, p);
 }
 
 template <typename T, int BN>
@@ -555,8 +564,9 @@ int igemm_stages(int dtype, int tile_n) {
 
 cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
                          const CUtensorMap& tmB, const CUtensorMap& tmB2, const CUtensorMap& tmY,
-                         const CUtensorMap& tmR, const IgemmParams& p, int grid, cudaStream_t stream) {
-#define FDNN_GO(T, BN) return launch_one<T, BN>(tmA, tmA2, tmB, tmB2, tmY, tmR, p, grid, stream);
+                         const CUtensorMap& tmR, const CUtensorMap& tmRbox, const IgemmParams& p, int grid,
+                         cudaStream_t stream) {
+#define FDNN_GO(T, BN) return launch_one<T, BN>(tmA, tmA2, tmB, tmB2, tmY, tmR, tmRbox, p, grid, stream);
   if (dtype == FDNN_F16) {
     if (tile_n == 64) FDNN_GO(__half, 64)
     if (tile_n == 128) FDNN_GO(__half, 128)

@@ -80,10 +80,13 @@ long long default_wait_limit_cycles();
 // Launchers (defined in conv_igemm_sm100.cu).  `dtype` is FDNN_F16/BF16/F32.
 // tmA2 / tmB2 are the low-half operands of the split-TF32 path (ignored for
 // 16-bit types); tmY is the output map used when p.tma_store is set; tmR covers the residual tensor
-// with one tile-sized box (L2 prefetch; read only when p.residual is set and y is dense NHWC).  Returns a cudaError_t from the launch.
+// with one tile-sized box (L2 prefetch; read only when p.residual is set and y is dense NHWC), tmRbox covers it
+// exactly as tmY covers y (32-row x 128-byte boxes the epilogue warps copy into their staging buffers).  Returns a
+// cudaError_t from the launch.
 cudaError_t launch_igemm(int dtype, int tile_n, const CUtensorMap& tmA, const CUtensorMap& tmA2,
                          const CUtensorMap& tmB, const CUtensorMap& tmB2, const CUtensorMap& tmY,
-                         const CUtensorMap& tmR, const IgemmParams& p, int grid, cudaStream_t stream);
+                         const CUtensorMap& tmR, const CUtensorMap& tmRbox, const IgemmParams& p, int grid,
+                         cudaStream_t stream);
 // Dynamic shared memory and pipeline depth of a tile configuration.
 int igemm_smem_bytes(int dtype, int tile_n);
 int igemm_stages(int dtype, int tile_n);
@@ -95,7 +98,7 @@ cudaError_t igemm_prepare_device();
 // tiles, TMA-store epilogue only (p.tma_store must be set).  `grid` must be even.
 cudaError_t launch_igemm_pair(int dtype, const CUtensorMap& tmA, const CUtensorMap& tmB,
                               const CUtensorMap& tmY, const CUtensorMap& tmY2, const CUtensorMap& tmR,
-                              const IgemmParams& p, int grid, cudaStream_t stream);
+                              const CUtensorMap& tmRbox, const IgemmParams& p, int grid, cudaStream_t stream);
 cudaError_t igemm_pair_prepare_device();
 int igemm_pair_smem_bytes();
 int igemm_pair_stages();

@@ -16,7 +16,8 @@ enum : uint32_t {
   kIncidentMmaWaitTmem = 3,    // MMA issuer: accumulator never drained
   kIncidentEpilogueWait = 4,   // epilogue: accumulator never completed
   kIncidentDrainWait = 5,      // teardown: outstanding copies never landed
-  kIncidentPartialWait = 6     // epilogue of a split tile: another pair's partial sums never arrived
+  kIncidentPartialWait = 6,    // epilogue of a split tile: another pair's partial sums never arrived
+  kIncidentResidualWait = 7    // epilogue: the residual box never landed in the staging buffer
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -147,15 +147,17 @@ __device__ __forceinline__ void words_to_pairs(const Words<VB>& r, F2 (&v)[VB / 
   }
 }
 
-// Shared memory rows of one block, fp32 [R*S + 2][pitch]: the taps of channels cbase .. cbase + cspan, then their
-// scale (1 when the call has none), then their bias (0 when none).
+// Shared memory of one block: fp32 pairs of neighbouring channels, [R*S + 2][V/2][tcx] — the taps of channels
+// cbase .. cbase + cspan, then their scale (1 when the call has none), then their bias (0 when none).  Thread tc
+// owns channels tc*V .. tc*V+V-1; with the thread index innermost the 32 lanes of a warp read 32 consecutive
+// 8-byte words, two wavefronts per load (rows of V floats per thread cost eight).
 template <typename T>
-__device__ __forceinline__ void fill_filter_rows(float* s_w, const DirectParams& p, int R, int S, int pitch,
+__device__ __forceinline__ void fill_filter_rows(float* s_w, const DirectParams& p, int R, int S, int V, int tcx,
                                                  int cbase, int cspan) {
   const T* w = static_cast<const T*>(p.w);
   const T* bias = static_cast<const T*>(p.bias);
   const T* scale = static_cast<const T*>(p.scale);
-  const int taps = R * S;
+  const int taps = R * S, h2 = V / 2;
   for (int i = threadIdx.x; i < (taps + 2) * cspan; i += blockDim.x) {
     const int tap = i / cspan, c = i - tap * cspan;
     float v;
@@ -167,19 +169,21 @@ __device__ __forceinline__ void fill_filter_rows(float* s_w, const DirectParams&
     } else {
       v = bias != nullptr ? to_f32<T>(bias[cbase + c]) : 0.0f;
     }
-    s_w[tap * pitch + c] = v;
+    const int tc = c / V, e = c - tc * V;
+    s_w[((tap * h2 + (e >> 1)) * tcx + tc) * 2 + (e & 1)] = v;
   }
 }
 
 // One output pixel's VB bytes of channels: scale and bias, residual, activation, one rounding, streaming store.
 template <typename T, int VB>
 __device__ __forceinline__ void emit_pixel(const F2 (&acc)[VB / (2 * sizeof(T))], const F2* s_scale, const F2* s_bias,
-                                           const T* res, T* y, int act) {
+                                           int pair_stride, const T* res, T* y, int act) {
   constexpr int H2 = VB / (2 * int(sizeof(T)));
   constexpr int V = 2 * H2;
   float v[V];
 #pragma unroll
-  for (int h = 0; h < H2; ++h) f2_split(f2_fma(acc[h], s_scale[h], s_bias[h]), v[2 * h], v[2 * h + 1]);
+  for (int h = 0; h < H2; ++h)
+    f2_split(f2_fma(acc[h], s_scale[h * pair_stride], s_bias[h * pair_stride]), v[2 * h], v[2 * h + 1]);
   if (res != nullptr) {
     const Words<VB> rw = load_words<VB>(res);
 #pragma unroll
@@ -214,7 +218,7 @@ __device__ __forceinline__ void emit_pixel(const F2 (&acc)[VB / (2 * sizeof(T))]
 // KR, KS, KSTRIDE: filter size and (equal) strides known at compile time, dilation 1 — every loop unrolls and
 // the tap a column serves for each output is resolved by the compiler; 0, 0, 0 takes everything from `p`.
 // VB: bytes of channels a thread owns (16, or 8 where more resident warps pay more than wider accesses).
-// Shared memory holds, as fp32 rows of tcx * V channels: the R*S taps, then the scale row, then the bias row.
+// Shared memory holds the R*S taps, the scale and the bias of the block's channels as fp32 pairs (fill_filter_rows).
 // All arithmetic is on pairs of neighbouring channels (fma.rn.f32x2: two independent, correctly rounded fp32
 // FMAs per instruction).
 template <typename T, int KR, int KS, int KSTRIDE, int VB>
@@ -232,13 +236,13 @@ depthwise_cl_kernel(const DirectParams p, const DwTiling g) {
   const int pitch = g.tcx * V;
   const int cbase = blockIdx.y * pitch;
   const int cspan = min(pitch, p.C - cbase);
-  fill_filter_rows<T>(s_w, p, R, S, pitch, cbase, cspan);
+  fill_filter_rows<T>(s_w, p, R, S, V, g.tcx, cbase, cspan);
   __syncthreads();
   const int tc = threadIdx.x % g.tcx, tp = threadIdx.x / g.tcx;
   if (tc * V >= cspan) return;
   const int c0 = cbase + tc * V;
-  const F2* s_mine = reinterpret_cast<const F2*>(s_w + tc * V);
-  const int pitch2 = pitch / 2;
+  const F2* s_mine = reinterpret_cast<const F2*>(s_w) + tc;   // pair h of tap t: s_mine[(t * H2 + h) * tcx]
+  const int tcx = g.tcx;
   const int act = p.act;
   constexpr int kSpanStatic = (PW - 1) * KSTRIDE + KS;           // input columns the PW outputs touch
   const int span = kStatic ? kSpanStatic : (PW - 1) * stride_w + (S - 1) * dil_w + 1;
@@ -296,9 +300,9 @@ depthwise_cl_kernel(const DirectParams p, const DwTiling g) {
           for (int q = 0; q < PW; ++q) {
             const int s = j - q * KSTRIDE;   // a constant once the loops are unrolled
             if (s >= 0 && s < KS) {
-              const F2* tap = s_mine + (r * KS + s) * pitch2;
+              const F2* tap = s_mine + (r * KS + s) * H2 * tcx;
 #pragma unroll
-              for (int h = 0; h < H2; ++h) acc[q][h] = f2_fma(xv[h], tap[h], acc[q][h]);
+              for (int h = 0; h < H2; ++h) acc[q][h] = f2_fma(xv[h], tap[h * tcx], acc[q][h]);
             }
           }
         }
@@ -319,9 +323,9 @@ depthwise_cl_kernel(const DirectParams p, const DwTiling g) {
             if (d < 0 || d % dil_w != 0) continue;
             const int s = d / dil_w;
             if (s >= S) continue;
-            const F2* tap = s_mine + (r * S + s) * pitch2;
+            const F2* tap = s_mine + (r * S + s) * H2 * tcx;
 #pragma unroll
-            for (int h = 0; h < H2; ++h) acc[q][h] = f2_fma(xv[h], tap[h], acc[q][h]);
+            for (int h = 0; h < H2; ++h) acc[q][h] = f2_fma(xv[h], tap[h * tcx], acc[q][h]);
           }
         }
       }
@@ -331,7 +335,7 @@ depthwise_cl_kernel(const DirectParams p, const DwTiling g) {
       const int ow = ow0 + q;
       if (ow >= p.OW) continue;
       const long long y_idx = oh * p.y_s[2] + ow * p.y_s[3];
-      emit_pixel<T, VB>(acc[q], s_mine + taps * pitch2, s_mine + (taps + 1) * pitch2,
+      emit_pixel<T, VB>(acc[q], s_mine + taps * H2 * tcx, s_mine + (taps + 1) * H2 * tcx, tcx,
                         res != nullptr ? res + y_idx : nullptr, yimg + y_idx, act);
     }
   }

@@ -988,6 +988,10 @@ EXTRA = {
                bound="hbm"),
     "dwcl": dict(desc="depthwise 3x3 conv (groups = C = K = 64) 56x56 N=256 bf16 channels-last + bias, stride 1 pad 1",
                  bound="hbm"),
+    # a grouped layer the reference times (benchmark/test_conv2d_perf.py:48) at a batch larger than L2: two groups
+    # of 32 -> 64 channels, one tensor-core launch per group
+    "grp": dict(desc="grouped 3x3 conv 64->128, groups = 2, 56x56 N=256 bf16 channels-last + bias, stride 1 pad 1",
+                bound="hbm"),
 }
 
 
@@ -1035,31 +1039,35 @@ def run_extra(args):
             return run, 2.0 * m * hw * hw * k * c, f"{m} of {n} images, conv2d*scale+bias, add, relu in bf16 on CPU"
         h2d, d2h = 2 * n * hw * hw * (c + k), 2 * n * hw * hw * k
         host_in = [t.contiguous(memory_format=torch.channels_last).cpu().pin_memory() for t in sets[0]]
-    elif args.workload in ("dw", "dwcl"):
+    elif args.workload in ("dw", "dwcl", "grp"):
         n, c, hw = 256, 64, 56
-        cl = args.workload == "dwcl"
-        w = rnd(c, 1, 3, 3, std=1 / 3)
-        bias = rnd(c, std=0.1)
-        per_set = 2 * 2 * n * c * hw * hw
+        cl = args.workload != "dw"
+        groups, k = (2, 128) if args.workload == "grp" else (c, c)
+        w = rnd(k, c // groups, 3, 3, std=(9 * c // groups) ** -0.5)
+        if cl:
+            w = w.contiguous(memory_format=torch.channels_last)
+        bias = rnd(k, std=0.1)
+        per_set = 2 * n * (c + k) * hw * hw
         n_sets = max(2, -(-3 * 126 * 2 ** 20 // per_set))
 
         def make_x():
             x = rnd(n, c, hw, hw)
             return x.contiguous(memory_format=torch.channels_last) if cl else x
         sets = [(make_x(),) for _ in range(n_sets)]
-        flops = 2.0 * n * c * hw * hw * 9
-        nbytes = per_set + 2 * (c * 9 + c)
+        flops = 2.0 * n * k * (c // groups) * hw * hw * 9
+        nbytes = per_set + 2 * (k * (c // groups) * 9 + k)
 
         def step(i):
-            return fd.conv2d(sets[i][0], w, bias, stride=1, padding=1, groups=c)
+            return fd.conv2d(sets[i][0], w, bias, stride=1, padding=1, groups=groups)
 
         def cpu_once(m):
             import oracle
 
             x, wc, bc = sets[0][0][:m].cpu(), w.cpu(), bias.cpu()
-            return ((lambda: oracle.conv2d_torch_cpu(x, wc, bc, 1, 1, 1, c, compute_dtype=bf)),
-                    2.0 * m * c * hw * hw * 9, f"{m} of {n} images, F.conv2d(groups={c}) in bf16 on CPU")
-        h2d, d2h = 2 * n * c * hw * hw, 2 * n * c * hw * hw
+            return ((lambda: oracle.conv2d_torch_cpu(x, wc, bc, 1, 1, 1, groups, compute_dtype=bf)),
+                    2.0 * m * k * (c // groups) * hw * hw * 9,
+                    f"{m} of {n} images, F.conv2d(groups={groups}) in bf16 on CPU")
+        h2d, d2h = 2 * n * c * hw * hw, 2 * n * k * hw * hw
         host_in = [sets[0][0].cpu().pin_memory()]
     else:
         m_, k_, n_ = 8192, 4096, 4096
@@ -1113,8 +1121,8 @@ def run_extra(args):
             d.copy_(h, non_blocking=True)
         if args.workload == "res":
             y = fd.conv2d_bias_act(dev_in[0], w, bias, scale=scale, relu=True, residual=dev_in[1])
-        elif args.workload in ("dw", "dwcl"):
-            y = fd.conv2d(dev_in[0], w, bias, stride=1, padding=1, groups=dev_in[0].shape[1])
+        elif args.workload in ("dw", "dwcl", "grp"):
+            y = fd.conv2d(dev_in[0], w, bias, stride=1, padding=1, groups=groups)
         else:
             y = fd.mm(dev_in[0], b_mat)
         host_out.copy_(y, non_blocking=True)

@@ -274,6 +274,26 @@ StreamK plan_stream_k(long long tiles, long long k_steps, int pairs, bool filter
   return r;
 }
 
+// Grouped layers that are not depthwise run as one tensor-core launch per group on strided views of x, w and y
+// (group g reads channels g*C/G.. of x, filters g*K/G.. of w and writes channels g*K/G.. of y), when the per-group
+// channel counts keep every group's pointers 16-byte aligned like the first group's, so that all groups get the
+// same plan.  The reference times such layers beside the dense ones (benchmark/test_conv2d_perf.py:48-49).
+bool group_loop_ok(const fdnn_conv_desc* d) {
+  if (d->groups <= 1 || d->groups > 64 || d->dtype == FDNN_F64) return false;
+  if ((d->algo & 0xff) == FDNN_ALGO_DIRECT || (d->algo & FDNN_ALGO_FLAG_OUT_F32) != 0) return false;
+  const int es = elem_size(d->dtype);
+  const int cg = d->c / d->groups, kg = d->k / d->groups;
+  return cg >= 8 && (cg * es) % 16 == 0 && (kg * es) % 16 == 0;
+}
+
+fdnn_conv_desc one_group_desc(const fdnn_conv_desc* d) {
+  fdnn_conv_desc sub = *d;
+  sub.c = d->c / d->groups;
+  sub.k = d->k / d->groups;
+  sub.groups = 1;
+  return sub;
+}
+
 int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void* y,
               fdnn_conv_plan* plan, bool allow_group = true) {
   int st = validate(d);
@@ -290,6 +310,20 @@ int make_plan(const fdnn_conv_desc* d, const void* x, const void* w, const void*
   const int cg = d->c / d->groups;
   plan->flops = 2.0 * m * d->k * cg * d->r * d->s;
   plan->bytes = es * (double(d->n) * d->c * d->h * d->w + double(d->k) * cg * d->r * d->s + d->k + m * d->k);
+
+  if (group_loop_ok(d)) {
+    const fdnn_conv_desc sub = one_group_desc(d);
+    fdnn_conv_plan ps;
+    if (make_plan(&sub, x, w, y, &ps, allow_group) == FDNN_OK && ps.algo != FDNN_ALGO_DIRECT) {
+      const double flops = plan->flops, bytes = plan->bytes;
+      *plan = ps;              // every group runs this plan; scratch is shared, the packed filters are not
+      plan->flops = flops;
+      plan->bytes = bytes;
+      plan->launches = ps.launches * d->groups;
+      plan->packed_weight_bytes = ps.packed_weight_bytes * d->groups;
+      return FDNN_OK;
+    }
+  }
 
   const bool geom_ok = igemm_geometry_ok(d) && m > 0 && m < 2.0e9;
   int algo = d->algo & 0xff;
@@ -946,6 +980,26 @@ int fdnn_conv2d_pack_weight(const fdnn_conv_desc* desc, const void* w, const voi
                             int64_t packed_bytes, void* stream) {
   fdnn_conv_desc d;
   if (desc == nullptr) return fail(FDNN_BAD_PARAM, "descriptor is NULL");
+  if (validate(desc) == FDNN_OK && group_loop_ok(desc)) {
+    // one packed filter per group, back to back
+    fdnn_conv_plan whole;
+    int gst = make_plan(desc, nullptr, reinterpret_cast<const void*>(uintptr_t(1)), y, &whole);
+    if (gst == FDNN_OK && whole.algo != FDNN_ALGO_DIRECT) {
+      if (w == nullptr || packed == nullptr) return fail(FDNN_BAD_PARAM, "w and packed must not be NULL");
+      if (packed_bytes < whole.packed_weight_bytes)
+        return fail(FDNN_WORKSPACE_TOO_SMALL, "packed filter buffer too small");
+      const fdnn_conv_desc sub = one_group_desc(desc);
+      const int es = elem_size(desc->dtype);
+      const long long per_group = whole.packed_weight_bytes / desc->groups;
+      for (int g = 0; g < desc->groups; ++g) {
+        const char* wg = static_cast<const char*>(w) + (long long)g * sub.k * desc->w_strides[0] * es;
+        const char* yg = y == nullptr ? nullptr : static_cast<const char*>(y) + (long long)g * sub.k * desc->y_strides[1] * es;
+        gst = fdnn_conv2d_pack_weight(&sub, wg, yg, static_cast<char*>(packed) + g * per_group, per_group, stream);
+        if (gst != FDNN_OK) return gst;
+      }
+      return FDNN_OK;
+    }
+  }
   d = *desc;
   // Planned as fdnn_conv2d_fwd will plan (same algo request; an unaligned filter pointer so that the answer
   // is "packed"; the y it will write, whose alignment decides between the generic [K,R,S,Cpad] layout and
@@ -1041,6 +1095,27 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
   if (x == nullptr || y == nullptr || (w == nullptr && w_packed == nullptr))
     return fail(FDNN_BAD_PARAM, "x, w and y must not be NULL");
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  if (d.groups > 1 && plan.algo != FDNN_ALGO_DIRECT) {
+    // one launch per group on views of the tensors (see group_loop_ok); the groups share the scratch, which the
+    // stream's order makes safe
+    const fdnn_conv_desc sub = one_group_desc(&d);
+    const int es = elem_size(d.dtype);
+    const long long per_group = plan.packed_weight_bytes / d.groups;
+    auto at = [es](const void* base, long long elems) -> const void* {
+      return base == nullptr ? nullptr : static_cast<const char*>(base) + elems * es;
+    };
+    for (int g = 0; g < d.groups; ++g) {
+      const long long k0 = (long long)g * sub.k;
+      st = fwd_impl(&sub, at(x, (long long)g * sub.c * d.x_strides[1]), at(w, k0 * d.w_strides[0]),
+                    w_packed == nullptr ? nullptr : static_cast<const char*>(w_packed) + g * per_group,
+                    at(bias, k0), at(scale, k0), at(residual, k0 * d.y_strides[1]), activation,
+                    const_cast<void*>(at(y, k0 * d.y_strides[1])), workspace, workspace_bytes, stream_v, allow_group,
+                    sub.k, sk_scratch, sk_bytes);
+      if (st != FDNN_OK) return st;
+    }
+    return FDNN_OK;
+  }
 
   if (plan.algo == FDNN_ALGO_DIRECT) {
     if (w == nullptr) return fail(FDNN_BAD_PARAM, "the direct path reads the unpacked filter; w is NULL");

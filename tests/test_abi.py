@@ -103,7 +103,7 @@ def test_query_routes_unsupported_geometry_to_direct(native_lib):
     for d in (_desc(groups=2), _desc(dtype=nat.F64), _desc(stride=9, h=40, w=40), _desc(pad=200, h=8, w=8)):
         assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
         assert plan.algo == nat.ALGO_DIRECT and plan.workspace_bytes == 0
-    d = _desc(groups=2, algo=nat.ALGO_IGEMM)
+    d = _desc(groups=16, algo=nat.ALGO_IGEMM)     # four channels per group: no tensor-core view of a group
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_NOT_SUPPORTED
     d = _desc(algo=nat.ALGO_IGEMM_PAIR, channels_last=False)  # NCHW output cannot go through the pair kernel
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_NOT_SUPPORTED
@@ -153,6 +153,28 @@ def test_query_tile_override_flags(native_lib):
     d = _desc(algo=nat.ALGO_FLAG_NO_PIXEL_GROUP, **narrow)
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
     assert plan.pixel_group <= 1 and grouped > 1, "the 64-channel 3x3 layer is the case pixel grouping exists for"
+
+
+def test_query_grouped_layers_run_one_launch_per_group(native_lib):
+    """groups > 1 with at least 8 channels per group and 16-byte multiples of channels on both sides: the plan of one
+    group, launched once per group, with one packed filter per group; depthwise and narrow groups stay direct."""
+    one, plan = nat.ConvPlan(), nat.ConvPlan()
+    sub = _desc(n=16, c=32, h=56, w=56, k=64, algo=nat.ALGO_IGEMM)
+    sub.w_strides[0] = 3 * 3 * 32
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(sub), None, 0x1002, None, ctypes.byref(one)) == nat.FDNN_OK
+    d = _desc(n=16, c=64, h=56, w=56, k=128, groups=2)                    # a grouped shape the reference times
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, 0x1002, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert plan.algo in (nat.ALGO_IGEMM, nat.ALGO_IGEMM_PAIR)
+    assert plan.launches == 2 * one.launches and plan.packed_weight_bytes == 2 * one.packed_weight_bytes
+    assert plan.flops == 2.0 * 16 * 56 * 56 * 128 * 32 * 9
+    d = _desc(n=16, c=128, h=28, w=28, k=128, groups=8)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert plan.algo == nat.ALGO_IGEMM and plan.launches % 8 == 0
+    for d in (_desc(n=16, c=64, h=56, w=56, k=64, groups=64), _desc(n=16, c=64, h=56, w=56, k=64, groups=16),
+              _desc(n=16, c=64, h=56, w=56, k=128, groups=2, algo=nat.ALGO_DIRECT),
+              _desc(dtype=nat.F32, n=16, c=20, h=56, w=56, k=20, groups=2)):     # 10 fp32 channels: 40 bytes
+        assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
+        assert plan.algo == nat.ALGO_DIRECT
 
 
 def test_query_unaligned_pointer_forces_repack(native_lib):

@@ -779,3 +779,43 @@ def test_depthwise_kernels_match_oracle_and_direct_kernel(fd, case):
     ref = torch.relu(oracle.conv2d_torch_cpu(x, w, b, stride, pad, dil, c, scale=sc) + shortcut.float().cpu())
     _check(fused, ref, dtype_name)
     assert fd.device_status() == 0
+
+
+GROUPED = [
+    # n, c, h, w, k, r, groups, stride, pad, dtype, channels_last
+    (4, 64, 56, 56, 128, 3, 2, 1, 1, "bfloat16", True),       # the reference's grouped perf shapes at a smaller batch
+    (8, 128, 28, 28, 128, 3, 8, 1, 1, "bfloat16", True),      # (benchmark/test_conv2d_perf.py:48-49)
+    (4, 64, 56, 56, 128, 3, 2, 1, 1, "float16", False),       # NCHW: every group's channels are relaid out
+    (4, 64, 30, 30, 96, 3, 2, 2, 1, "float32", True),         # fp32 (split TF32), stride 2, 48 filters per group
+    (4, 512, 14, 14, 512, 1, 4, 1, 0, "bfloat16", True),      # 1x1, 128 -> 128 per group
+    (3, 96, 17, 19, 48, 5, 3, 1, 2, "bfloat16", True),        # three groups of 32 -> 16, ragged sizes
+]
+
+
+@pytest.mark.parametrize("case", GROUPED, ids=[f"c{c[1]}k{c[4]}g{c[6]}_{c[9]}_{'cl' if c[10] else 'nchw'}" for c in GROUPED])
+def test_grouped_layers_on_the_tensor_core_path_match_oracle(fd, case):
+    """groups > 1 (not depthwise) with 16-byte multiples of channels per group: one tensor-core launch per group on
+    views of x, w and y; against the oracle, against the direct kernel, and with the full epilogue."""
+    n, c, h, w_, k, r, groups, stride, pad, dtype_name, cl = case
+    dtype = DTYPES[dtype_name]
+    x = _to_dev(_rand((n, c, h, w_), 90), dtype, cl)
+    w = _to_dev(_rand((k, c // groups, r, r), 91, std=(c // groups * r * r) ** -0.5), dtype, cl)
+    b = _to_dev(_rand((k,), 92, std=0.1), dtype, False)
+    sc = (torch.rand(k, generator=torch.Generator().manual_seed(93)) + 0.5).to(dtype).cuda()
+    plan = fd.conv2d_plan(x, w, stride=stride, padding=pad, groups=groups)
+    assert plan["algo"] != 1 and plan["launches"] % groups == 0, "expected one tensor-core launch per group"
+    got = fd.conv2d(x, w, b, stride=stride, padding=pad, groups=groups)
+    ref = oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, groups)
+    _check(got, ref, dtype_name)
+    fd.set_algo("direct")
+    try:
+        plain = fd.conv2d(x, w, b, stride=stride, padding=pad, groups=groups)
+    finally:
+        fd.set_algo("auto")
+    torch.testing.assert_close(got.float(), plain.float(), **TOL[dtype_name])
+    shortcut = _to_dev(_rand(tuple(got.shape), 94), dtype, cl)
+    fused = fd.conv2d_bias_act(x, w, b, stride=stride, padding=pad, groups=groups, scale=sc, relu=True,
+                               residual=shortcut)
+    ref = torch.relu(oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, groups, scale=sc) + shortcut.float().cpu())
+    _check(fused, ref, dtype_name)
+    assert fd.device_status() == 0

@@ -726,7 +726,13 @@ bool launch_overlap_enabled() {
 }
 
 namespace {
-long long* g_prof_buffer = nullptr;  // set through fdnn_debug_set_profile_buffer
+std::atomic<long long*> g_prof_buffer[64];  // per device ordinal; set through fdnn_debug_set_profile_buffer
+
+long long* prof_buffer_of_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  return g_prof_buffer[dev].load(std::memory_order_relaxed);
+}
 std::atomic<long long> g_wait_limit{0};  // 0: the default limit; set through fdnn_debug_set_wait_limit
 std::atomic<int> g_skip_copies{0};
 
@@ -859,7 +865,7 @@ int fwd_low_channel(const fdnn_conv_desc& d, const fdnn_conv_plan& plan, int dev
     p.slot_elems = int(lc.slot_bytes / es);
     p.k16_per_step = 3;
   }
-  p.prof = g_prof_buffer;
+  p.prof = prof_buffer_of_current_device();
   fill_debug_params(&p);
   p.status = g_status_ptr[dev];
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
@@ -1294,7 +1300,7 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
     st = encode_output_map(&tmRbox, d.dtype, const_cast<void*>(residual), d.k, p.M, p.y_row);
     if (st != FDNN_OK) return st;
   }
-  p.prof = g_prof_buffer;
+  p.prof = prof_buffer_of_current_device();
   fill_debug_params(&p);
   p.status = g_status_ptr[dev];
   if (p.status == nullptr) return fail(FDNN_CUDA_ERROR, "status word address unavailable");
@@ -1318,7 +1324,9 @@ static int fwd_impl(const fdnn_conv_desc* desc, const void* x, const void* w, co
 }
 
 int fdnn_debug_set_profile_buffer(void* device_buffer_16_int64) {
-  g_prof_buffer = static_cast<long long*>(device_buffer_16_int64);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(FDNN_CUDA_ERROR, "no current device");
+  g_prof_buffer[dev].store(static_cast<long long*>(device_buffer_16_int64), std::memory_order_relaxed);
   return FDNN_OK;
 }
 

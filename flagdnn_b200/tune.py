@@ -35,6 +35,7 @@ CANDIDATES = [
     ("cta256", nat.ALGO_IGEMM | nat.ALGO_FLAG_TILE_N_256 | nat.ALGO_FLAG_NO_PIXEL_GROUP),
     ("cta+group", nat.ALGO_IGEMM),
     ("pair", nat.ALGO_IGEMM_PAIR),
+    ("pair+split", nat.ALGO_IGEMM_PAIR | nat.ALGO_FLAG_STREAM_K),   # reduction steps shared evenly between the pairs
 ]
 
 

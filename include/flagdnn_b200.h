@@ -274,7 +274,8 @@ const char* fdnn_static_scratch_last_error(void);
  * kernel's first CTA writes per-role cycle counters into it on every launch
  * (producer: [0] stage-wait, [1] copy-issue, [2] total, [3] reduction steps;
  * issuer: [4] data-wait, [5] accumulator-wait, [6] total, [7] tiles;
- * epilogue: [8] accumulator-wait, [9] total).  NULL switches it off (default). */
+ * epilogue: [8] accumulator-wait, [9] total).  NULL switches it off (default).
+ * The setting belongs to the device that is current when this is called. */
 int fdnn_debug_set_profile_buffer(void* device_buffer_16_int64);
 
 /* Test aid for the bounded waits: launches made after this call give up a wait

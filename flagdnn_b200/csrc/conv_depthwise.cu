@@ -138,11 +138,7 @@ __device__ __forceinline__ void words_to_pairs(const Words<VB>& r, F2 (&v)[VB / 
     if constexpr (std::is_same<T, float>::value) {
       v[h] = f2_make(r.w[2 * h], r.w[2 * h + 1]);
     } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-#ifdef FDNN_DW_INT64_PAIRS
-      v[h] = (static_cast<F2>(r.w[h] & 0xffff0000u) << 32) | static_cast<F2>(r.w[h] << 16);
-#else
       v[h] = f2_make(r.w[h] << 16, r.w[h] & 0xffff0000u);
-#endif
     } else {
       float lo, hi;
       unpack2<T>(r.w[h], lo, hi);

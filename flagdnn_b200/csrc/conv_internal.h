@@ -160,6 +160,10 @@ cudaError_t launch_pack_w_lowc(int dtype, const void* w, const long long w_s[4],
 cudaError_t launch_pack_w_grouped(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
                                   int S, int stride_w, int q, int c_pad, void* dst, cudaStream_t stream);
 // w[K,C,R,S] (any strides) -> dense [K,R,S,c_pad]; f32 split like x.
+// A grouped filter as the dense channels-last [K][R][S][C] filter of the same convolution (zeros outside each
+// filter's own group of input channels).
+cudaError_t launch_densify_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R, int S, int groups,
+                             void* dense, cudaStream_t stream);
 cudaError_t launch_pack_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
                           int S, int c_pad, void* dst, long long plane_elems, cudaStream_t stream);
 

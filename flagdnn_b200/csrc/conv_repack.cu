@@ -331,6 +331,50 @@ cudaError_t launch_pack_w_grouped(int dtype, const void* w, const long long w_s[
   return cudaGetLastError();
 }
 
+// A grouped filter [K][C/G][R][S] (any strides) written as the dense channels-last filter [K][R][S][C] of the
+// same convolution: filter k keeps its group's C/G channels at their place among the C input channels and is zero
+// everywhere else (a block-diagonal GEMM operand).
+template <typename T>
+__global__ void densify_w_kernel(const T* __restrict__ w, long long s0, long long s1, long long s2, long long s3, int K,
+                                 int C, int R, int S, int groups, T* __restrict__ dense) {
+  const long long total = (long long)K * R * S * C;
+  const int cg = C / groups, kg = K / groups;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long t = i;
+    const int c = int(t % C); t /= C;
+    const int s = int(t % S); t /= S;
+    const int r = int(t % R); t /= R;
+    const int k = int(t);
+    const int local = c - (k / kg) * cg;
+    T v = static_cast<T>(0.0f);
+    if (local >= 0 && local < cg) v = w[k * s0 + local * s1 + r * s2 + s * s3];
+    dense[i] = v;
+  }
+}
+
+template <typename T>
+cudaError_t densify_w_t(const void* w, const long long w_s[4], int K, int C, int R, int S, int groups, void* dense,
+                        cudaStream_t stream) {
+  const long long total = (long long)K * R * S * C;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  if (blocks < 1) blocks = 1;
+  densify_w_kernel<T><<<int(blocks), 256, 0, stream>>>(static_cast<const T*>(w), w_s[0], w_s[1], w_s[2], w_s[3], K, C, R,
+                                                       S, groups, static_cast<T*>(dense));
+  return cudaGetLastError();
+}
+
+cudaError_t launch_densify_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R, int S, int groups,
+                             void* dense, cudaStream_t stream) {
+  switch (dtype) {
+    case FDNN_F16: return densify_w_t<__half>(w, w_s, K, C, R, S, groups, dense, stream);
+    case FDNN_BF16: return densify_w_t<__nv_bfloat16>(w, w_s, K, C, R, S, groups, dense, stream);
+    case FDNN_F32: return densify_w_t<float>(w, w_s, K, C, R, S, groups, dense, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
 cudaError_t launch_pack_w(int dtype, const void* w, const long long w_s[4], int K, int C, int R,
                           int S, int c_pad, void* dst, long long plane_elems, cudaStream_t stream) {
   switch (dtype) {

@@ -100,7 +100,7 @@ def test_query_plans_headline_configs(native_lib):
 
 def test_query_routes_unsupported_geometry_to_direct(native_lib):
     plan = nat.ConvPlan()
-    for d in (_desc(groups=2), _desc(dtype=nat.F64), _desc(stride=9, h=40, w=40), _desc(pad=200, h=8, w=8)):
+    for d in (_desc(groups=2, n=1), _desc(dtype=nat.F64), _desc(stride=9, h=40, w=40), _desc(pad=200, h=8, w=8)):
         assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
         assert plan.algo == nat.ALGO_DIRECT and plan.workspace_bytes == 0
     d = _desc(groups=16, algo=nat.ALGO_IGEMM)     # four channels per group: no tensor-core view of a group
@@ -155,24 +155,34 @@ def test_query_tile_override_flags(native_lib):
     assert plan.pixel_group <= 1 and grouped > 1, "the 64-channel 3x3 layer is the case pixel grouping exists for"
 
 
-def test_query_grouped_layers_run_one_launch_per_group(native_lib):
-    """groups > 1 with at least 8 channels per group and 16-byte multiples of channels on both sides: the plan of one
-    group, launched once per group, with one packed filter per group; depthwise and narrow groups stay direct."""
-    one, plan = nat.ConvPlan(), nat.ConvPlan()
-    sub = _desc(n=16, c=32, h=56, w=56, k=64, algo=nat.ALGO_IGEMM)
-    sub.w_strides[0] = 3 * 3 * 32
-    assert native_lib.fdnn_conv2d_query(ctypes.byref(sub), None, 0x1002, None, ctypes.byref(one)) == nat.FDNN_OK
+def test_query_grouped_layers_take_a_tensor_core_route(native_lib):
+    """groups > 1, not depthwise.  Up to eight groups: one dense convolution with a block-diagonal filter (the dense
+    plan, plus room for the dense filter in front of the packed one).  More groups with at least 8 channels and
+    16-byte multiples of channels per group: the plan of one group, launched once per group, one packed filter per
+    group.  Depthwise, narrow groups and a forced direct kernel stay direct."""
+    dense, one, plan = nat.ConvPlan(), nat.ConvPlan(), nat.ConvPlan()
     d = _desc(n=16, c=64, h=56, w=56, k=128, groups=2)                    # a grouped shape the reference times
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, 0x1002, None, ctypes.byref(plan)) == nat.FDNN_OK
-    assert plan.algo in (nat.ALGO_IGEMM, nat.ALGO_IGEMM_PAIR)
-    assert plan.launches == 2 * one.launches and plan.packed_weight_bytes == 2 * one.packed_weight_bytes
-    assert plan.flops == 2.0 * 16 * 56 * 56 * 128 * 32 * 9
+    v = _desc(n=16, c=64, h=56, w=56, k=128)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(v), None, None, None, ctypes.byref(dense)) == nat.FDNN_OK
+    assert plan.algo == dense.algo and plan.algo != nat.ALGO_DIRECT and plan.launches == dense.launches
+    assert (plan.tile_n, plan.pixel_group, plan.grid) == (dense.tile_n, dense.pixel_group, dense.grid)
+    assert plan.w_packed == 1 and plan.packed_weight_bytes == 128 * 9 * 64 * 2 + dense.packed_weight_bytes
+    assert plan.flops == 2.0 * 16 * 56 * 56 * 128 * 32 * 9                # the layer's work, not the dense GEMM's
     d = _desc(n=16, c=128, h=28, w=28, k=128, groups=8)
     assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
-    assert plan.algo == nat.ALGO_IGEMM and plan.launches % 8 == 0
+    assert plan.algo != nat.ALGO_DIRECT and plan.packed_weight_bytes >= 128 * 9 * 128 * 2
+
+    sub = _desc(n=16, c=16, h=28, w=28, k=32, algo=nat.ALGO_IGEMM)
+    sub.w_strides[0] = 3 * 3 * 16
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(sub), None, 0x1002, None, ctypes.byref(one)) == nat.FDNN_OK
+    d = _desc(n=16, c=256, h=28, w=28, k=512, groups=16, algo=nat.ALGO_IGEMM)
+    assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, 0x1002, None, ctypes.byref(plan)) == nat.FDNN_OK
+    assert plan.algo == nat.ALGO_IGEMM
+    assert plan.launches == 16 * one.launches and plan.packed_weight_bytes == 16 * one.packed_weight_bytes
     for d in (_desc(n=16, c=64, h=56, w=56, k=64, groups=64), _desc(n=16, c=64, h=56, w=56, k=64, groups=16),
               _desc(n=16, c=64, h=56, w=56, k=128, groups=2, algo=nat.ALGO_DIRECT),
-              _desc(dtype=nat.F32, n=16, c=20, h=56, w=56, k=20, groups=2)):     # 10 fp32 channels: 40 bytes
+              _desc(dtype=nat.F32, n=16, c=160, h=56, w=56, k=160, groups=16)):     # 10 fp32 channels: 40 bytes
         assert native_lib.fdnn_conv2d_query(ctypes.byref(d), None, None, None, ctypes.byref(plan)) == nat.FDNN_OK
         assert plan.algo == nat.ALGO_DIRECT
 

@@ -789,13 +789,17 @@ GROUPED = [
     (4, 64, 30, 30, 96, 3, 2, 2, 1, "float32", True),         # fp32 (split TF32), stride 2, 48 filters per group
     (4, 512, 14, 14, 512, 1, 4, 1, 0, "bfloat16", True),      # 1x1, 128 -> 128 per group
     (3, 96, 17, 19, 48, 5, 3, 1, 2, "bfloat16", True),        # three groups of 32 -> 16, ragged sizes
+    (8, 256, 28, 28, 256, 3, 16, 1, 1, "bfloat16", True),     # sixteen groups: one launch per group
+    (8, 256, 28, 28, 512, 3, 16, 1, 1, "float16", False),     # ... from NCHW tensors
+    (16, 8, 64, 64, 32, 3, 2, 1, 1, "bfloat16", True),        # two groups of 4 -> 16 channels: dense 8 -> 32
 ]
 
 
 @pytest.mark.parametrize("case", GROUPED, ids=[f"c{c[1]}k{c[4]}g{c[6]}_{c[9]}_{'cl' if c[10] else 'nchw'}" for c in GROUPED])
 def test_grouped_layers_on_the_tensor_core_path_match_oracle(fd, case):
-    """groups > 1 (not depthwise) with 16-byte multiples of channels per group: one tensor-core launch per group on
-    views of x, w and y; against the oracle, against the direct kernel, and with the full epilogue."""
+    """groups > 1, not depthwise: up to eight groups run as one dense convolution with a block-diagonal filter, more
+    groups as one tensor-core launch per group on views of x, w and y; against the oracle, against the direct
+    kernel, and with the full epilogue."""
     n, c, h, w_, k, r, groups, stride, pad, dtype_name, cl = case
     dtype = DTYPES[dtype_name]
     x = _to_dev(_rand((n, c, h, w_), 90), dtype, cl)
@@ -803,7 +807,9 @@ def test_grouped_layers_on_the_tensor_core_path_match_oracle(fd, case):
     b = _to_dev(_rand((k,), 92, std=0.1), dtype, False)
     sc = (torch.rand(k, generator=torch.Generator().manual_seed(93)) + 0.5).to(dtype).cuda()
     plan = fd.conv2d_plan(x, w, stride=stride, padding=pad, groups=groups)
-    assert plan["algo"] != 1 and plan["launches"] % groups == 0, "expected one tensor-core launch per group"
+    assert plan["algo"] != 1, "expected a tensor-core route"
+    if groups > 8:
+        assert plan["launches"] % groups == 0, "expected one launch per group"
     got = fd.conv2d(x, w, b, stride=stride, padding=pad, groups=groups)
     ref = oracle.conv2d_torch_cpu(x, w, b, stride, pad, 1, groups)
     _check(got, ref, dtype_name)

@@ -103,13 +103,16 @@ typedef struct fdnn_conv_plan {
   int32_t w_packed;             /* 1: fwd needs a packed filter from fdnn_conv2d_pack_weight */
   int32_t c_padded;             /* channel count the igemm kernel iterates over */
   int32_t grid, block;          /* launch shape of the main kernel */
-  int32_t launches;             /* kernels one fwd call launches (main + repack) */
+  int32_t launches;             /* kernels one fwd call launches (main + repack; per-group launches of a
+                                   grouped layer all counted) */
   int32_t low_channel;          /* 1: C <= 4 path (pixel quads as GEMM rows, 16-pixel input windows) */
   int32_t pixel_group;          /* > 1: that many neighbouring output pixels form one GEMM row (narrow layers) */
   int32_t stream_k;             /* 1: given streamk_bytes of scratch, fdnn_conv2d_fwd_ex splits reductions over the CTA pairs */
   int64_t workspace_bytes;      /* scratch fwd needs (0 when x is consumed in place) */
   int64_t streamk_bytes;        /* size of that optional scratch (0: the plan does not split) */
-  int64_t packed_weight_bytes;  /* size of the packed filter (0 when w is consumed in place) */
+  int64_t packed_weight_bytes;  /* size of the packed filter (0 when w is consumed in place); for a grouped
+                                   layer the dense block-diagonal filter plus its packed form, or one
+                                   packed filter per group back to back */
   int64_t smem_bytes;           /* dynamic shared memory of the main kernel */
   double flops;                 /* 2*N*OH*OW*K*(C/groups)*R*S, benchmark/test_conv2d_perf.py:139-148 */
   double bytes;                 /* x + w + bias + y once each, benchmark/base.py:661-668 */

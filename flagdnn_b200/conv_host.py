@@ -66,8 +66,9 @@ def _streamk_scratch(device: torch.device, stream: int, nbytes: int) -> torch.Te
     return buf
 
 
-_WORKSPACE: "dict[tuple, torch.Tensor]" = {}
+_WORKSPACE: "OrderedDict[tuple, torch.Tensor]" = OrderedDict()
 _WORKSPACE_KEEP_BYTES = 256 << 20
+_WORKSPACE_KEEP_STREAMS = 8
 
 
 def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
@@ -80,10 +81,13 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
     key = (device.index, stream)
     buf = _WORKSPACE.get(key)
     if buf is not None and buf.numel() >= nbytes:
+        _WORKSPACE.move_to_end(key)
         return buf
     buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
     if nbytes <= _WORKSPACE_KEEP_BYTES:
         _WORKSPACE[key] = buf
+        while len(_WORKSPACE) > _WORKSPACE_KEEP_STREAMS:   # the streams used longest ago give their buffers back
+            _WORKSPACE.popitem(last=False)
     return buf
 
 

@@ -369,3 +369,19 @@ def test_conv2d_plan_reports_library_decision(native_lib):
     w = torch.empty(256, 256, 3, 3, dtype=torch.bfloat16).contiguous(memory_format=torch.channels_last)
     plan = flag_dnn.conv2d_plan(x, w, padding=1)
     assert plan["algo"] == 3 and plan["tile_n"] == 256 and plan["x_repacked"] == 0 and plan["w_packed"] == 0
+
+
+def test_tune_tool_needs_a_gpu_and_says_so():
+    """`python -m flagdnn_b200.tune` measures on the device: without one it explains itself and exits with 2
+    instead of falling back to anything."""
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present: the tool would run its sweep")
+    proc = subprocess.run([sys.executable, "-m", "flagdnn_b200.tune", "--batch", "2"], capture_output=True, text=True,
+                          cwd=ROOT, timeout=300)
+    assert proc.returncode == 2
+    assert "needs a CUDA device" in proc.stderr

@@ -1305,6 +1305,73 @@ def run_reference_gpu(args):
         clocks=clocks.summary(), gpu_launches=0)))
 
 
+def run_reference_gpu_extra(args):
+    """The reference's eager conv2d on the depthwise / grouped workloads (its Triton depthwise kernels,
+    src/flag_dnn/ops/conv2d.py:2613 and :3089, and its grouped path), same tensors and timing as run_extra."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+
+    base = {"impl": "reference-gpu", "metric": "fused_conv2d_tflops", "unit": "TFLOP/s", "n_gpus": 1,
+            "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "description": EXTRA[args.workload]["desc"]}}
+    try:
+        flag_dnn = _import_reference_gpu()
+    except Exception as exc:
+        print(json.dumps(dict(base, unavailable=f"{type(exc).__name__}: {str(exc)[:200]}")))
+        return
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    g = torch.Generator(device=device).manual_seed(4321)
+    n, c, hw = 256, 64, 56
+    cl = args.workload != "dw"
+    groups, k = (2, 128) if args.workload == "grp" else (c, c)
+
+    def rnd(*shape, std=1.0):
+        return (torch.randn(*shape, generator=g, device=device) * std).to(torch.bfloat16)
+
+    w = rnd(k, c // groups, 3, 3, std=(9 * c // groups) ** -0.5)
+    if cl:
+        w = w.contiguous(memory_format=torch.channels_last)
+    bias = rnd(k, std=0.1)
+    per_set = 2 * n * (c + k) * hw * hw
+    n_sets = max(2, -(-3 * 126 * 2 ** 20 // per_set))
+    xs = [rnd(n, c, hw, hw) for _ in range(n_sets)]
+    if cl:
+        xs = [x.contiguous(memory_format=torch.channels_last) for x in xs]
+    try:
+        call = lambda x: flag_dnn.ops.conv2d(x, w, bias, stride=1, padding=1, groups=groups)
+        t_first = time.perf_counter()
+        y0 = call(xs[0])
+        torch.cuda.synchronize()
+        first_call_s = time.perf_counter() - t_first
+        for i in range(max(3, args.warmup)):
+            call(xs[i % n_sets])
+        torch.cuda.synchronize()
+        steps = max(1, min(args.steps, 200))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            call(xs[i % n_sets])
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+    except Exception as exc:
+        print(json.dumps(dict(base, unavailable=f"the reference's GPU path failed: {type(exc).__name__}: {str(exc)[:300]}")))
+        return
+    import oracle
+
+    ref = oracle.conv2d_torch_cpu(xs[0][:1], w, bias, 1, 1, 1, groups)
+    err = float((y0[:1].float().cpu() - ref).abs().max())
+    flops = 2.0 * n * k * (c // groups) * hw * hw * 9
+    nbytes = per_set + 2 * (k * (c // groups) * 9 + k)
+    print(json.dumps(dict(
+        base, value=flops / (ms * 1e-3) / 1e12, steps=steps, warmup=max(3, args.warmup), ms_per_step=ms,
+        scaling="weak", vs_baseline=None, first_call_seconds=first_call_s,
+        launch="eager calls through the reference's public API", l2=f"{n_sets} rotating x sets",
+        hbm_gbs=nbytes / (ms * 1e-3) / 1e9, max_abs_err_image0_vs_fp32_oracle=err, gpu_launches=0)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1321,8 +1388,11 @@ def main():
                     help="skip the end-to-end and CPU-baseline legs (short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference-gpu":
+        if args.workload in ("dw", "dwcl", "grp"):
+            run_reference_gpu_extra(args)
+            return
         if args.workload not in WORKLOADS:
-            raise SystemExit("--impl reference-gpu measures the single-layer workloads c1..c4")
+            raise SystemExit("--impl reference-gpu measures the single-layer workloads c1..c4, dw, dwcl and grp")
         run_reference_gpu(args)
         return
     if args.workload in EXTRA:
